@@ -1,0 +1,50 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+# Tolerances of the parity gate for fp16 kernels against the fp32 oracle on
+# identical fp16-valued inputs (outputs and every gradient).
+REL_L2_TOL = 2e-3
+MAX_ABS_TOL = 1e-2
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def golden(name):
+    """Load tests/golden/<name>.npz as a dict of torch tensors (fp16 arrays -> fp32)."""
+    out = {}
+    with np.load(os.path.join(GOLDEN, name + ".npz")) as f:
+        for k in f.files:
+            a = f[k]
+            t = torch.from_numpy(np.ascontiguousarray(a)) if a.ndim else torch.tensor(a.item())
+            out[k] = t.float() if t.dtype == torch.float16 else t
+    return out
+
+
+@pytest.fixture(scope="session")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+def assert_close(got, want, what, rel=REL_L2_TOL, mabs=MAX_ABS_TOL):
+    from oracle.rfa_oracle import max_abs, rel_l2
+    got = got.detach().float().cpu()
+    want = want.detach().float().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    r, m = rel_l2(got, want), max_abs(got, want)
+    assert r <= rel and m <= mabs, f"{what}: rel-L2 {r:.3e} (tol {rel}), max-abs {m:.3e} (tol {mabs})"
+    return r, m
