@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the RFA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
+
+One "step" = causal RFA forward + backward at the upstream kernel boundary
+(``RFA.apply`` on given features and its gradient) on one batch of synthetic input:
+batch 8, heads 16, seq 2048, head_dim 64, proj_dim 64 (phi width 128), fp16.
+Metric: tokens/s with tokens = batch * seq per step; with N GPUs every rank runs
+its own batch (weak scaling over batch x heads, no collective on the data path).
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` instead times the CPU
+restatement of upstream's PyTorch path (oracle/rfa_oracle.py) on the host cores,
+on a bounded slice of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B, H, T, D_HEAD, D_PROJ = 8, 16, 2048, 64, 64
+K_FEAT = 2 * D_PROJ
+BH = B * H
+TOKENS_PER_STEP = B * T
+# algorithmic bytes per (token, head): fwd reads q,k (2*K*2) + v (d*2), writes out (d*2);
+# bwd reads q,k,v,g and writes gq,gk (2*K*2) + gv (d*2)
+BYTES_FWD = 2 * K_FEAT * 2 + 2 * D_HEAD * 2                       # 768
+BYTES_BWD_Q = 2 * K_FEAT * 2 + 2 * D_HEAD * 2 + K_FEAT * 2          # 1024  (q,k,v,g in; gq out)
+BYTES_BWD_KV = 2 * K_FEAT * 2 + 2 * D_HEAD * 2 + K_FEAT * 2 + D_HEAD * 2   # 1152  (q,k,v,g in; gk,gv out)
+BYTES_PATH = 2176                                                 # fwd 768 + bwd (768 in + 640 out)
+WORKLOAD = f"causal RFA fwd+bwd, B{B} H{H} T{T} d{D_HEAD} D{D_PROJ} fp16, RFA.apply boundary"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_inputs(seed, device):
+    """q,k,v,g for the workload.  Features come from the feature map of N(0,1) vectors
+    (seed 0) with one orthogonal random matrix per head (numpy seed 1), v and the upstream
+    gradient are N(0,1); everything rounded to fp16."""
+    from rfa_b200 import ops
+    from rfa_b200.construct_random_matrices import orf
+    import numpy as np
+    np.random.seed(1)
+    w = torch.tensor(np.stack([orf(head_dim=D_HEAD, proj_dim=D_PROJ) for _ in range(H)]), dtype=torch.float32)
+    g = torch.Generator().manual_seed(seed)
+    xq = torch.randn(T, B, H, D_HEAD, generator=g).half()
+    xk = torch.randn(T, B, H, D_HEAD, generator=g).half()
+    v = torch.randn(T, B, H, D_HEAD, generator=g).half()
+    up = torch.randn(T, B, H, D_HEAD, generator=g).half()
+    wd = w.to(device)
+    q = ops.feature_map_fwd(xq.to(device), wd, 0.1).view(T, BH, K_FEAT)
+    k = ops.feature_map_fwd(xk.to(device), wd, 0.1).view(T, BH, K_FEAT)
+    return q, k, v.to(device).view(T, BH, D_HEAD), up.to(device).view(T, BH, D_HEAD), (xq, xk, w)
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                            "samples": len(sm)}
+
+
+def timed(fn, iters, stream):
+    """Average device milliseconds per call of fn over iters calls (CUDA events on stream)."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(iters):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def cpu_port_sample(threads=None):
+    """Upstream's PyTorch path restated on the CPU (oracle), fwd+bwd, on a BH slice of the workload.
+    Returns (tokens_per_s for the FULL workload by linear scaling in BH, cores, description, seconds)."""
+    from oracle import rfa_oracle as O
+    if threads:
+        torch.set_num_threads(threads)
+    bh = 32
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(T, bh, K_FEAT, generator=g) * 0.1
+    k = torch.randn(T, bh, K_FEAT, generator=g) * 0.1
+    v = torch.randn(T, bh, D_HEAD, generator=g)
+    up = torch.randn(T, bh, D_HEAD, generator=g)
+    O.causal_forward(q[:256], k[:256], v[:256])     # warm the thread pool
+    t0 = time.perf_counter()
+    O.causal_forward(q, k, v)
+    O.causal_backward(q, k, v, up)
+    dt = time.perf_counter() - t0
+    full = dt * (BH / bh)
+    return TOKENS_PER_STEP / full, torch.get_num_threads(), f"BH={bh} of {BH} heads at full T={T}, fp32, scaled linearly in BH", dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    samples = []
+    for i in range(args.warmup + args.steps):
+        tps, cores, desc, dt = cpu_port_sample()
+        if i >= args.warmup:
+            samples.append((tps, dt))
+    tps = statistics.median(s[0] for s in samples)
+    ms = TOKENS_PER_STEP / tps * 1e3
+    line = {"impl": "reference", "metric": "causal_rfa_fwd_bwd_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "CPU restatement of upstream rfa.py:47-103 (PyTorch), host cores"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def extras(device, stream, hbm):
+    """Secondary measurements: decode (config 4), cross attention (config 3), feature map."""
+    from rfa_b200 import ops
+    out = {}
+    # ---- incremental decoding: B64 H16, fp32 state, prefill 512 tokens, 4096 fused steps
+    try:
+        Bd, Hd, steps, chunk = 64, 16, 4096, 128
+        g = torch.Generator().manual_seed(3)
+        import numpy as np
+        from rfa_b200.construct_random_matrices import orf
+        np.random.seed(1)
+        w = torch.tensor(np.stack([orf(head_dim=64, proj_dim=64) for _ in range(Hd)]), dtype=torch.float32, device=device)
+        pre = [torch.randn(512, Bd, Hd, 64, generator=g).half().to(device) for _ in range(3)]
+        pq = ops.feature_map_fwd(pre[0], w, 0.1).view(512, Bd * Hd, 128)
+        pk = ops.feature_map_fwd(pre[1], w, 0.1).view(512, Bd * Hd, 128)
+        _, s, z = ops.causal_fwd(pq, pk, pre[2].view(512, Bd * Hd, 64), return_state=True)
+        s, z = s.view(Bd, Hd, 128, 64), z.view(Bd, Hd, 128)
+        qs, ks, vs = (torch.randn(chunk, Bd, Hd, 64, generator=g).half().to(device) for _ in range(3))
+        o = torch.empty(chunk, Bd, Hd, 64, dtype=torch.half, device=device)
+
+        def run_chunk():
+            for i in range(chunk):
+                ops.decode_step_fused(qs[i], ks[i], vs[i], w, 0.1, s, z, o[i])
+        run_chunk()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run_chunk()
+        stream = torch.cuda.current_stream()
+        graph.replay()
+        ms = timed(graph.replay, steps // chunk, stream) / chunk           # per decode step
+        per_step_bytes = Bd * Hd * 67328
+        out["decode"] = {"workload": "decode B64 H16 d64 D64, fp32 state, fused feature map, CUDA graph of 128 steps",
+                         "tokens_per_s": Bd / (ms * 1e-3), "us_per_step": ms * 1e3,
+                         "algorithmic_GBps": per_step_bytes / (ms * 1e-3) / 1e9,
+                         "frac_of_hbm": per_step_bytes / (ms * 1e-3) / 1e9 / hbm,
+                         "note": "state (34 MB) fits in L2; algorithmic bytes, not DRAM bytes"}
+        del graph
+    except Exception as e:  # noqa: BLE001
+        out["decode"] = {"error": repr(e)}
+    # ---- cross attention fwd+bwd: B16 H16 Tq=Tk=1024, key lengths U[512,1024]
+    try:
+        Bc, Hc, Tq = 16, 16, 1024
+        g = torch.Generator().manual_seed(2)
+        lens = torch.randint(512, 1025, (Bc,), generator=g)
+        pad = (torch.arange(Tq)[None] >= lens[:, None]).to(device)
+        pq = (torch.randn(Tq, Bc, Hc, 128, generator=g) * 0.1).half().to(device)
+        pk = (torch.randn(Tq, Bc, Hc, 128, generator=g) * 0.1).half().to(device)
+        v = torch.randn(Tq, Bc, Hc, 64, generator=g).half().to(device)
+        up = torch.randn(Tq, Bc, Hc, 64, generator=g).half().to(device)
+
+        def cross_step():
+            s, z = ops.cross_state_fwd(pk, v, pad)
+            ops.cross_query_fwd(pq, s, z)
+            _, d_s, d_z = ops.cross_query_bwd(pq, s, z, up)
+            ops.cross_state_bwd(pk, v, pad, d_s, d_z)
+        for _ in range(3):
+            cross_step()
+        ms = timed(cross_step, 10, stream)
+        nbytes = Tq * Bc * Hc * BYTES_PATH
+        out["cross"] = {"workload": "cross RFA fwd+bwd B16 H16 Tq=Tk=1024 fp16, given features",
+                        "query_tokens_per_s": Bc * Tq / (ms * 1e-3), "ms": ms,
+                        "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm}
+    except Exception as e:  # noqa: BLE001
+        out["cross"] = {"error": repr(e)}
+    # ---- feature map alone at the causal workload's shape
+    try:
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(T, B, H, 64, generator=g).half().to(device)
+        w = torch.randn(H, 64, 64, generator=g).to(device)
+        gp = torch.randn(T, B, H, 128, generator=g).half().to(device)
+        for _ in range(3):
+            ops.feature_map_fwd(x, w, 0.1)
+        ms_f = timed(lambda: ops.feature_map_fwd(x, w, 0.1), 10, stream)
+        ms_b = timed(lambda: ops.feature_map_bwd(x, w, gp, 0.1, True), 10, stream)
+        nb = T * BH * 384
+        out["feature_map"] = {"fwd_ms": ms_f, "fwd_GBps": nb / (ms_f * 1e-3) / 1e9, "fwd_frac_of_hbm": nb / (ms_f * 1e-3) / 1e9 / hbm,
+                              "bwd_ms": ms_b, "bwd_GBps": T * BH * 512 / (ms_b * 1e-3) / 1e9}
+    except Exception as e:  # noqa: BLE001
+        out["feature_map"] = {"error": repr(e)}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from rfa_b200 import ops
+    from rfa_b200.rfa import RFA
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU baseline")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    hbm, peak_src = peaks()
+    stream = torch.cuda.current_stream()
+    q, k, v, up, _ = make_inputs(rank, device)
+    gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    out = torch.empty_like(v)
+    lib = ops._lib.load()
+    nws = lib.rfa_causal_workspace_bytes(T, BH, K_FEAT, D_HEAD)
+    ws = torch.empty(max(nws, 256), dtype=torch.uint8, device=device)
+    P, st = ops.ptr, stream.cuda_stream
+
+    def fwd():
+        ops.check(lib.rfa_causal_fwd(P(q), P(k), P(v), P(out), None, None, None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD, st), "fwd")
+
+    def bwd_q():
+        ops.check(lib.rfa_causal_bwd_q(P(q), P(k), P(v), P(up), P(gq), None, None, None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD, st), "bwd_q")
+
+    def bwd_kv():
+        ops.check(lib.rfa_causal_bwd_kv(P(q), P(k), P(v), P(up), P(gk), P(gv), None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD, st), "bwd_kv")
+
+    def step():
+        fwd(); bwd_q(); bwd_kv()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    with ClockSampler(local_rank) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        total_ms = e0.elapsed_time(e1)
+        # per-kernel durations, also inside the sampled region
+        per = {"causal_fwd": timed(fwd, args.steps, stream), "causal_bwd_q": timed(bwd_q, args.steps, stream),
+               "causal_bwd_kv": timed(bwd_kv, args.steps, stream)}
+    t = torch.tensor([total_ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * TOKENS_PER_STEP / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the timed region
+    e2e_steps = min(args.steps, 5)
+    hq, hk, hv, hg = (x.cpu().pin_memory() for x in (q, k, v, up))
+    ho = [torch.empty_like(x, device="cpu").pin_memory() for x in (out, q, k, v)]
+
+    def e2e_step():
+        dq = hq.to(device, non_blocking=True).requires_grad_(True)
+        dk = hk.to(device, non_blocking=True).requires_grad_(True)
+        dv = hv.to(device, non_blocking=True).requires_grad_(True)
+        dg = hg.to(device, non_blocking=True)
+        o = RFA.apply(dq, dk, dv)
+        o.backward(dg)
+        for dst, src in zip(ho, (o.detach(), dq.grad, dk.grad, dv.grad)):
+            dst.copy_(src, non_blocking=True)
+    e2e_step()
+    barrier()
+    e2e_ms = timed(e2e_step, e2e_steps, stream)
+    t = torch.tensor([e2e_ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hg))
+    d2h = sum(x.numel() * x.element_size() for x in ho)
+
+    if rank == 0:
+        units = T * BH
+        kbytes = {"causal_fwd": BYTES_FWD, "causal_bwd_q": BYTES_BWD_Q, "causal_bwd_kv": BYTES_BWD_KV}
+        dom = max(per, key=per.get)
+        achieved = units * kbytes[dom] / (per[dom] * 1e-3) / 1e9
+        line = {
+            "metric": "causal_rfa_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": B * world, "heads": H, "seq_len": T,
+                       "l2": "inputs+outputs 570 MB per step, larger than the 126 MB L2; no flush",
+                       "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"},
+            "clocks": clk.summary,
+            "e2e": {"value": world * TOKENS_PER_STEP / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "api": "rfa_b200.rfa.RFA.apply + .backward, pinned host buffers"},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                         "frac": achieved / hbm, "peak_source": peak_src, "traffic": None,
+                         "algorithmic_bytes_per_launch": units * kbytes[dom], "ms_per_launch": per[dom],
+                         "per_kernel_ms": per,
+                         "path": {"bytes_per_step": units * BYTES_PATH,
+                                  "achieved": units * BYTES_PATH / (ms_per_step * 1e-3) / 1e9,
+                                  "frac": units * BYTES_PATH / (ms_per_step * 1e-3) / 1e9 / hbm}},
+        }
+        if world == 1:
+            tps, cores, desc, dt = cpu_port_sample()
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc,
+                                    "seconds": dt}
+            if not args.no_extras:
+                line["extra"] = extras(device, stream, hbm)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

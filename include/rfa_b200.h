@@ -1,0 +1,168 @@
+/*
+ * rfa_b200 -- C ABI of the B200 (sm_100a) Random Feature Attention kernels.
+ *
+ * Plain pointers and sizes only; no framework types.  Every pointer is a DEVICE
+ * pointer unless stated otherwise, every array is contiguous in the layout
+ * given, and the caller owns all memory: the library never allocates or frees
+ * (the one query function below tells the caller how much scratch to bring).
+ * All launches are asynchronous on the stream handed in (a cudaStream_t passed
+ * as void*; NULL = the legacy default stream) on the CURRENT device.
+ *
+ * Return value of every int function: 0 on success; a negative RFA_E* code for
+ * a rejected argument (nothing was launched); a positive value is the
+ * cudaError_t of a failed launch.  rfa_last_error() gives the text for the
+ * calling thread's most recent failure.
+ *
+ * Upstream = Noahs-ARK/RFA, package random_feature_attention; "replaces" names
+ * the upstream interface (file:line) each entry point stands in for.
+ *
+ * Shapes: T tokens (time-major), BH = batch*heads, K = 2*D = width of phi,
+ * d = head_dim.  The attention kernels support K == 128 and d == 64 (the only
+ * geometry upstream's benchmarks and checks use); anything else is rejected
+ * with RFA_EUNSUPPORTED.  fp16 arrays are IEEE binary16 ("half").
+ */
+#ifndef RFA_B200_H_
+#define RFA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RFA_B200_VERSION 100
+
+enum {
+  RFA_OK = 0,
+  RFA_EINVAL = -1,       /* null pointer, negative size, bad enum              */
+  RFA_EALIGN = -2,       /* pointer not 16-byte aligned                        */
+  RFA_EUNSUPPORTED = -3, /* geometry or dtype this build has no kernel for     */
+  RFA_EWORKSPACE = -4,   /* workspace missing or too small                     */
+  RFA_EDEVICE = -5       /* not an sm_100 device / driver entry point missing  */
+};
+
+/* element types accepted where a signature has a *_dtype argument */
+enum { RFA_F16 = 0, RFA_F32 = 1 };
+
+typedef void* rfa_stream_t;
+
+int rfa_version(void);
+const char* rfa_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Feature map  phi(x) = scale * [sin(W xhat) | cos(W xhat)], xhat = x/(|x|+1e-3)
+ * replaces utils.py:100-120 (_normalize + random_project); W is the effective
+ * matrix sigma*W/tau of utils.py:90-97, fp32 [H, D, d].
+ * x [rows, H, d] (rows = T*B), phi [rows, H, 2D].  d <= 128, d % 8 == 0,
+ * D % 8 == 0, D <= 128.
+ * ---------------------------------------------------------------------- */
+int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w,
+                        void* phi, int phi_dtype,
+                        int64_t rows, int H, int d, int D, float scale,
+                        rfa_stream_t stream);
+
+/* Gradient of the above: g_x [rows,H,d] and g_w [H,D,d] fp32.  g_w is
+ * ACCUMULATED into (atomic adds): the caller zeroes it.  g_w may be NULL. */
+int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w,
+                        const void* g_phi, int g_dtype,
+                        void* g_x, int gx_dtype, float* g_w,
+                        int64_t rows, int H, int d, int D, float scale,
+                        rfa_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Causal RFA.  q,k [T,BH,K] fp16, v/out/g [T,BH,d] fp16, time-major.
+ *   out_t = q_t^T S_t / max(q_t . z_t, 1),  S_t = S_in + sum_{s<=t} k_s v_s^T,
+ *   z_t = z_in + sum_{s<=t} k_s.
+ * replaces rfa_cuda.forward  (cuda/rfa_cuda.cpp:22-27 -> cuda/forward.cu:128-169)
+ *      and rfa_cuda.backward (cuda/rfa_cuda.cpp:29-36 -> cuda/backward.cu:530-585),
+ * reached from RFA.forward/backward (rfa.py:113-145).
+ *
+ * s_in/z_in ([BH,K,d] / [BH,K] fp32, may both be NULL = zeros) is the state of
+ * tokens before this call's first token; s_out/z_out (may be NULL) receives
+ * the state after its last token (prefill -> decode hand-off; segment carry).
+ * workspace: rfa_causal_workspace_bytes(T,BH,K,d) bytes, 256-byte aligned.
+ * ---------------------------------------------------------------------- */
+size_t rfa_causal_workspace_bytes(int64_t T, int BH, int K, int d);
+
+int rfa_causal_fwd(const void* q, const void* k, const void* v, void* out,
+                   const float* s_in, const float* z_in,
+                   float* s_out, float* z_out,
+                   void* workspace, size_t workspace_bytes,
+                   int64_t T, int BH, int K, int d, rfa_stream_t stream);
+
+/* Full backward.  ds_in/dz_in (NULL = zeros) is the reverse carry: the sum over
+ * tokens AFTER this call's last token of q (x) grad_qs and of q*grad_qz. */
+int rfa_causal_bwd(const void* q, const void* k, const void* v, const void* g,
+                   void* gq, void* gk, void* gv,
+                   const float* s_in, const float* z_in,
+                   const float* ds_in, const float* dz_in,
+                   void* workspace, size_t workspace_bytes,
+                   int64_t T, int BH, int K, int d, rfa_stream_t stream);
+
+/* The two halves of the backward, for a sequence sharded across devices:
+ * _bwd_q runs the forward-direction sweep (gq; leaves per-token scalars in the
+ * workspace) and writes this shard's own reverse-state total to ds_seg/dz_seg;
+ * after the shards have exchanged those, _bwd_kv runs the reverse sweep with
+ * the carry ds_in/dz_in.  The same workspace must be passed to both. */
+int rfa_causal_bwd_q(const void* q, const void* k, const void* v, const void* g,
+                     void* gq, const float* s_in, const float* z_in,
+                     float* ds_seg, float* dz_seg,
+                     void* workspace, size_t workspace_bytes,
+                     int64_t T, int BH, int K, int d, rfa_stream_t stream);
+int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, const void* g,
+                      void* gk, void* gv, const float* ds_in, const float* dz_in,
+                      void* workspace, size_t workspace_bytes,
+                      int64_t T, int BH, int K, int d, rfa_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * State reduction  s = sum_t k_t v_t^T [BH,K,d], z = sum_t k_t [BH,K]  (fp32)
+ * over unpadded positions; k [T,BH,K], v [T,BH,d] fp16; pad_mask [B,T] bytes
+ * (non-zero = padding, may be NULL), BH = B*H with bh = b*H + h.
+ * replaces cross_attention.py:97-104 (masked_fill + einsum + sum); also the
+ * per-shard total of the sequence-sharded causal path.
+ * ---------------------------------------------------------------------- */
+int rfa_cross_state_fwd(const void* phi_k, const void* v, const uint8_t* pad_mask,
+                        float* s, float* z,
+                        int64_t T, int B, int H, int K, int d, rfa_stream_t stream);
+
+/* Gradient of the reduction: g_phi_k [T,BH,K] (zero at padded rows),
+ * g_v [T,BH,d] from d_s [BH,K,d], d_z [BH,K] fp32. */
+int rfa_cross_state_bwd(const void* phi_k, const void* v, const uint8_t* pad_mask,
+                        const float* d_s, const float* d_z,
+                        void* g_phi_k, void* g_v,
+                        int64_t T, int B, int H, int K, int d, rfa_stream_t stream);
+
+/* out_t = phi_q_t . s / max(|phi_q_t . z|, 1);  phi_q [T,BH,K], out [T,BH,d] fp16.
+ * replaces CrossAttention.rfa, cross_attention.py:266-269. */
+int rfa_cross_query_fwd(const void* phi_q, const float* s, const float* z, void* out,
+                        int64_t T, int BH, int K, int d, rfa_stream_t stream);
+
+/* Gradient of the above for upstream g [T,BH,d]: g_phi_q [T,BH,K] fp16 and the
+ * state gradients d_s [BH,K,d], d_z [BH,K] fp32 (overwritten, not accumulated). */
+int rfa_cross_query_bwd(const void* phi_q, const float* s, const float* z, const void* g,
+                        void* g_phi_q, float* d_s, float* d_z,
+                        int64_t T, int BH, int K, int d, rfa_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * One incremental-decoding step, in place on the state:
+ *   s += phi_k (x) v;  z += phi_k;  out = phi_q . s / max(phi_q . z, 1)
+ * phi_q, phi_k [BH,K], v/out [BH,d] of in_dtype; s [BH,K,d], z [BH,K] of
+ * state_dtype.  replaces the loop body of incremental_rfa,
+ * causal_attention.py:42-50 (which allocates a new state every token).
+ * ---------------------------------------------------------------------- */
+int rfa_decode_step(const void* phi_q, const void* phi_k, const void* v, int in_dtype,
+                    void* s, void* z, int state_dtype, void* out,
+                    int BH, int K, int d, rfa_stream_t stream);
+
+/* The same step from raw q,k [BH,d]: applies the feature map (W fp32 [H,D,d],
+ * bh % H selects the head) inside the kernel.  K = 2*D. */
+int rfa_decode_step_fused(const void* q, const void* k, const void* v, int in_dtype,
+                          const float* w, float scale,
+                          void* s, void* z, int state_dtype, void* out,
+                          int BH, int H, int D, int d, rfa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RFA_B200_H_ */

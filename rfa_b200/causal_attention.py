@@ -1,0 +1,157 @@
+"""Causal RFA: functional forms and the ``CausalAttention`` layer, with upstream's
+names, arguments and tensor layouts (``causal_attention.py``).  The three hot
+functions run on the sm_100a kernels:
+
+* ``cuda_causal_rfa``  -> chunked prefix-scan kernels through ``RFA.apply``
+* ``incremental_rfa``  -> the state-streaming decode kernel (one token) or the
+                          causal kernel with a state carry (several tokens)
+* the feature map      -> ``utils.random_project``
+"""
+import math
+from typing import Dict, Optional
+
+import torch
+from torch import Tensor, nn
+from torch.nn import Parameter
+
+from . import ops
+from .rfa import RFA
+from .utils import (EPS, build_random_matrices, normalize_attn_weights, random_project,
+                    upgrade_state_dict_named)
+
+
+def incremental_rfa(*, phi_q: Tensor, phi_k: Tensor, v: Tensor,
+                    s: Optional[Tensor] = None, z: Optional[Tensor] = None):
+    """Advance the running state by ``tgt_len`` tokens and attend.
+
+    phi_q, phi_k ``[tgt_len, bsz, num_heads, 2*proj_dim]``, v ``[tgt_len, bsz, num_heads,
+    head_dim]``; state s ``[bsz, num_heads, 2*proj_dim, head_dim]``, z ``[bsz, num_heads,
+    2*proj_dim]``.  Returns ``(attn [tgt_len, bsz, num_heads*head_dim], s, z)``.
+
+    Differences from upstream (causal_attention.py:17-54), both for accuracy/speed:
+    a fresh state is created in fp32 (upstream: v's dtype), and a state that is
+    passed in is UPDATED IN PLACE and returned (upstream allocates a new one per
+    token).  No autograd through this path (it is the inference loop)."""
+    tgt_len, bsz, num_heads, feat = phi_q.shape
+    head_dim = v.size(-1)
+    if s is None:
+        assert z is None
+        s = torch.zeros(bsz, num_heads, feat, head_dim, device=v.device, dtype=torch.float32)
+        z = torch.zeros(bsz, num_heads, feat, device=v.device, dtype=torch.float32)
+    with torch.no_grad():
+        if tgt_len == 1:
+            attn = ops.decode_step(phi_q[0], phi_k[0], v[0], s, z).unsqueeze(0)
+        else:   # several tokens at once: the causal kernel with (s, z) carried in and out
+            BH = bsz * num_heads
+            h = lambda t: t.contiguous().view(tgt_len, BH, -1).half()
+            attn, s_new, z_new = ops.causal_fwd(h(phi_q), h(phi_k), h(v), s.view(BH, feat, head_dim).float(),
+                                                z.view(BH, feat).float(), return_state=True)
+            s.copy_(s_new.view_as(s))
+            z.copy_(z_new.view_as(z))
+            attn = attn.to(v.dtype)
+    return attn.reshape(tgt_len, bsz, num_heads * head_dim), s, z
+
+
+def masked_rfa(*, phi_q: Tensor, phi_k: Tensor, v: Tensor,
+               key_padding_mask: Optional[Tensor] = None, attn_mask: Optional[Tensor] = None) -> Tensor:
+    """Quadratic, explicitly masked variant selected by ``cuda_causal_rfa=False``
+    (upstream causal_attention.py:57-109).  It is a different function from the
+    kernel path -- weights are normalised by ``|row sum|`` clamped at 1e-3, not by
+    ``max(row sum, 1)`` -- and stays in PyTorch exactly as upstream has it."""
+    tgt_len, bsz, num_heads, _ = phi_q.shape
+    head_dim = v.size(-1)
+    if key_padding_mask is not None and key_padding_mask.dim() == 0:
+        key_padding_mask = None
+    scores = torch.einsum("tbhk,sbhk->bhts", phi_q, phi_k)
+    if key_padding_mask is not None:
+        assert key_padding_mask.shape == (bsz, tgt_len)
+        scores = scores.masked_fill(key_padding_mask.to(torch.bool)[:, None, None, :], 0.0)
+    if attn_mask is not None:
+        scores = scores.masked_fill((attn_mask < 0.0)[None, None], 0.0)
+    weights = normalize_attn_weights(scores, dtype=scores.dtype)
+    attn = torch.einsum("bhts,sbhd->tbhd", weights, v)
+    return attn.contiguous().view(tgt_len, bsz, num_heads * head_dim)
+
+
+def cuda_causal_rfa(*, phi_q: Tensor, phi_k: Tensor, v: Tensor,
+                    key_padding_mask: Optional[Tensor] = None) -> Tensor:
+    """Kernel-backed causal RFA (upstream causal_attention.py:112-151).
+
+    phi_q, phi_k ``[tgt_len, bsz, num_heads, 2*proj_dim]``, v ``[tgt_len, bsz, num_heads,
+    head_dim]``; key_padding_mask ``[bsz, tgt_len]`` with 1 = padding: those keys'
+    features are zeroed, so they add nothing to the running state.  Returns
+    ``[tgt_len, bsz, num_heads*head_dim]``.  The kernels are fp16; other float
+    dtypes are converted on the way in and the result converted back."""
+    tgt_len, bsz, num_heads, _ = phi_q.shape
+    head_dim = v.size(-1)
+    if key_padding_mask is not None and key_padding_mask.dim() == 0:
+        key_padding_mask = None
+    if key_padding_mask is not None:
+        assert key_padding_mask.shape == (bsz, tgt_len)
+        pad = key_padding_mask.to(torch.bool).t()[:, :, None, None]
+        phi_k = phi_k.masked_fill(pad, 0.0)
+    dtype = v.dtype
+    flat = lambda t: t.contiguous().view(tgt_len, bsz * num_heads, -1).to(torch.float16)
+    attn = RFA.apply(flat(phi_q), flat(phi_k), flat(v))
+    return attn.view(tgt_len, bsz, num_heads * head_dim).to(dtype)
+
+
+class CausalAttention(nn.Module):
+    """Random feature causal self-attention layer (upstream causal_attention.py:154-280):
+    q/k/v projections, per-head feature map with W' = sigma * W / tau, causal RFA,
+    output projection.  Parameter names match upstream so its checkpoints load."""
+
+    def __init__(self, *, embed_dim: int, num_heads: int, head_dim: int, proj_dim: int,
+                 tau: float = 1.0, reparam_proj: bool = True, cuda_causal_rfa: bool = True):
+        super().__init__()
+        assert head_dim * num_heads == embed_dim, "embed_dim must be divisible by num_heads"
+        self.embed_dim, self.num_heads, self.head_dim = embed_dim, num_heads, head_dim
+        self.proj_dim, self.tau = proj_dim, tau
+        self.reparam_proj, self.cuda_causal_rfa = reparam_proj, cuda_causal_rfa
+        self.q_proj = nn.Linear(embed_dim, embed_dim, bias=True)
+        self.k_proj = nn.Linear(embed_dim, embed_dim, bias=True)
+        self.v_proj = nn.Linear(embed_dim, embed_dim, bias=True)
+        self.out_proj = nn.Linear(embed_dim, embed_dim, bias=True)
+        if reparam_proj:
+            self.sigma = Parameter(Tensor(num_heads, 1, head_dim))
+        self.reset_parameters()
+        self.upgrade_state_dict_named = upgrade_state_dict_named
+
+    def reset_parameters(self):
+        for lin in (self.q_proj, self.k_proj, self.v_proj, self.out_proj):
+            nn.init.xavier_uniform_(lin.weight, gain=1 / math.sqrt(2))
+        if self.reparam_proj:
+            nn.init.constant_(self.sigma, 1.)
+        if self.out_proj.bias is not None:
+            nn.init.constant_(self.out_proj.bias, 0.0)
+
+    def _heads(self, t: Tensor) -> Tensor:
+        return t.contiguous().view(t.size(0), t.size(1), self.num_heads, self.head_dim)
+
+    def forward(self, x: Tensor, random_matrices: Tensor, key_padding_mask: Optional[Tensor] = None,
+                attn_mask: Optional[Tensor] = None,
+                saved_state: Optional[Dict[str, Optional[Tensor]]] = None) -> Tensor:
+        """x ``[tgt_len, bsz, embed_dim]``, random_matrices ``[num_heads, proj_dim, head_dim]``
+        -> ``[tgt_len, bsz, embed_dim]``.  With ``saved_state`` (a dict; keys ``prev_s``,
+        ``prev_z`` are created on first use) the call is one incremental-decoding step
+        and tgt_len must be 1; masks are ignored there, as upstream does."""
+        tgt_len, bsz, embed_dim = x.size()
+        assert embed_dim == self.embed_dim
+        q, k, v = self._heads(self.q_proj(x)), self._heads(self.k_proj(x)), self._heads(self.v_proj(x))
+        w = build_random_matrices(random_matrices=random_matrices, tau=self.tau,
+                                  sigma=self.sigma if self.reparam_proj else None,
+                                  reparam_proj=self.reparam_proj)
+        phi_q = random_project(x=q, random_matrices=w)
+        phi_k = random_project(x=k, random_matrices=w)
+        if saved_state is not None:
+            assert tgt_len == 1
+            prev_s, prev_z = saved_state.get("prev_s"), saved_state.get("prev_z")
+            assert (prev_s is None) == (prev_z is None)
+            attn, s, z = incremental_rfa(phi_q=phi_q, phi_k=phi_k, v=v, s=prev_s, z=prev_z)
+            saved_state["prev_s"], saved_state["prev_z"] = s, z
+        elif self.cuda_causal_rfa:
+            attn = cuda_causal_rfa(phi_q=phi_q, phi_k=phi_k, v=v, key_padding_mask=key_padding_mask)
+        else:
+            attn = masked_rfa(phi_q=phi_q, phi_k=phi_k, v=v, attn_mask=attn_mask,
+                              key_padding_mask=key_padding_mask)
+        return self.out_proj(attn.to(x.dtype))

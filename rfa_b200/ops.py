@@ -1,0 +1,217 @@
+"""Tensor-level wrappers over the C ABI: allocate outputs, pass raw pointers and
+the current stream, turn status codes into exceptions.  No arithmetic happens
+here; every function launches kernels from ``librfa_b200.so``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import check, dtype_code, ptr, require_half, stream_of
+
+K_BUILT, D_BUILT = 128, 64      # geometry the attention kernels are built for
+
+
+def _guard(t: Tensor):
+    if not t.is_cuda:
+        raise RuntimeError(f"rfa_b200 kernels take CUDA tensors only (there is no CPU path); got a {t.device} tensor")
+    return torch.cuda.device(t.device)
+
+
+def _workspace(T: int, BH: int, K: int, d: int, like: Tensor) -> Tuple[Tensor, int]:
+    n = _lib.load().rfa_causal_workspace_bytes(T, BH, K, d)
+    ws = torch.empty(max(n, 256), dtype=torch.uint8, device=like.device)
+    return ws, n
+
+
+# --------------------------------------------------------------------------- feature map
+def feature_map_fwd(x: Tensor, w: Tensor, scale: float, out_dtype: Optional[torch.dtype] = None) -> Tensor:
+    """x [..., H, d], w [H, D, d] fp32 -> phi [..., H, 2D]."""
+    H, D, d = w.shape
+    assert x.shape[-2] == H and x.shape[-1] == d, (x.shape, w.shape)
+    x = x.contiguous()
+    w = w.contiguous().float()
+    phi = torch.empty(*x.shape[:-1], 2 * D, dtype=out_dtype or x.dtype, device=x.device)
+    rows = x.numel() // (H * d)
+    with _guard(x):
+        check(_lib.load().rfa_feature_map_fwd(ptr(x), dtype_code(x), ptr(w), ptr(phi), dtype_code(phi),
+                                              rows, H, d, D, float(scale), stream_of(x)), "rfa_feature_map_fwd")
+    return phi
+
+
+def feature_map_bwd(x: Tensor, w: Tensor, g_phi: Tensor, scale: float, need_gw: bool) -> Tuple[Tensor, Optional[Tensor]]:
+    H, D, d = w.shape
+    x = x.contiguous()
+    w = w.contiguous().float()
+    g_phi = g_phi.contiguous().to(x.dtype)
+    g_x = torch.empty_like(x)
+    g_w = torch.zeros(H, D, d, dtype=torch.float32, device=x.device) if need_gw else None
+    rows = x.numel() // (H * d)
+    with _guard(x):
+        check(_lib.load().rfa_feature_map_bwd(ptr(x), dtype_code(x), ptr(w), ptr(g_phi), dtype_code(g_phi),
+                                              ptr(g_x), dtype_code(g_x), ptr(g_w), rows, H, d, D, float(scale),
+                                              stream_of(x)), "rfa_feature_map_bwd")
+    return g_x, g_w
+
+
+# --------------------------------------------------------------------------- causal
+def causal_fwd(q: Tensor, k: Tensor, v: Tensor, s_in: Optional[Tensor] = None, z_in: Optional[Tensor] = None,
+               return_state: bool = False):
+    """q,k [T,BH,K], v [T,BH,d] fp16 -> out [T,BH,d] (and the final state when asked)."""
+    require_half(q, k, v)
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    assert k.shape == q.shape and v.shape[:2] == q.shape[:2]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty(T, BH, d, dtype=torch.float16, device=q.device)
+    s_out = torch.empty(BH, K, d, dtype=torch.float32, device=q.device) if return_state else None
+    z_out = torch.empty(BH, K, dtype=torch.float32, device=q.device) if return_state else None
+    if s_in is not None:
+        s_in, z_in = s_in.contiguous().float(), z_in.contiguous().float()
+    ws, n = _workspace(T, BH, K, d, q)
+    with _guard(q):
+        check(_lib.load().rfa_causal_fwd(ptr(q), ptr(k), ptr(v), ptr(out), ptr(s_in), ptr(z_in), ptr(s_out),
+                                         ptr(z_out), ptr(ws), n, T, BH, K, d, stream_of(q)), "rfa_causal_fwd")
+    return (out, s_out, z_out) if return_state else out
+
+
+def causal_bwd(q: Tensor, k: Tensor, v: Tensor, g: Tensor, s_in: Optional[Tensor] = None,
+               z_in: Optional[Tensor] = None, ds_in: Optional[Tensor] = None, dz_in: Optional[Tensor] = None):
+    require_half(q, k, v, g)
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws, n = _workspace(T, BH, K, d, q)
+    with _guard(q):
+        check(_lib.load().rfa_causal_bwd(ptr(q), ptr(k), ptr(v), ptr(g), ptr(gq), ptr(gk), ptr(gv), ptr(s_in),
+                                         ptr(z_in), ptr(ds_in), ptr(dz_in), ptr(ws), n, T, BH, K, d, stream_of(q)),
+              "rfa_causal_bwd")
+    return gq, gk, gv
+
+
+def causal_bwd_q(q, k, v, g, s_in, z_in, want_dseg: bool):
+    """Forward-direction half of the backward.  Returns (gq, ds_seg, dz_seg, workspace)."""
+    require_half(q, k, v, g)
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    gq = torch.empty_like(q)
+    ds = torch.empty(BH, K, d, dtype=torch.float32, device=q.device) if want_dseg else None
+    dz = torch.empty(BH, K, dtype=torch.float32, device=q.device) if want_dseg else None
+    ws, n = _workspace(T, BH, K, d, q)
+    with _guard(q):
+        check(_lib.load().rfa_causal_bwd_q(ptr(q), ptr(k), ptr(v), ptr(g), ptr(gq), ptr(s_in), ptr(z_in), ptr(ds),
+                                           ptr(dz), ptr(ws), n, T, BH, K, d, stream_of(q)), "rfa_causal_bwd_q")
+    return gq, ds, dz, ws
+
+
+def causal_bwd_kv(q, k, v, g, ds_in, dz_in, ws: Tensor):
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    gk, gv = torch.empty_like(k), torch.empty_like(v)
+    with _guard(q):
+        check(_lib.load().rfa_causal_bwd_kv(ptr(q), ptr(k), ptr(v), ptr(g), ptr(gk), ptr(gv), ptr(ds_in), ptr(dz_in),
+                                            ptr(ws), ws.numel(), T, BH, K, d, stream_of(q)), "rfa_causal_bwd_kv")
+    return gk, gv
+
+
+# --------------------------------------------------------------------------- cross
+def _mask_bytes(pad_mask: Optional[Tensor], B: int, T: int, dev) -> Optional[Tensor]:
+    if pad_mask is None:
+        return None
+    m = pad_mask.to(device=dev).reshape(B, T)
+    return (m != 0).to(torch.uint8).contiguous()
+
+
+def cross_state_fwd(phi_k: Tensor, v: Tensor, pad_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    """phi_k [T,B,H,K], v [T,B,H,d] fp16, pad_mask [B,T] (non-zero = pad) -> s [B,H,K,d], z [B,H,K] fp32."""
+    require_half(phi_k, v)
+    T, B, H, K = phi_k.shape
+    d = v.shape[-1]
+    phi_k, v = phi_k.contiguous(), v.contiguous()
+    m = _mask_bytes(pad_mask, B, T, phi_k.device)
+    s = torch.empty(B, H, K, d, dtype=torch.float32, device=phi_k.device)
+    z = torch.empty(B, H, K, dtype=torch.float32, device=phi_k.device)
+    with _guard(phi_k):
+        check(_lib.load().rfa_cross_state_fwd(ptr(phi_k), ptr(v), ptr(m), ptr(s), ptr(z), T, B, H, K, d,
+                                              stream_of(phi_k)), "rfa_cross_state_fwd")
+    return s, z
+
+
+def cross_state_bwd(phi_k: Tensor, v: Tensor, pad_mask: Optional[Tensor], d_s: Tensor, d_z: Tensor):
+    T, B, H, K = phi_k.shape
+    d = v.shape[-1]
+    phi_k, v = phi_k.contiguous(), v.contiguous()
+    m = _mask_bytes(pad_mask, B, T, phi_k.device)
+    d_s, d_z = d_s.contiguous().float(), d_z.contiguous().float()
+    g_k, g_v = torch.empty_like(phi_k), torch.empty_like(v)
+    with _guard(phi_k):
+        check(_lib.load().rfa_cross_state_bwd(ptr(phi_k), ptr(v), ptr(m), ptr(d_s), ptr(d_z), ptr(g_k), ptr(g_v),
+                                              T, B, H, K, d, stream_of(phi_k)), "rfa_cross_state_bwd")
+    return g_k, g_v
+
+
+def cross_query_fwd(phi_q: Tensor, s: Tensor, z: Tensor) -> Tensor:
+    """phi_q [T,B,H,K] fp16, s [B,H,K,d], z [B,H,K] fp32 -> out [T,B,H,d] fp16."""
+    require_half(phi_q)
+    T, B, H, K = phi_q.shape
+    d = s.shape[-1]
+    phi_q = phi_q.contiguous()
+    s, z = s.contiguous().float(), z.contiguous().float()
+    out = torch.empty(T, B, H, d, dtype=torch.float16, device=phi_q.device)
+    with _guard(phi_q):
+        check(_lib.load().rfa_cross_query_fwd(ptr(phi_q), ptr(s), ptr(z), ptr(out), T, B * H, K, d,
+                                              stream_of(phi_q)), "rfa_cross_query_fwd")
+    return out
+
+
+def cross_query_bwd(phi_q: Tensor, s: Tensor, z: Tensor, g: Tensor):
+    require_half(phi_q, g)
+    T, B, H, K = phi_q.shape
+    d = s.shape[-1]
+    phi_q, g = phi_q.contiguous(), g.contiguous()
+    s, z = s.contiguous().float(), z.contiguous().float()
+    g_q = torch.empty_like(phi_q)
+    d_s, d_z = torch.empty_like(s), torch.empty_like(z)
+    with _guard(phi_q):
+        check(_lib.load().rfa_cross_query_bwd(ptr(phi_q), ptr(s), ptr(z), ptr(g), ptr(g_q), ptr(d_s), ptr(d_z),
+                                              T, B * H, K, d, stream_of(phi_q)), "rfa_cross_query_bwd")
+    return g_q, d_s, d_z
+
+
+# --------------------------------------------------------------------------- decode
+def decode_step(phi_q: Tensor, phi_k: Tensor, v: Tensor, s: Tensor, z: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """One token, state updated IN PLACE.  phi_q,phi_k [B,H,K], v [B,H,d]; s [B,H,K,d], z [B,H,K]."""
+    B, H, K = phi_q.shape
+    d = v.shape[-1]
+    phi_q, phi_k, v = phi_q.contiguous(), phi_k.contiguous(), v.contiguous()
+    if not (s.is_contiguous() and z.is_contiguous()):
+        raise ValueError("decode_step: state tensors must be contiguous (they are updated in place)")
+    if out is None:
+        out = torch.empty(B, H, d, dtype=v.dtype, device=v.device)
+    with _guard(v):
+        check(_lib.load().rfa_decode_step(ptr(phi_q), ptr(phi_k), ptr(v), dtype_code(v), ptr(s), ptr(z), dtype_code(s),
+                                          ptr(out), B * H, K, d, stream_of(v)), "rfa_decode_step")
+    return out
+
+
+def decode_step_fused(q: Tensor, k: Tensor, v: Tensor, w: Tensor, scale: float, s: Tensor, z: Tensor,
+                      out: Optional[Tensor] = None) -> Tensor:
+    """One token from raw q,k [B,H,d]; w [H,D,d] fp32 contiguous; state updated IN PLACE."""
+    B, H, d = q.shape
+    D = w.shape[1]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if w.dtype != torch.float32 or not w.is_contiguous():
+        raise ValueError("decode_step_fused: w must be a contiguous fp32 [H,D,d] tensor")
+    if out is None:
+        out = torch.empty(B, H, d, dtype=v.dtype, device=v.device)
+    with _guard(v):
+        check(_lib.load().rfa_decode_step_fused(ptr(q), ptr(k), ptr(v), dtype_code(v), ptr(w), float(scale), ptr(s),
+                                                ptr(z), dtype_code(s), ptr(out), B * H, H, D, d, stream_of(v)),
+              "rfa_decode_step_fused")
+    return out

@@ -1,0 +1,280 @@
+"""Parity of the sm_100a kernels (called through the C ABI) with the CPU oracle and
+with the fixtures produced by the upstream Python sources.
+
+Gate for fp16 kernels against the fp32 oracle on identical fp16-valued inputs:
+relative L2 error <= 2e-3 and max abs error <= 1e-2, outputs and all gradients
+(REL_L2_TOL / MAX_ABS_TOL in conftest.py).  fp32-state quantities (S, z) are held
+to 1e-4 relative."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden
+from oracle import rfa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def h16(t):
+    return t.half().float()
+
+
+def feats(T, BH, seed, scale=1.0):
+    """phi-like inputs: fp16-valued q,k [T,BH,128], v,g [T,BH,64]."""
+    gen = torch.Generator().manual_seed(seed)
+    w = torch.from_numpy(O.draw_matrices("orf", 1, 64, 64, seed + 100)).float()
+    xq, xk = torch.randn(T, BH, 1, 64, generator=gen), torch.randn(T, BH, 1, 64, generator=gen)
+    q = h16(O.random_project(xq, w)).view(T, BH, 128) * scale
+    k = h16(O.random_project(xk, w)).view(T, BH, 128) * scale
+    v = h16(torch.randn(T, BH, 64, generator=gen))
+    g = h16(torch.randn(T, BH, 64, generator=gen))
+    return h16(q), h16(k), v, g
+
+
+# ----------------------------------------------------------------------------- causal
+def run_causal(dev, q, k, v, g, **kw):
+    from rfa_b200 import ops
+    cu = lambda t: None if t is None else t.to(dev)
+    qh, kh, vh, gh = (t.half().to(dev) for t in (q, k, v, g))
+    out = ops.causal_fwd(qh, kh, vh, cu(kw.get("s0")), cu(kw.get("z0")))
+    gq, gk, gv = ops.causal_bwd(qh, kh, vh, gh, cu(kw.get("s0")), cu(kw.get("z0")), cu(kw.get("ds")), cu(kw.get("dz")))
+    torch.cuda.synchronize()
+    return out, gq, gk, gv
+
+
+@pytest.mark.parametrize("name", ["causal_fwd_gradcheck", "causal_bwd_gradcheck", "causal_features"])
+def test_causal_against_upstream_fixtures(dev, name):
+    g = golden(name)
+    up = g["g"] if "g" in g else torch.ones_like(g["v"])
+    out, gq, gk, gv = run_causal(dev, g["q"], g["k"], g["v"], up)
+    assert_close(out, g["attn"], f"{name}.attn")
+    if "gq" in g:
+        assert_close(gq, g["gq"], f"{name}.gq")
+        assert_close(gk, g["gk"], f"{name}.gk")
+        assert_close(gv, g["gv"], f"{name}.gv")
+        # upstream's own criterion (grad_check.py:13-14): squared difference < 1e-4 everywhere
+        for a, b in ((gq, g["gq"]), (gk, g["gk"]), (gv, g["gv"]), (out, g["attn"])):
+            assert ((a.float().cpu() - b) ** 2 < 1e-4).all()
+
+
+@pytest.mark.parametrize("T,BH", [(1, 1), (2, 3), (63, 2), (64, 2), (65, 2), (131, 3), (513, 2), (1100, 2), (2048, 5)])
+def test_causal_vs_oracle_shapes(dev, T, BH):
+    """Ragged lengths around the chunk size, one-token sequences, and (T >= 1024, few
+    heads) the segmented path with its pre-pass + scan."""
+    q, k, v, g = feats(T, BH, seed=T * 7 + BH)
+    out, gq, gk, gv = run_causal(dev, q, k, v, g)
+    ro = O.causal_forward(q, k, v)
+    rq, rk, rv = O.causal_backward(q, k, v, g)
+    assert_close(out, ro, "out"); assert_close(gq, rq, "gq"); assert_close(gk, rk, "gk"); assert_close(gv, rv, "gv")
+
+
+def test_causal_unclamped_large_denominators(dev):
+    """Positive features so that q.z >> 1 everywhere except the first tokens."""
+    gen = torch.Generator().manual_seed(4)
+    T, BH = 300, 2
+    q = h16(torch.rand(T, BH, 128, generator=gen) * 0.2)
+    k = h16(torch.rand(T, BH, 128, generator=gen) * 0.2)
+    v = h16(torch.randn(T, BH, 64, generator=gen)); g = h16(torch.randn(T, BH, 64, generator=gen))
+    out, gq, gk, gv = run_causal(dev, q, k, v, g)
+    ro = O.causal_forward(q, k, v); rq, rk, rv = O.causal_backward(q, k, v, g)
+    assert_close(out, ro, "out"); assert_close(gq, rq, "gq"); assert_close(gk, rk, "gk"); assert_close(gv, rv, "gv")
+
+
+@pytest.mark.parametrize("T,BH,cut", [(200, 2, 70), (1300, 2, 1100)])
+def test_causal_state_carry_in_and_out(dev, T, BH, cut):
+    """Second half of a sequence run with (S,z) carried in and (dS,dz) carried back equals
+    the unsplit run -- the property the sequence-sharded path relies on."""
+    from rfa_b200 import ops
+    q, k, v, g = feats(T, BH, seed=33)
+    ro = O.causal_forward(q, k, v); rq, rk, rv = O.causal_backward(q, k, v, g)
+    c = lambda t: t.half().to(dev)
+    o1, s, z = ops.causal_fwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), return_state=True)
+    o2, s2, z2 = ops.causal_fwd(c(q[cut:]), c(k[cut:]), c(v[cut:]), s, z, return_state=True)
+    assert_close(torch.cat([o1, o2]), ro, "out")
+    rs, rz = O.segment_state(k, v)
+    assert_close(s2, rs, "state S", rel=1e-4, mabs=1e-2); assert_close(z2, rz, "state z", rel=1e-4, mabs=1e-2)
+    # backward: later shard first (no reverse carry), its dS total feeds the earlier shard
+    gq2, ds, dz, ws2 = ops.causal_bwd_q(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), s, z, True)
+    gk2, gv2 = ops.causal_bwd_kv(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), None, None, ws2)
+    gq1, gk1, gv1 = ops.causal_bwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), c(g[:cut]), None, None, ds, dz)
+    assert_close(torch.cat([gq1, gq2]), rq, "gq"); assert_close(torch.cat([gk1, gk2]), rk, "gk")
+    assert_close(torch.cat([gv1, gv2]), rv, "gv")
+
+
+def test_rfa_autograd_function_and_rfa_cuda_shim(dev):
+    import rfa_b200
+    rfa_b200.install_aliases()
+    import rfa_cuda
+    from random_feature_attention.rfa import RFA
+    g = golden("causal_features")
+    q, k, v = (g[n].half().to(dev).requires_grad_(True) for n in ("q", "k", "v"))
+    out = RFA.apply(q, k, v)
+    (out.float() * g["g"].to(dev)).sum().backward()
+    assert_close(out, g["attn"], "attn"); assert_close(q.grad, g["gq"], "gq")
+    assert_close(k.grad, g["gk"], "gk"); assert_close(v.grad, g["gv"], "gv")
+    assert_close(rfa_cuda.forward(q.detach(), k.detach(), v.detach()), g["attn"], "rfa_cuda.forward")
+    assert_close(RFA.forward_torch(q.detach().float(), k.detach().float(), v.detach().float()), g["attn"],
+                 "forward_torch twin", rel=1e-5, mabs=1e-5)
+    with pytest.raises(TypeError):
+        rfa_cuda.forward(q.detach().float(), k.detach().float(), v.detach().float())
+
+
+def test_outputs_fully_written(dev):
+    """Poison the caching allocator's blocks with NaN first: every output element must be
+    written by the kernels (upstream hid this behind torch::zeros)."""
+    q, k, v, g = feats(130, 3, seed=5)
+    junk = [torch.full((130, 3, 128), float("nan"), dtype=torch.half, device=dev) for _ in range(6)]
+    del junk
+    out, gq, gk, gv = run_causal(dev, q, k, v, g)
+    for t in (out, gq, gk, gv):
+        assert torch.isfinite(t).all()
+
+
+# ----------------------------------------------------------------------------- feature map
+def test_feature_map_against_upstream_fixture(dev):
+    from rfa_b200 import utils
+    g = golden("feature_map")
+    x = g["x"].half().to(dev).requires_grad_(True)
+    w = g["w_eff"].to(dev).requires_grad_(True)
+    phi = utils.random_project(x=x, random_matrices=w)
+    assert phi.dtype == torch.half
+    assert_close(phi, g["phi"], "phi", rel=1e-3, mabs=2e-4)
+    (phi.float() * g["g_phi"].to(dev)).sum().backward()
+    assert_close(x.grad, g["g_x"], "g_x"); assert_close(w.grad, g["g_w"], "g_w", rel=2e-3, mabs=5e-2)
+    x32 = g["x"].to(dev)
+    assert_close(utils.random_project(x=x32, random_matrices=g["w"].to(dev)), g["phi_plain"], "phi fp32", rel=1e-5, mabs=1e-6)
+
+
+@pytest.mark.parametrize("rows,H,d,D", [(1, 1, 64, 64), (77, 3, 64, 64), (130, 2, 32, 48), (65, 2, 128, 128), (9, 5, 16, 8)])
+def test_feature_map_shapes_fp32(dev, rows, H, d, D):
+    from rfa_b200 import ops
+    gen = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, H, d, generator=gen) * 2
+    x[0, 0] = 0                                             # zero vector: norm 0
+    w = torch.randn(H, D, d, generator=gen)
+    gp = torch.randn(rows, H, 2 * D, generator=gen)
+    phi = ops.feature_map_fwd(x.to(dev), w.to(dev), 0.1)
+    gx, gw = ops.feature_map_bwd(x.to(dev), w.to(dev), gp.to(dev), 0.1, True)
+    assert_close(phi, O.random_project(x, w), "phi", rel=1e-5, mabs=1e-6)
+    rx, rw = O.random_project_backward(x, w, gp)
+    assert_close(gx, rx, "g_x", rel=1e-4, mabs=1e-4); assert_close(gw, rw, "g_w", rel=1e-4, mabs=1e-3)
+
+
+# ----------------------------------------------------------------------------- decode
+def test_decode_against_upstream_fixture(dev):
+    from rfa_b200.causal_attention import incremental_rfa
+    g = golden("incremental")
+    pq, pk, v = (g[n].half().to(dev) for n in ("phi_q", "phi_k", "v"))
+    a1, s, z = incremental_rfa(phi_q=pq[:6], phi_k=pk[:6], v=v[:6])               # multi-token: causal kernel + carry
+    assert s.dtype == torch.float32
+    assert_close(a1, g["attn_a"], "attn_a"); assert_close(z, g["z_a"], "z_a", rel=1e-4)
+    outs = []
+    for i in range(6, 9):                                                         # one token at a time: decode kernel
+        a, s, z = incremental_rfa(phi_q=pq[i:i + 1], phi_k=pk[i:i + 1], v=v[i:i + 1], s=s, z=z)
+        outs.append(a)
+    assert_close(torch.cat(outs), g["attn_b"], "attn_b")
+    assert_close(s, g["s_b"], "s_b", rel=1e-4); assert_close(z, g["z_b"], "z_b", rel=1e-4)
+
+
+@pytest.mark.parametrize("state_dtype,in_dtype", [(torch.float32, torch.float16), (torch.float16, torch.float16), (torch.float32, torch.float32)])
+def test_decode_steps_vs_oracle(dev, state_dtype, in_dtype):
+    from rfa_b200 import ops
+    gen = torch.Generator().manual_seed(3)
+    B, H, steps = 3, 4, 5
+    w = torch.from_numpy(O.draw_matrices("orf", H, 64, 64, 1)).float()
+    s = torch.zeros(B, H, 128, 64); z = torch.zeros(B, H, 128)
+    sd, zd = s.to(dev, state_dtype), z.to(dev, state_dtype)
+    sf, zf = s.to(dev, state_dtype), z.to(dev, state_dtype)
+    for i in range(steps):
+        q, k, v = (h16(torch.randn(B, H, 64, generator=gen)) for _ in range(3))
+        pq, pk = h16(O.random_project(q, w)), h16(O.random_project(k, w))
+        ref, s, z = O.incremental_rfa(pq[None], pk[None], v[None], s, z)
+        out = ops.decode_step(pq.to(dev, in_dtype), pk.to(dev, in_dtype), v.to(dev, in_dtype), sd, zd)
+        outf = ops.decode_step_fused(q.to(dev, in_dtype), k.to(dev, in_dtype), v.to(dev, in_dtype), w.to(dev), 0.1, sf, zf)
+        assert_close(out.reshape(1, B, -1), ref, f"step {i}")
+        assert_close(outf.reshape(1, B, -1), ref, f"fused step {i}")
+    tol = 1e-4 if state_dtype == torch.float32 else 2e-3
+    assert_close(sd, s, "S", rel=tol); assert_close(zd, z, "z", rel=tol)
+    assert_close(sf, s, "S fused", rel=2e-3); assert_close(zf, z, "z fused", rel=2e-3)
+
+
+# ----------------------------------------------------------------------------- cross
+def run_cross(dev, pq, pk, v, g, pad):
+    from rfa_b200.cross_attention import cross_rfa_query, cross_rfa_state
+    pq_, pk_, v_ = (t.half().to(dev).requires_grad_(True) for t in (pq, pk, v))
+    s, z = cross_rfa_state(pk_, v_, None if pad is None else pad.to(dev))
+    attn = cross_rfa_query(pq_, s, z)
+    (attn.float() * g.to(dev)).sum().backward()
+    return attn, s, z, pq_.grad, pk_.grad, v_.grad
+
+
+@pytest.mark.parametrize("name", ["cross", "cross_signed"])
+def test_cross_against_upstream_fixtures(dev, name):
+    g = golden(name)
+    pad = g.get("pad")
+    attn, s, z, gq, gk, gv = run_cross(dev, g["phi_q"], g["phi_k"], g["v"], g["g"], pad)
+    assert_close(attn, g["attn"], "attn")
+    if "s" in g:
+        assert_close(s, g["s"], "s", rel=1e-4); assert_close(z, g["z"], "z", rel=1e-4)
+    assert_close(gq, g["g_phi_q"], "g_phi_q"); assert_close(gk, g["g_phi_k"], "g_phi_k"); assert_close(gv, g["g_v"], "g_v")
+    if pad is not None:
+        assert (gk.cpu()[pad.T] == 0).all() and (gv.cpu()[pad.T] == 0).all()
+
+
+@pytest.mark.parametrize("Tq,Ts,B,H", [(1, 1, 1, 1), (70, 129, 2, 3), (200, 64, 3, 2)])
+def test_cross_vs_oracle_ragged(dev, Tq, Ts, B, H):
+    gen = torch.Generator().manual_seed(Tq + Ts)
+    q, _, _, _ = feats(Tq, B * H, seed=Tq)
+    _, k, v, _ = feats(Ts, B * H, seed=Ts + 1)
+    pq, pk, v = q.view(Tq, B, H, 128), k.view(Ts, B, H, 128), v.view(Ts, B, H, 64)
+    g = h16(torch.randn(Tq, B, H, 64, generator=gen))
+    lens = torch.randint(1, Ts + 1, (B,), generator=gen)
+    lens[0] = Ts
+    pad = torch.arange(Ts)[None] >= lens[:, None]
+    attn, s, z, gq, gk, gv = run_cross(dev, pq, pk, v, g, pad)
+    rs, rz = O.cross_state(pk, v, pad)
+    assert_close(s, rs, "s", rel=1e-4); assert_close(z, rz, "z", rel=1e-4)
+    assert_close(attn, O.cross_query(pq, rs, rz), "attn")
+    rq, rk, rv = O.cross_backward(pq, pk, v, g, pad)
+    assert_close(gq, rq, "g_phi_q"); assert_close(gk, rk, "g_phi_k"); assert_close(gv, rv, "g_v")
+
+
+# ----------------------------------------------------------------------------- modules
+def test_modules_against_upstream_fixture(dev):
+    from rfa_b200 import CausalAttention, CrossAttention
+    from rfa_b200.cross_attention import CrossAttentionProjectLayer
+    g = golden("modules")
+    sub = lambda pre: {k[len(pre):]: v for k, v in g.items() if k.startswith(pre)}
+    w = g["w"].to(dev)
+    mod = CausalAttention(embed_dim=128, num_heads=2, head_dim=64, proj_dim=64, tau=0.9).to(dev)
+    mod.load_state_dict(sub("causal."))
+    y = mod(g["x"].to(dev), w, key_padding_mask=g["kpm"].to(dev))
+    assert_close(y, g["y"], "CausalAttention", rel=4e-3)
+    st = {}
+    ys = torch.cat([mod(g["x"][i:i + 1].to(dev), w, saved_state=st) for i in range(4)])
+    assert_close(ys, g["y_inc"], "incremental", rel=4e-3)
+    assert_close(st["prev_s"], g["prev_s"], "prev_s", rel=2e-3); assert_close(st["prev_z"], g["prev_z"], "prev_z", rel=2e-3)
+    layer = CrossAttentionProjectLayer(embed_dim=128, num_heads=2, head_dim=64, proj_dim=64, tau=1.1).to(dev)
+    layer.load_state_dict(sub("xlayer."))
+    dec = CrossAttention(embed_dim=128, num_heads=2, head_dim=64, proj_dim=64, tau=1.1).to(dev)
+    dec.load_state_dict(sub("xdec."))
+    state = layer(encoder_output=g["enc"].to(dev), random_matrices=w, mask=g["emask"].to(dev))
+    assert_close(state.s, g["xs"], "cross s", rel=2e-3); assert_close(state.z, g["xz"], "cross z", rel=2e-3)
+    assert_close(dec(g["query"].to(dev), state), g["yq"], "CrossAttention", rel=4e-3)
+    # gradients reach every parameter through the kernels
+    mod.zero_grad()
+    mod(g["x"].to(dev), w).sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in mod.parameters())
+
+
+# ----------------------------------------------------------------------------- argument checking
+def test_bad_arguments_are_rejected_without_launching(dev):
+    from rfa_b200 import ops
+    q = torch.zeros(8, 2, 96, dtype=torch.half, device=dev)
+    v = torch.zeros(8, 2, 64, dtype=torch.half, device=dev)
+    with pytest.raises(ValueError, match="only K=128"):
+        ops.causal_fwd(q, q, v)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.causal_fwd(q.cpu(), q.cpu(), v.cpu())
+    q = torch.zeros(0, 2, 128, dtype=torch.half, device=dev)
+    assert ops.causal_fwd(q, q, torch.zeros(0, 2, 64, dtype=torch.half, device=dev)).shape == (0, 2, 64)
