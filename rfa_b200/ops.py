@@ -67,10 +67,16 @@ def causal_fwd(q: Tensor, k: Tensor, v: Tensor, s_in: Optional[Tensor] = None, z
     assert k.shape == q.shape and v.shape[:2] == q.shape[:2]
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     out = torch.empty(T, BH, d, dtype=torch.float16, device=q.device)
-    s_out = torch.empty(BH, K, d, dtype=torch.float32, device=q.device) if return_state else None
-    z_out = torch.empty(BH, K, dtype=torch.float32, device=q.device) if return_state else None
     if s_in is not None:
         s_in, z_in = s_in.contiguous().float(), z_in.contiguous().float()
+    if T == 0:      # nothing to launch (empty tensors have no address); the state passes through
+        if not return_state:
+            return out
+        if s_in is None:
+            return out, torch.zeros(BH, K, d, device=q.device), torch.zeros(BH, K, device=q.device)
+        return out, s_in.clone(), z_in.clone()
+    s_out = torch.empty(BH, K, d, dtype=torch.float32, device=q.device) if return_state else None
+    z_out = torch.empty(BH, K, dtype=torch.float32, device=q.device) if return_state else None
     ws, n = _workspace(T, BH, K, d, q)
     with _guard(q):
         check(_lib.load().rfa_causal_fwd(ptr(q), ptr(k), ptr(v), ptr(out), ptr(s_in), ptr(z_in), ptr(s_out),
@@ -85,6 +91,8 @@ def causal_bwd(q: Tensor, k: Tensor, v: Tensor, g: Tensor, s_in: Optional[Tensor
     d = v.shape[-1]
     q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
     gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if T == 0:
+        return gq, gk, gv
     ws, n = _workspace(T, BH, K, d, q)
     with _guard(q):
         check(_lib.load().rfa_causal_bwd(ptr(q), ptr(k), ptr(v), ptr(g), ptr(gq), ptr(gk), ptr(gv), ptr(s_in),
