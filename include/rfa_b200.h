@@ -50,6 +50,13 @@ typedef void* rfa_stream_t;
 int rfa_version(void);
 const char* rfa_last_error(void);
 
+/* Device-side health of the tensor-core kernels on the current device.  Every wait
+ * inside them is bounded; a wait that runs out records its site here and the kernel
+ * leaves early (outputs are then invalid).  Returns 0 when no wait ever ran out, else
+ * the site code; synchronises the device and clears the flag.  No upstream
+ * counterpart (upstream never reads launch or device errors, cuda/forward.cu:155). */
+int rfa_debug_status(void);
+
 /* ------------------------------------------------------------------------
  * Feature map  phi(x) = scale * [sin(W xhat) | cos(W xhat)], xhat = x/(|x|+1e-3)
  * replaces utils.py:100-120 (_normalize + random_project); W is the effective

@@ -24,6 +24,7 @@ _i64, _int, _f32, _vp, _sz = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size
 SIGNATURES = {
     "rfa_version": (_int, []),
     "rfa_last_error": (C.c_char_p, []),
+    "rfa_debug_status": (_int, []),
     "rfa_feature_map_fwd": (_int, [_vp, _int, _vp, _vp, _int, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_feature_map_bwd": (_int, [_vp, _int, _vp, _vp, _int, _vp, _int, _vp, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_causal_workspace_bytes": (_sz, [_i64, _int, _int, _int]),

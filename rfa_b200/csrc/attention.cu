@@ -12,6 +12,8 @@
 // grad_k, grad_v.  With few (batch, head) pairs the sequence is additionally cut into
 // segments that run as separate CTAs; their boundary states come from a reduction
 // pre-pass plus an exclusive scan, the same primitive a multi-device split uses.
+#include <stdlib.h>
+
 #include "tiles.cuh"
 
 namespace rfa {
@@ -22,17 +24,24 @@ namespace rfa {
 // ---------------------------------------------------------------------------
 struct CausalPlan {
   int nseg;        // segments per (batch, head)
-  int64_t tseg;    // tokens per segment (multiple of kC)
+  int64_t tseg;    // tokens per segment (multiple of every kernel's chunk length)
 };
 
+constexpr int kSegAlign = 128;
+
+// tensor-core forward (causal_tc.cu)
+int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __half* out, const float* s_seg,
+                         const float* z_seg, float* s_out, float* z_out, int64_t T, int BH, int nseg, int64_t tseg,
+                         cudaStream_t st);
+
 static CausalPlan plan_causal(int64_t T, int BH) {
-  CausalPlan p{1, ((T + kC - 1) / kC) * kC};
+  CausalPlan p{1, ((T + kSegAlign - 1) / kSegAlign) * kSegAlign};
   if (BH >= 120 || T < 1024) return p;
   int64_t want = (148 + BH - 1) / BH;           // CTAs to cover the SMs
   int64_t maxseg = T / 512;                     // keep segments >= 512 tokens
   int64_t n = want < maxseg ? want : maxseg;
   if (n < 1) n = 1;
-  int64_t tseg = ((T + n - 1) / n + kC - 1) / kC * kC;
+  int64_t tseg = ((T + n - 1) / n + kSegAlign - 1) / kSegAlign * kSegAlign;
   p.nseg = (int)((T + tseg - 1) / tseg);
   p.tseg = tseg;
   return p;
@@ -592,11 +601,15 @@ extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void*
     s_seg = ws.s_seg;
     z_seg = ws.z_seg;
   }
-  if (int e = opt_in_smem(causal_fwd_kernel, kSmemFwd, "causal_fwd")) return e;
-  causal_fwd_kernel<<<dim3(BH, p.nseg), kThreads, kSmemFwd, st>>>((const __half*)q, (const __half*)k, (const __half*)v,
-                                                                  (__half*)out, s_seg, z_seg, s_out, z_out, T, BH,
-                                                                  p.nseg, p.tseg);
-  return check_launch("rfa_causal_fwd");
+  if (getenv("RFA_DEBUG_SIMT_FWD")) {
+    if (int e = opt_in_smem(causal_fwd_kernel, kSmemFwd, "causal_fwd")) return e;
+    causal_fwd_kernel<<<dim3(BH, p.nseg), kThreads, kSmemFwd, st>>>((const __half*)q, (const __half*)k, (const __half*)v,
+                                                                    (__half*)out, s_seg, z_seg, s_out, z_out, T, BH,
+                                                                    p.nseg, p.tseg);
+    return check_launch("rfa_causal_fwd");
+  }
+  return launch_causal_fwd_tc((const __half*)q, (const __half*)k, (const __half*)v, (__half*)out, s_seg, z_seg, s_out,
+                              z_out, T, BH, p.nseg, p.tseg, st);
 }
 
 extern "C" int rfa_causal_bwd_q(const void* q, const void* k, const void* v, const void* g, void* gq,

@@ -51,3 +51,12 @@ def assert_close(got, want, what, rel=REL_L2_TOL, mabs=MAX_ABS_TOL):
     mabs = max(mabs, float(want.abs().max()) * 2.0 ** -10) if want.numel() else mabs
     assert r <= rel and m <= mabs, f"{what}: rel-L2 {r:.3e} (tol {rel}), max-abs {m:.3e} (tol {mabs})"
     return r, m
+
+
+@pytest.fixture(autouse=True)
+def _device_health(request):
+    """After every GPU test: no bounded wait inside a tensor-core kernel may have run out."""
+    yield
+    if request.node.get_closest_marker("gpu") and torch.cuda.is_available():
+        from rfa_b200 import _lib
+        assert _lib.load().rfa_debug_status() == 0, "a bounded wait inside a kernel ran out"
