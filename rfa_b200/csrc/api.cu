@@ -23,7 +23,21 @@ int check_launch(const char* what) {
   return (int)e;
 }
 
+int tc_status_causal_fwd();
+int tc_status_causal_bwd();
+
 }  // namespace rfa
+
+// Sticky device-side status of the tensor-core kernels: 0 = no bounded wait ever ran out;
+// otherwise 100 * kernel family + the site code of the first wait that did.  Synchronises
+// the device and clears the flags.
+extern "C" int rfa_debug_status(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1000;
+  const int f = rfa::tc_status_causal_fwd(), b = rfa::tc_status_causal_bwd();
+  if (f) return f < 0 ? f : 100 + f;
+  if (b) return b < 0 ? b : 200 + b;
+  return 0;
+}
 
 extern "C" int rfa_version(void) { return RFA_B200_VERSION; }
 extern "C" const char* rfa_last_error(void) { return rfa::g_err; }

@@ -33,6 +33,10 @@ constexpr int kSegAlign = 128;
 int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __half* out, const float* s_seg,
                          const float* z_seg, float* s_out, float* z_out, int64_t T, int BH, int nseg, int64_t tseg,
                          cudaStream_t st);
+// tensor-core backward, forward-direction sweep (causal_bwd_tc.cu)
+int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gq,
+                           const float* s_seg, const float* z_seg, float* ws_den, float* ws_gz, float* ds_seg,
+                           float* dz_seg, int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st);
 
 static CausalPlan plan_causal(int64_t T, int BH) {
   CausalPlan p{1, ((T + kSegAlign - 1) / kSegAlign) * kSegAlign};
@@ -265,8 +269,8 @@ causal_bwd_q_kernel(const __half* __restrict__ q, const __half* __restrict__ k, 
         den[r] = dn;
         gzs[r] = gzv;
         if (r < valid) {
-          ws_den[(size_t)(t0 + r) * BH + bh] = dn;
-          ws_gz[(size_t)(t0 + r) * BH + bh] = gzv;
+          ws_den[(size_t)bh * T + t0 + r] = dn;
+          ws_gz[(size_t)bh * T + t0 + r] = gzv;
         }
       }
     }
@@ -328,8 +332,8 @@ causal_bwd_kv_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
     stage_rows<kD>(Gs, kLD, g + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
     if (threadIdx.x < kC) {
       const int r = threadIdx.x;
-      den[r] = r < valid ? ws_den[(size_t)(t0 + r) * BH + bh] : 1.f;
-      gzs[r] = r < valid ? ws_gz[(size_t)(t0 + r) * BH + bh] : 0.f;
+      den[r] = r < valid ? ws_den[(size_t)bh * T + t0 + r] : 1.f;
+      gzs[r] = r < valid ? ws_gz[(size_t)bh * T + t0 + r] : 0.f;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < kC * kD; idx += kThreads) Gs[(idx / kD) * kLD + (idx % kD)] /= den[idx / kD];
@@ -641,11 +645,17 @@ extern "C" int rfa_causal_bwd_q(const void* q, const void* k, const void* v, con
     z_seg = ws.z_seg;
   }
   const bool want_dseg = p.nseg > 1 || ds_seg != nullptr;
-  if (int e = opt_in_smem(causal_bwd_q_kernel, kSmemBwdQ, "causal_bwd_q")) return e;
-  causal_bwd_q_kernel<<<dim3(BH, p.nseg), kThreads, kSmemBwdQ, st>>>(
-      (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gq, s_seg, z_seg, ws.den, ws.gz,
-      want_dseg ? ws.ds_seg : nullptr, want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg);
-  if (int e = check_launch("rfa_causal_bwd_q")) return e;
+  if (getenv("RFA_DEBUG_SIMT_BWD")) {
+    if (int e = opt_in_smem(causal_bwd_q_kernel, kSmemBwdQ, "causal_bwd_q")) return e;
+    causal_bwd_q_kernel<<<dim3(BH, p.nseg), kThreads, kSmemBwdQ, st>>>(
+        (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gq, s_seg, z_seg, ws.den, ws.gz,
+        want_dseg ? ws.ds_seg : nullptr, want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg);
+    if (int e = check_launch("rfa_causal_bwd_q")) return e;
+  } else if (int e = launch_causal_bwd_q_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g,
+                                            (__half*)gq, s_seg, z_seg, ws.den, ws.gz, want_dseg ? ws.ds_seg : nullptr,
+                                            want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg, st)) {
+    return e;
+  }
   if (ds_seg) {   // this shard's own total, before any carry is known
     if (int e = scan_launch(ws.ds_seg, nullptr, ds_seg, BH, p.nseg, kK * kD, 1, 0, st)) return e;
     if (int e = scan_launch(ws.dz_seg, nullptr, dz_seg, BH, p.nseg, kK, 1, 0, st)) return e;

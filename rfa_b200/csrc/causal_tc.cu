@@ -14,14 +14,10 @@
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 =
 // epilogue (thread <-> TMEM lane <-> token row / state row).  Two shared-memory stages
 // of Q, K, V; two TMEM buffers for A/P.  All waits are bounded.
-#include "sm100.cuh"
-#include "tiles.cuh"
+#include "tc_common.cuh"
 
 namespace rfa {
 
-using namespace sm100;
-
-constexpr int kTC = 128;                       // tokens per chunk
 constexpr int kTcThreads = 192;
 
 // shared memory map (bytes from a 1024-aligned base)
@@ -41,22 +37,6 @@ constexpr uint32_t kColS = 384;      // 128 (64 S + z + zeros)
 
 enum { kBarFull = 0, kBarEmpty = 2, kBarA = 4, kBarP = 6, kBarN = 8, kBarNFree = 9, kBarS = 10, kBarSt = 11, kBarEpi = 12, kNumBars = 13 };
 
-__device__ int g_tc_status;          // sticky: first timeout site (0 = none)
-
-__device__ __forceinline__ void tc_fail(int code) { atomicCAS(&g_tc_status, 0, code); }
-
-// Barrier among the 128 epilogue threads built on an mbarrier so that it, too, is bounded.
-__device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase) {
-  mbar_arrive(bar);
-  const bool ok = mbar_wait(bar, phase);
-  phase ^= 1u;
-  return ok;
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -342,14 +322,6 @@ int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __ha
   return check_launch("rfa_causal_fwd");
 }
 
-}  // namespace rfa
+int tc_status_causal_fwd() { return tc_status_read_clear(); }
 
-// Sticky device-side status of the tensor-core kernels: 0 = no bounded wait ever ran out;
-// otherwise the code of the first wait that did.  Synchronises the device; resets the flag.
-extern "C" int rfa_debug_status(void) {
-  int v = 0, zero = 0;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -1000;
-  if (cudaMemcpyFromSymbol(&v, rfa::g_tc_status, sizeof(int)) != cudaSuccess) return -1001;
-  cudaMemcpyToSymbol(rfa::g_tc_status, &zero, sizeof(int));
-  return v;
-}
+}  // namespace rfa
