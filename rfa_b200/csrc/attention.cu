@@ -38,6 +38,10 @@ int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, co
                            const float* s_seg, const float* z_seg, float* ws_den, float* ws_gz, float* ds_seg,
                            float* dz_seg, int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st);
 
+int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gk, __half* gv,
+                            const float* ws_den, const float* ws_gz, const float* ds_seg, const float* dz_seg,
+                            int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st);
+
 static CausalPlan plan_causal(int64_t T, int BH) {
   CausalPlan p{1, ((T + kSegAlign - 1) / kSegAlign) * kSegAlign};
   if (BH >= 120 || T < 1024) return p;
@@ -683,11 +687,15 @@ extern "C" int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, co
     ds_seg = ws.ds_seg;
     dz_seg = ws.dz_seg;
   }
-  if (int e = opt_in_smem(causal_bwd_kv_kernel, kSmemBwdKV, "causal_bwd_kv")) return e;
-  causal_bwd_kv_kernel<<<dim3(BH, p.nseg), kThreads, kSmemBwdKV, st>>>(
-      (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gk, (__half*)gv, ws.den, ws.gz,
-      ds_seg, dz_seg, T, BH, p.nseg, p.tseg);
-  return check_launch("rfa_causal_bwd_kv");
+  if (getenv("RFA_DEBUG_SIMT_BWD")) {
+    if (int e = opt_in_smem(causal_bwd_kv_kernel, kSmemBwdKV, "causal_bwd_kv")) return e;
+    causal_bwd_kv_kernel<<<dim3(BH, p.nseg), kThreads, kSmemBwdKV, st>>>(
+        (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gk, (__half*)gv, ws.den, ws.gz,
+        ds_seg, dz_seg, T, BH, p.nseg, p.tseg);
+    return check_launch("rfa_causal_bwd_kv");
+  }
+  return launch_causal_bwd_kv_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gk,
+                                 (__half*)gv, ws.den, ws.gz, ds_seg, dz_seg, T, BH, p.nseg, p.tseg, st);
 }
 
 extern "C" int rfa_causal_bwd(const void* q, const void* k, const void* v, const void* g,
