@@ -107,6 +107,27 @@ int rfa_causal_bwd(const void* q, const void* k, const void* v, const void* g,
                    void* workspace, size_t workspace_bytes,
                    int64_t T, int BH, int K, int d, rfa_stream_t stream);
 
+/* Backward without any caller scratch and without any allocation: the same two
+ * sweeps as rfa_causal_bwd from a zero state (no carries), with the per-token
+ * scalars kept in a fixed 4 MiB array inside the library (present on every GPU
+ * that loads it).  For hosts that may not call cudaMalloc once they are running
+ * (a server that owns all device memory in its own pools; a C caller without a
+ * device allocator).  It has no counterpart in upstream, whose extension
+ * allocates its outputs itself (cuda/backward.cu:556-558).
+ *   - T * BH must not exceed rfa_causal_bwd_noalloc_max_token_heads() (524288);
+ *     larger problems are refused with RFA_EWORKSPACE.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that call before starting any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels can
+ *     overlap on the GPU (different streams, no dependency) race on it.  Calls
+ *     on one stream are safe.  Nothing in it needs clearing between calls: each
+ *     call's first sweep rewrites every element its second sweep reads.
+ *   - Calls neither cudaMalloc/cudaFree nor any allocating library routine. */
+int64_t rfa_causal_bwd_noalloc_max_token_heads(void);
+int rfa_causal_bwd_noalloc(const void* q, const void* k, const void* v, const void* g,
+                           void* gq, void* gk, void* gv,
+                           int64_t T, int BH, int K, int d, rfa_stream_t stream);
+
 /* The two halves of the backward, for a sequence sharded across devices:
  * _bwd_q runs the forward-direction sweep (gq; leaves per-token scalars in the
  * workspace) and writes this shard's own reverse-state total to ds_seg/dz_seg;

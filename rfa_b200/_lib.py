@@ -32,6 +32,8 @@ SIGNATURES = {
     "rfa_causal_bwd": (_int, [_vp] * 4 + [_vp] * 3 + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_causal_bwd_q": (_int, [_vp] * 4 + [_vp] + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_causal_bwd_kv": (_int, [_vp] * 4 + [_vp] * 2 + [_vp] * 2 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
+    "rfa_causal_bwd_noalloc_max_token_heads": (_i64, []),
+    "rfa_causal_bwd_noalloc": (_int, [_vp] * 4 + [_vp] * 3 + [_i64, _int, _int, _int, _vp]),
     "rfa_cross_state_fwd": (_int, [_vp] * 5 + [_i64, _int, _int, _int, _int, _vp]),
     "rfa_cross_state_bwd": (_int, [_vp] * 7 + [_i64, _int, _int, _int, _int, _vp]),
     "rfa_cross_query_fwd": (_int, [_vp] * 4 + [_i64, _int, _int, _int, _vp]),
