@@ -1,19 +1,12 @@
-// Causal and cross Random Feature Attention, forward and backward, as a chunked
-// prefix scan (K = 128, d = 64, fp16 I/O, fp32 arithmetic and fp32 carried state).
+// Host orchestration of causal RFA (segment planning, workspace, boundary-state scan; the
+// chunk kernels themselves are the tcgen05 kernels in causal_tc.cu / causal_bwd_tc.cu), the
+// state-reduction and scan kernels, and the cross-attention kernels (K = 128, d = 64, fp16
+// I/O, fp32 arithmetic and fp32 state).
 //
 // Notation per (batch, head):  S = sum k v^T [K,d],  z = sum k [K]  (upstream rfa.py:57-64).
-// A sequence is cut into chunks of C tokens.  Inside a chunk the contributions of
-// the chunk's own tokens are dense products
-//     A  = mask(Q K^T)              N = A V + Q S_prev        den = rowsum(A) + Q z_prev
-// and the running state moves on by  S += K^T V, z += colsum(K).  The backward
-// (upstream rfa.py:79-101) is two sweeps: a forward-direction sweep that rebuilds
-// out/den and produces grad_q, and a reverse sweep that carries
-// dS = sum_{later t} q_t (x) g_t/den_t,  dz = sum_{later t} q_t * gz_t  and produces
-// grad_k, grad_v.  With few (batch, head) pairs the sequence is additionally cut into
-// segments that run as separate CTAs; their boundary states come from a reduction
-// pre-pass plus an exclusive scan, the same primitive a multi-device split uses.
-#include <stdlib.h>
-
+// With few (batch, head) pairs a sequence is cut into segments that run as separate CTAs;
+// the states at their boundaries come from a reduction pre-pass plus an exclusive scan, the
+// same primitive a multi-device split of the sequence uses.
 #include "tiles.cuh"
 
 namespace rfa {
@@ -136,236 +129,6 @@ __global__ void scan_states_kernel(float* __restrict__ seg, const float* __restr
     sum += t;
   }
   if (total) total[i] = sum;
-}
-
-// ---------------------------------------------------------------------------
-// causal forward, grid (BH, nseg)
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
-causal_fwd_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
-                  __half* __restrict__ out, const float* __restrict__ s_seg, const float* __restrict__ z_seg,
-                  float* __restrict__ s_out, float* __restrict__ z_out, int64_t T, int BH, int nseg,
-                  int64_t tseg) {
-  extern __shared__ __align__(16) float sm[];
-  float* Qs = sm;
-  float* Ks = Qs + kC * kLK;
-  float* Vs = Ks + kC * kLK;
-  float* As = Vs + kC * kLD;
-  float* Ns = As + kC * kLD;
-  float* St = Ns + kC * kLD;
-  float* zs = St + kK * kLD;
-  float* den = zs + kK;
-  const int bh = blockIdx.x, seg = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
-  const size_t slot = (size_t)bh * nseg + seg;
-  load_state(St, zs, s_seg ? s_seg + slot * kK * kD : nullptr, z_seg ? z_seg + slot * kK : nullptr);
-  for (int64_t t0 = t_begin; t0 < t_end; t0 += kC) {
-    const int valid = (int)min((int64_t)kC, t_end - t0);
-    __syncthreads();
-    stage_rows<kK>(Qs, kLK, q + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kK>(Ks, kLK, k + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kD>(Vs, kLD, v + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    __syncthreads();
-    // A[t][s] = q_t . k_s for s <= t (inclusive prefix: a token sees itself)
-    tile_gemm<4, 4>(kC, kC, kK,
-                    [&](int r, int l) { return Qs[r * kLK + l]; },
-                    [&](int l, int c) { return Ks[c * kLK + l]; },
-                    [&](int r, int c, float a) { As[r * kLD + c] = c <= r ? a : 0.f; });
-    __syncthreads();
-    // N = A V + Q S_prev
-    tile_gemm<4, 4>(kC, kD, kC + kK,
-                    [&](int r, int l) { return l < kC ? As[r * kLD + l] : Qs[r * kLK + l - kC]; },
-                    [&](int l, int j) { return l < kC ? Vs[l * kLD + j] : St[(l - kC) * kLD + j]; },
-                    [&](int r, int j, float a) { Ns[r * kLD + j] = a; });
-    for (int r = warp; r < kC; r += kThreads / 32) {
-      float p = As[r * kLD + lane] + As[r * kLD + lane + 32];
-#pragma unroll
-      for (int l = lane; l < kK; l += 32) p = fmaf(Qs[r * kLK + l], zs[l], p);
-      p = warp_sum(p);
-      if (lane == 0) den[r] = fmaxf(p, kEps);
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < kC * (kD / 8); idx += kThreads) {
-      const int r = idx / (kD / 8), c = (idx % (kD / 8)) * 8;
-      if (r >= valid) continue;
-      const float inv = 1.f / den[r];
-      float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = Ns[r * kLD + c + e] * inv;
-      store8(out + ((size_t)(t0 + r) * BH + bh) * kD + c, f);
-    }
-    accumulate_state(St, zs, Ks, Vs, nullptr);
-  }
-  __syncthreads();
-  if (s_out && seg == nseg - 1) store_state(s_out + (size_t)bh * kK * kD, z_out + (size_t)bh * kK, St, zs);
-}
-
-// ---------------------------------------------------------------------------
-// causal backward, sweep 1 (forward direction): grad_q, per-token den / gz into the
-// workspace, optionally this segment's reverse-state total.  grid (BH, nseg)
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
-causal_bwd_q_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
-                    const __half* __restrict__ g, __half* __restrict__ gq,
-                    const float* __restrict__ s_seg, const float* __restrict__ z_seg,
-                    float* __restrict__ ws_den, float* __restrict__ ws_gz,
-                    float* __restrict__ ds_seg, float* __restrict__ dz_seg,
-                    int64_t T, int BH, int nseg, int64_t tseg) {
-  extern __shared__ __align__(16) float sm[];
-  float* Qs = sm;
-  float* Ks = Qs + kC * kLK;
-  float* Ds = Ks + kC * kLK;      // N (first kC*kLD floats), then grad_q tile
-  float* Vs = Ds + kC * kLK;
-  float* Gs = Vs + kC * kLD;
-  float* As = Gs + kC * kLD;
-  float* St = As + kC * kLD;
-  float* dSt = St + kK * kLD;
-  float* zs = dSt + kK * kLD;
-  float* dzs = zs + kK;
-  float* den = dzs + kK;
-  float* gzs = den + kC;
-  float* Ns = Ds;
-  const int bh = blockIdx.x, seg = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
-  const size_t slot = (size_t)bh * nseg + seg;
-  const bool want_dseg = ds_seg != nullptr;
-  load_state(St, zs, s_seg ? s_seg + slot * kK * kD : nullptr, z_seg ? z_seg + slot * kK : nullptr);
-  load_state(dSt, dzs, nullptr, nullptr);
-  for (int64_t t0 = t_begin; t0 < t_end; t0 += kC) {
-    const int valid = (int)min((int64_t)kC, t_end - t0);
-    __syncthreads();
-    stage_rows<kK>(Qs, kLK, q + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kK>(Ks, kLK, k + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kD>(Vs, kLD, v + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    stage_rows<kD>(Gs, kLD, g + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    __syncthreads();
-    tile_gemm<4, 4>(kC, kC, kK,
-                    [&](int r, int l) { return Qs[r * kLK + l]; },
-                    [&](int l, int c) { return Ks[c * kLK + l]; },
-                    [&](int r, int c, float a) { As[r * kLD + c] = c <= r ? a : 0.f; });
-    __syncthreads();
-    tile_gemm<4, 4>(kC, kD, kC + kK,
-                    [&](int r, int l) { return l < kC ? As[r * kLD + l] : Qs[r * kLK + l - kC]; },
-                    [&](int l, int j) { return l < kC ? Vs[l * kLD + j] : St[(l - kC) * kLD + j]; },
-                    [&](int r, int j, float a) { Ns[r * kLD + j] = a; });
-    for (int r = warp; r < kC; r += kThreads / 32) {
-      float p = As[r * kLD + lane] + As[r * kLD + lane + 32];
-#pragma unroll
-      for (int l = lane; l < kK; l += 32) p = fmaf(Qs[r * kLK + l], zs[l], p);
-      p = warp_sum(p);
-      if (lane == 0) den[r] = p;      // raw; clamped below
-    }
-    __syncthreads();
-    // per-row scalars:  gs = g/den,  gz = -(g.out)/den * [raw > 1]   (strict >, rfa.py:91)
-    for (int r = warp; r < kC; r += kThreads / 32) {
-      const float raw = den[r];
-      const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
-      const float g0 = Gs[r * kLD + lane], g1 = Gs[r * kLD + lane + 32];
-      float go = g0 * Ns[r * kLD + lane] + g1 * Ns[r * kLD + lane + 32];
-      go = warp_sum(go) * inv;                       // g . out
-      const float gzv = raw > kEps ? -go * inv : 0.f;
-      Gs[r * kLD + lane] = g0 * inv;
-      Gs[r * kLD + lane + 32] = g1 * inv;
-      __syncwarp();
-      if (lane == 0) {
-        den[r] = dn;
-        gzs[r] = gzv;
-        if (r < valid) {
-          ws_den[(size_t)bh * T + t0 + r] = dn;
-          ws_gz[(size_t)bh * T + t0 + r] = gzv;
-        }
-      }
-    }
-    __syncthreads();
-    // dA[t][s] = gs_t . v_s + gz_t  for s <= t
-    tile_gemm<4, 4>(kC, kC, kD,
-                    [&](int r, int l) { return Gs[r * kLD + l]; },
-                    [&](int l, int c) { return Vs[c * kLD + l]; },
-                    [&](int r, int c, float a) { As[r * kLD + c] = c <= r ? a + gzs[r] : 0.f; });
-    __syncthreads();
-    // grad_q = dA K + gs S_prev^T + gz z_prev^T
-    tile_gemm<4, 8>(kC, kK, kC + kD,
-                    [&](int r, int l) { return l < kC ? As[r * kLD + l] : Gs[r * kLD + l - kC]; },
-                    [&](int l, int c) { return l < kC ? Ks[l * kLK + c] : St[c * kLD + l - kC]; },
-                    [&](int r, int c, float a) { Ds[r * kLK + c] = fmaf(gzs[r], zs[c], a); });
-    __syncthreads();
-    unstage_rows<kK>(gq + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, Ds, kLK, valid);
-    accumulate_state(St, zs, Ks, Vs, nullptr);
-    if (want_dseg) accumulate_state(dSt, dzs, Qs, Gs, gzs);
-  }
-  __syncthreads();
-  if (want_dseg) store_state(ds_seg + slot * kK * kD, dz_seg + slot * kK, dSt, dzs);
-}
-
-// ---------------------------------------------------------------------------
-// causal backward, sweep 2 (reverse direction): grad_k, grad_v.  grid (BH, nseg)
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
-causal_bwd_kv_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
-                     const __half* __restrict__ g, __half* __restrict__ gk, __half* __restrict__ gv,
-                     const float* __restrict__ ws_den, const float* __restrict__ ws_gz,
-                     const float* __restrict__ ds_seg, const float* __restrict__ dz_seg,
-                     int64_t T, int BH, int nseg, int64_t tseg) {
-  extern __shared__ __align__(16) float sm[];
-  float* Qs = sm;
-  float* Ks = Qs + kC * kLK;
-  float* Ds = Ks + kC * kLK;      // grad_k tile
-  float* Vs = Ds + kC * kLK;
-  float* Gs = Vs + kC * kLD;
-  float* As = Gs + kC * kLD;
-  float* dAs = As + kC * kLD;
-  float* Os = dAs + kC * kLD;     // grad_v tile
-  float* dSt = Os + kC * kLD;
-  float* dzs = dSt + kK * kLD;
-  float* den = dzs + kK;
-  float* gzs = den + kC;
-  const int bh = blockIdx.x, seg = blockIdx.y;
-  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
-  const size_t slot = (size_t)bh * nseg + seg;
-  load_state(dSt, dzs, ds_seg ? ds_seg + slot * kK * kD : nullptr, dz_seg ? dz_seg + slot * kK : nullptr);
-  const int64_t nchunk = (t_end - t_begin + kC - 1) / kC;
-  for (int64_t ci = nchunk - 1; ci >= 0; --ci) {
-    const int64_t t0 = t_begin + ci * kC;
-    const int valid = (int)min((int64_t)kC, t_end - t0);
-    __syncthreads();
-    stage_rows<kK>(Qs, kLK, q + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kK>(Ks, kLK, k + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kD>(Vs, kLD, v + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    stage_rows<kD>(Gs, kLD, g + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    if (threadIdx.x < kC) {
-      const int r = threadIdx.x;
-      den[r] = r < valid ? ws_den[(size_t)bh * T + t0 + r] : 1.f;
-      gzs[r] = r < valid ? ws_gz[(size_t)bh * T + t0 + r] : 0.f;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < kC * kD; idx += kThreads) Gs[(idx / kD) * kLD + (idx % kD)] /= den[idx / kD];
-    tile_gemm<4, 4>(kC, kC, kK,
-                    [&](int r, int l) { return Qs[r * kLK + l]; },
-                    [&](int l, int c) { return Ks[c * kLK + l]; },
-                    [&](int r, int c, float a) { As[r * kLD + c] = c <= r ? a : 0.f; });
-    __syncthreads();
-    tile_gemm<4, 4>(kC, kC, kD,
-                    [&](int r, int l) { return Gs[r * kLD + l]; },
-                    [&](int l, int c) { return Vs[c * kLD + l]; },
-                    [&](int r, int c, float a) { dAs[r * kLD + c] = c <= r ? a + gzs[r] : 0.f; });
-    __syncthreads();
-    // grad_k[s] = sum_t dA[t][s] q_t + dS_next v_s + dz_next
-    tile_gemm<4, 8>(kC, kK, kC + kD,
-                    [&](int s, int l) { return l < kC ? dAs[l * kLD + s] : Vs[s * kLD + l - kC]; },
-                    [&](int l, int c) { return l < kC ? Qs[l * kLK + c] : dSt[c * kLD + l - kC]; },
-                    [&](int s, int c, float a) { Ds[s * kLK + c] = a + dzs[c]; });
-    // grad_v[s] = sum_t A[t][s] gs_t + dS_next^T k_s
-    tile_gemm<4, 4>(kC, kD, kC + kK,
-                    [&](int s, int l) { return l < kC ? As[l * kLD + s] : Ks[s * kLK + l - kC]; },
-                    [&](int l, int j) { return l < kC ? Gs[l * kLD + j] : dSt[(l - kC) * kLD + j]; },
-                    [&](int s, int j, float a) { Os[s * kLD + j] = a; });
-    __syncthreads();
-    unstage_rows<kK>(gk + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, Ds, kLK, valid);
-    unstage_rows<kD>(gv + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, Os, kLD, valid);
-    accumulate_state(dSt, dzs, Qs, Gs, gzs);
-  }
 }
 
 // ---------------------------------------------------------------------------
@@ -520,9 +283,6 @@ cross_state_bwd_kernel(const __half* __restrict__ k, const __half* __restrict__ 
 // host side
 // ---------------------------------------------------------------------------
 constexpr size_t kSmemState = (size_t)(kC * kLK + kC * kLD + kK * kLD + kK) * sizeof(float);
-constexpr size_t kSmemFwd = (size_t)(2 * kC * kLK + 3 * kC * kLD + kK * kLD + kK + kC) * sizeof(float);
-constexpr size_t kSmemBwdQ = (size_t)(3 * kC * kLK + 3 * kC * kLD + 2 * kK * kLD + 2 * kK + 2 * kC) * sizeof(float);
-constexpr size_t kSmemBwdKV = (size_t)(3 * kC * kLK + 5 * kC * kLD + kK * kLD + kK + 2 * kC) * sizeof(float);
 constexpr size_t kSmemXqFwd = (size_t)(kC * kLK + kC * kLD + kK * kLD + kK + kC) * sizeof(float);
 constexpr size_t kSmemXqBwd = (size_t)(2 * kC * kLK + 2 * kC * kLD + 2 * kK * kLD + 2 * kK + 2 * kC) * sizeof(float);
 constexpr size_t kSmemXsBwd = (size_t)(2 * kC * kLK + 2 * kC * kLD + kK * kLD + kK + kC) * sizeof(float);
@@ -609,13 +369,6 @@ extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void*
     s_seg = ws.s_seg;
     z_seg = ws.z_seg;
   }
-  if (getenv("RFA_DEBUG_SIMT_FWD")) {
-    if (int e = opt_in_smem(causal_fwd_kernel, kSmemFwd, "causal_fwd")) return e;
-    causal_fwd_kernel<<<dim3(BH, p.nseg), kThreads, kSmemFwd, st>>>((const __half*)q, (const __half*)k, (const __half*)v,
-                                                                    (__half*)out, s_seg, z_seg, s_out, z_out, T, BH,
-                                                                    p.nseg, p.tseg);
-    return check_launch("rfa_causal_fwd");
-  }
   return launch_causal_fwd_tc((const __half*)q, (const __half*)k, (const __half*)v, (__half*)out, s_seg, z_seg, s_out,
                               z_out, T, BH, p.nseg, p.tseg, st);
 }
@@ -649,17 +402,10 @@ extern "C" int rfa_causal_bwd_q(const void* q, const void* k, const void* v, con
     z_seg = ws.z_seg;
   }
   const bool want_dseg = p.nseg > 1 || ds_seg != nullptr;
-  if (getenv("RFA_DEBUG_SIMT_BWD")) {
-    if (int e = opt_in_smem(causal_bwd_q_kernel, kSmemBwdQ, "causal_bwd_q")) return e;
-    causal_bwd_q_kernel<<<dim3(BH, p.nseg), kThreads, kSmemBwdQ, st>>>(
-        (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gq, s_seg, z_seg, ws.den, ws.gz,
-        want_dseg ? ws.ds_seg : nullptr, want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg);
-    if (int e = check_launch("rfa_causal_bwd_q")) return e;
-  } else if (int e = launch_causal_bwd_q_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g,
-                                            (__half*)gq, s_seg, z_seg, ws.den, ws.gz, want_dseg ? ws.ds_seg : nullptr,
-                                            want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg, st)) {
+  if (int e = launch_causal_bwd_q_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g,
+                                     (__half*)gq, s_seg, z_seg, ws.den, ws.gz, want_dseg ? ws.ds_seg : nullptr,
+                                     want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg, st))
     return e;
-  }
   if (ds_seg) {   // this shard's own total, before any carry is known
     if (int e = scan_launch(ws.ds_seg, nullptr, ds_seg, BH, p.nseg, kK * kD, 1, 0, st)) return e;
     if (int e = scan_launch(ws.dz_seg, nullptr, dz_seg, BH, p.nseg, kK, 1, 0, st)) return e;
@@ -686,13 +432,6 @@ extern "C" int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, co
     if (int e = scan_launch(ws.dz_seg, dz_in, nullptr, BH, p.nseg, kK, 1, 1, st)) return e;
     ds_seg = ws.ds_seg;
     dz_seg = ws.dz_seg;
-  }
-  if (getenv("RFA_DEBUG_SIMT_BWD")) {
-    if (int e = opt_in_smem(causal_bwd_kv_kernel, kSmemBwdKV, "causal_bwd_kv")) return e;
-    causal_bwd_kv_kernel<<<dim3(BH, p.nseg), kThreads, kSmemBwdKV, st>>>(
-        (const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gk, (__half*)gv, ws.den, ws.gz,
-        ds_seg, dz_seg, T, BH, p.nseg, p.tseg);
-    return check_launch("rfa_causal_bwd_kv");
   }
   return launch_causal_bwd_kv_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gk,
                                  (__half*)gv, ws.den, ws.gz, ds_seg, dz_seg, T, BH, p.nseg, p.tseg, st);
