@@ -1,0 +1,107 @@
+"""The sequence-sharded scan on CPU ranks (gloo, world size 2 and 3): the rank-level logic of
+rfa_b200.sharded -- local reduction, exclusive prefix / suffix scan over ranks, carries --
+with the CPU oracle standing in for the local kernels.  The sharded result must equal the
+unsharded oracle on the full sequence, outputs and all gradients."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import rfa_oracle as O
+
+
+class OracleKernels:
+    """Same four steps as rfa_b200.sharded._CudaKernels, computed by the oracle in fp64."""
+
+    @staticmethod
+    def segment_state(k, v):
+        return O.segment_state(k, v)
+
+    @staticmethod
+    def forward(q, k, v, s_in, z_in):
+        return O.causal_forward(q, k, v, s0=s_in, z0=z_in)
+
+    @staticmethod
+    def backward_q(q, k, v, g, s_in, z_in):
+        gq, _, _, ds, dz = O.causal_backward(q, k, v, g, s0=s_in, z0=z_in, return_dstate=True)
+        return gq, ds, dz, (s_in, z_in)
+
+    @staticmethod
+    def backward_kv(q, k, v, g, ds_in, dz_in, ctx):
+        s_in, z_in = ctx
+        _, gk, gv = O.causal_backward(q, k, v, g, s0=s_in, z0=z_in, ds_in=ds_in, dz_in=dz_in)
+        return gk, gv
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, T, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from rfa_b200 import sharded
+        sharded.SequenceShardedRFA.kernels = OracleKernels
+        out_q.put((rank, _run(rank, world, T, sharded)))
+    except Exception as e:  # noqa: BLE001 -- report instead of leaving the parent waiting
+        out_q.put((rank, [repr(e)]))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(rank, world, T, sharded):
+    if True:
+        gen = torch.Generator().manual_seed(0)
+        BH, K, d = 3, 16, 8
+        q = (torch.rand(T, BH, K, generator=gen, dtype=torch.float64) * 0.4)
+        k = (torch.rand(T, BH, K, generator=gen, dtype=torch.float64) * 0.4)
+        v = torch.randn(T, BH, d, generator=gen, dtype=torch.float64)
+        g = torch.randn(T, BH, d, generator=gen, dtype=torch.float64)
+        lo, hi = sharded.shard_bounds(T, world, rank, align=8)
+        ql, kl, vl = (t[lo:hi].clone().requires_grad_(True) for t in (q, k, v))
+        out = sharded.sequence_sharded_causal_rfa(ql, kl, vl)
+        out.backward(g[lo:hi])
+        ro = O.causal_forward(q, k, v)
+        rq, rk, rv = O.causal_backward(q, k, v, g)
+        errs = [float((out.detach() - ro[lo:hi]).abs().max()) if hi > lo else 0.0]
+        for a, b in ((ql.grad, rq), (kl.grad, rk), (vl.grad, rv)):
+            errs.append(float((a - b[lo:hi]).abs().max()) if hi > lo else 0.0)
+        # the scan primitive itself
+        x = torch.full((2, 3), float(rank + 1))
+        pre = sharded.exclusive_scan_over_ranks(x)
+        suf = sharded.exclusive_scan_over_ranks(x, reverse=True)
+        errs.append(float((pre - sum(range(1, rank + 1))).abs().max()))
+        errs.append(float((suf - sum(range(rank + 2, world + 1))).abs().max()))
+        return errs
+
+
+@pytest.mark.parametrize("world,T", [(2, 64), (3, 50)])
+def test_sequence_sharded_equals_unsharded(world, T):
+    ctx = mp.get_context("spawn")
+    out_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, T, out_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out_q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, errs in results:
+        assert all(isinstance(e, float) for e in errs), (rank, errs)
+        assert max(errs) < 1e-10, (rank, errs)
+
+
+def test_shard_bounds_cover_the_sequence():
+    from rfa_b200.sharded import shard_bounds
+    for T, world in ((131072, 8), (1000, 3), (5, 4), (0, 2)):
+        spans = [shard_bounds(T, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == T
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert all((lo % 128 == 0) or lo == T for lo, _ in spans)
