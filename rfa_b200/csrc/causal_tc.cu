@@ -1,44 +1,47 @@
 // Causal RFA forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
 // One CTA walks one (batch, head[, segment]) in chunks of C = 128 tokens.  Per chunk
-// (Q, K: [C][128] fp16; V: [C][64] fp16; S: running [128][64] state; z: running [128]):
+// (Q, K: [C][128] fp16; V: [C][64] fp16; [S|z]: running [128][64+1] state, fp32 in TMEM):
 //     A   = Q K^T                      tcgen05.mma  M128 N128 K128   (smem x smem -> TMEM)
-//     N   = Q [S|z]_prev^T             tcgen05.mma  M128 N80  K128   (smem x smem)
-//     P   = mask(A) as fp16, row sums  epilogue warps, TMEM -> registers -> TMEM (aliases A)
+//     N   = Q [S|z]_prev               tcgen05.mma  M128 N80  K128   (smem x smem; state tile MN-major)
+//     P   = mask(A) as fp16, row sums  score warps: TMEM -> registers -> TMEM (over A)
 //     N  += P V                        tcgen05.mma  M128 N64  K128   (TMEM x smem)
-//     [S|z] += K^T [V|1]               tcgen05.mma  M128 N128 K128   (smem x smem, fp32 in TMEM)
+//     [S|z] += K^T [V|1]               tcgen05.mma  M128 N80  K128   (smem x smem)
 //     out = N[:, :64] / max(rowsum + N[:, 64], 1)
-// The fp32 state never leaves TMEM; its fp16 transposed copy ([80][128], K-major) is
-// re-exported to shared memory once per chunk as the B operand of the next chunk.
+// The fp32 state never leaves TMEM; its fp16 copy ([128 k][64 + 16] in two swizzled boxes)
+// is re-exported to shared memory once per chunk as the B operand of the next chunk.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 =
-// epilogue (thread <-> TMEM lane <-> token row / state row).  Two shared-memory stages
-// of Q, K, V; two TMEM buffers for A/P.  All waits are bounded.
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = score
+// group (A -> P), warps 6..9 = output/state group (N -> out, state export).  Within a group
+// thread <-> TMEM lane <-> token row / state row.  Two shared-memory stages of Q, K, V; two
+// TMEM buffers each for A/P and N, so the score group works one chunk ahead of the output
+// group.  The only per-chunk serial chain is  state MMA -> state export -> next state MMA.
+// All waits are bounded.
 #include "tc_common.cuh"
 
 namespace rfa {
 
-constexpr int kTcThreads = 192;
+constexpr int kFwThreads = 320;
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr uint32_t kBoxQK = 128 * 128;         // one [128 rows][64 halves] box
-constexpr uint32_t kOffQ = 0, kOffK = 2 * kBoxQK, kOffV = 4 * kBoxQK, kStage = 5 * kBoxQK;   // 81920 per stage
-constexpr uint32_t kOffOnes = 2 * kStage;                       // [128][64] box: column 0 = 1, rest 0
-constexpr uint32_t kOffSt = kOffOnes + kBoxQK;                  // [80][128] fp16, two [80][64] boxes
-constexpr uint32_t kBoxSt = 80 * 128;
-constexpr uint32_t kOffOut = kOffSt + 2 * kBoxSt;               // [128][64] output staging
-constexpr uint32_t kOffBar = kOffOut + kBoxQK;
-constexpr uint32_t kTcSmem = kOffBar + 256 + 1024;              // + alignment slack
+constexpr uint32_t kFwQ = 0, kFwK = 2 * kBox, kFwV = 4 * kBox, kFwStage = 5 * kBox;   // 81920 per stage
+constexpr uint32_t kFwOnes = 2 * kFwStage;          // [128][64] box: logical column 0 = 1, rest 0
+constexpr uint32_t kFwS = kFwOnes + kBox;           // state tile: box 0 = S [128 k][64 n], box 1 = [z | 0...]
+constexpr uint32_t kFwOut = kFwS + 2 * kBox;        // [128][64] output staging for the TMA store
+constexpr uint32_t kFwRs = kFwOut + kBox;           // fp32 [2][128] row sums handed from score to output group
+constexpr uint32_t kFwBar = kFwRs + 1024;
+constexpr uint32_t kFwSmem = kFwBar + 256 + 1024;   // + alignment slack
 
 // TMEM columns
-constexpr uint32_t kColA = 0;        // two buffers of 128
-constexpr uint32_t kColN = 256;      // 80
-constexpr uint32_t kColS = 384;      // 128 (64 S + z + zeros)
+constexpr uint32_t fColA = 0;        // two buffers of 128
+constexpr uint32_t fColN = 256;      // two buffers of 80
+constexpr uint32_t fColS = 416;      // 80: S (64) | z | zeros
 
-enum { kBarFull = 0, kBarEmpty = 2, kBarA = 4, kBarP = 6, kBarN = 8, kBarNFree = 9, kBarS = 10, kBarSt = 11, kBarEpi = 12, kNumBars = 13 };
+enum { fFull = 0, fEmpty = 2, fA = 4, fP = 6, fN = 8, fNFree = 10, fS = 12, fSt = 13, fY = 14, fFullV = 15, fEmptyV = 17, fNum = 19 };
+// fFull/fEmpty guard the Q and K tiles of a stage (free once the state MMA has read K), fFullV/fEmptyV its V tile
+// (free once P V has run): the Q, K loads of chunk c+2 start while chunk c is still being finished.
 
-
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kFwThreads, 1)
 causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                      const float* __restrict__ s_seg, const float* __restrict__ z_seg,
@@ -46,8 +49,9 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                      int64_t T, int BH, int nseg, int64_t tseg) {
   extern __shared__ unsigned char tc_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBar);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kFwBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + fNum);
+  float* rs = reinterpret_cast<float*>(sm + kFwRs);
   const uint32_t sbase = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, seg = blockIdx.y;
@@ -59,16 +63,18 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars[kBarFull + i], 1);
-      mbar_init(&bars[kBarEmpty + i], 1);
-      mbar_init(&bars[kBarA + i], 1);
-      mbar_init(&bars[kBarP + i], 128);
+      mbar_init(&bars[fFull + i], 1);
+      mbar_init(&bars[fEmpty + i], 1);
+      mbar_init(&bars[fFullV + i], 1);
+      mbar_init(&bars[fEmptyV + i], 1);
+      mbar_init(&bars[fA + i], 1);
+      mbar_init(&bars[fP + i], 128);
+      mbar_init(&bars[fN + i], 1);
+      mbar_init(&bars[fNFree + i], 128);
     }
-    mbar_init(&bars[kBarN], 1);
-    mbar_init(&bars[kBarNFree], 128);
-    mbar_init(&bars[kBarS], 1);
-    mbar_init(&bars[kBarSt], 128);
-    mbar_init(&bars[kBarEpi], 128);
+    mbar_init(&bars[fS], 1);
+    mbar_init(&bars[fSt], 128);
+    mbar_init(&bars[fY], 128);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_o);
   }
@@ -77,11 +83,11 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tmem_relinquish();
   }
   // the ones box: row r is 128 bytes; logical column 0 lives in 16-byte chunk (r & 7)
-  for (int i = tid; i < (int)(kBoxQK / 16); i += kTcThreads) {
+  for (int i = tid; i < (int)(kBox / 16); i += kFwThreads) {
     const int r = i >> 3, c = i & 7;
     uint4 val = make_uint4(0, 0, 0, 0);
     if (c == (r & 7)) val.x = 0x00003C00u;     // fp16 1.0 in the low half
-    *reinterpret_cast<uint4*>(sm + kOffOnes + i * 16) = val;
+    *reinterpret_cast<uint4*>(sm + kFwOnes + i * 16) = val;
   }
   fence_async_smem();
   tc_fence_before_sync();
@@ -94,111 +100,95 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (lane == 0) {
       for (int c = 0; c < nchunk; ++c) {
         const int st = c & 1;
-        if (c >= 2 && !mbar_wait(&bars[kBarEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
-        unsigned char* base = sm + st * kStage;
+        if (c >= 2 && !mbar_wait(&bars[fEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
+        unsigned char* base = sm + st * kFwStage;
         const int t0 = (int)(t_begin + (int64_t)c * kTC);
-        mbar_arrive_expect_tx(&bars[kBarFull + st], kStage);
-        tma_load_3d(base + kOffQ, &tm_q, &bars[kBarFull + st], 0, bh, t0);
-        tma_load_3d(base + kOffQ + kBoxQK, &tm_q, &bars[kBarFull + st], 64, bh, t0);
-        tma_load_3d(base + kOffK, &tm_k, &bars[kBarFull + st], 0, bh, t0);
-        tma_load_3d(base + kOffK + kBoxQK, &tm_k, &bars[kBarFull + st], 64, bh, t0);
-        tma_load_3d(base + kOffV, &tm_v, &bars[kBarFull + st], 0, bh, t0);
+        uint64_t* fb = &bars[fFull + st];
+        mbar_arrive_expect_tx(fb, 4 * kBox);
+        tma_load_3d(base + kFwQ, &tm_q, fb, 0, bh, t0);
+        tma_load_3d(base + kFwQ + kBox, &tm_q, fb, 64, bh, t0);
+        tma_load_3d(base + kFwK, &tm_k, fb, 0, bh, t0);
+        tma_load_3d(base + kFwK + kBox, &tm_k, fb, 64, bh, t0);
+        if (c >= 2 && !mbar_wait(&bars[fEmptyV + st], ((c >> 1) + 1) & 1)) { tc_fail(14); break; }
+        mbar_arrive_expect_tx(&bars[fFullV + st], kBox);
+        tma_load_3d(base + kFwV, &tm_v, &bars[fFullV + st], 0, bh, t0);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idA = umma_idesc_f16(128, 128, false, false);   // Q K^T
-      constexpr uint32_t idN = umma_idesc_f16(128, 80, false, false);    // Q St^T
-      constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V      (B MN-major)
-      constexpr uint32_t idS = umma_idesc_f16(128, 128, true, true);     // K^T [V|1] (A, B MN-major)
+      constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);    // Q [S|z]   (B MN-major)
+      constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V       (B MN-major)
+      constexpr uint32_t idS = umma_idesc_f16(128, 80, true, true);      // K^T [V|1] (A, B MN-major)
       auto issue_A = [&](int c) {
-        const uint32_t sb = sbase + (c & 1) * kStage;
+        const uint32_t sb = sbase + (c & 1) * kFwStage;
         for (int j = 0; j < 8; ++j) {
-          const uint32_t kk = (j >> 2) * kBoxQK + (j & 3) * 32;
-          umma_ss(tmem + kColA + (c & 1) * 128, umma_smem_desc(sb + kOffQ + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kOffK + kk, 0, 1024, kSwizzle128B), idA, j > 0);
+          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
+          umma_ss(tmem + fColA + (c & 1) * 128, umma_smem_desc(sb + kFwQ + kk, 0, 1024, kSwizzle128B),
+                  umma_smem_desc(sb + kFwK + kk, 0, 1024, kSwizzle128B), idA, j > 0);
         }
-        umma_commit(&bars[kBarA + (c & 1)]);
+        umma_commit(&bars[fA + (c & 1)]);
       };
       bool ok = true;
       if (nchunk > 0) {
-        ok = mbar_wait(&bars[kBarFull + 0], 0);
+        ok = mbar_wait(&bars[fFull + 0], 0);
         if (ok) { tc_fence_after_sync(); issue_A(0); } else tc_fail(2);
       }
       for (int c = 0; ok && c < nchunk; ++c) {
         const int st = c & 1;
-        const uint32_t sb = sbase + st * kStage;
-        if (c + 1 < nchunk) {
-          if (!mbar_wait(&bars[kBarFull + ((c + 1) & 1)], ((c + 1) >> 1) & 1)) { tc_fail(3); break; }
+        const uint32_t sb = sbase + st * kFwStage;
+        // the state before this chunk is in the operand tile, and the output group has let go of S
+        if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); break; }
+        if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); break; }
+        tc_fence_after_sync();
+        for (int j = 0; j < 8; ++j) {            // N = Q [S|z]_prev
+          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
+          umma_ss(tmem + fColN + st * 80, umma_smem_desc(sb + kFwQ + kk, 0, 1024, kSwizzle128B),
+                  umma_smem_desc(sbase + kFwS + j * 2048, kBox, 1024, kSwizzle128B), idQS, j > 0);
+        }
+        if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }
+        tc_fence_after_sync();
+        const bool fresh = (c == 0 && s_in == nullptr);
+        for (int j = 0; j < 8; ++j)              // [S|z] += K^T [V|1]
+          umma_ss(tmem + fColS, umma_smem_desc(sb + kFwK + j * 2048, kBox, 1024, kSwizzle128B),
+                  umma_smem_desc(sb + kFwV + j * 2048, kFwOnes - (st * kFwStage + kFwV), 1024, kSwizzle128B), idS,
+                  (fresh && j == 0) ? 0 : 1);
+        umma_commit(&bars[fS]);
+        umma_commit(&bars[fEmpty + st]);         // Q and K of this stage have been read for the last time
+        // next chunk's scores as early as its Q, K are there, so the score group never starves --
+        // but never hold back this chunk's P V (and with it the release of V) for a load in flight
+        bool next_issued = (c + 1 >= nchunk);
+        if (!next_issued && mbar_try_wait(&bars[fFull + ((c + 1) & 1)], ((c + 1) >> 1) & 1)) {
+          tc_fence_after_sync();
+          issue_A(c + 1);
+          next_issued = true;
+        }
+        if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); break; }
+        tc_fence_after_sync();
+        for (int j = 0; j < 8; ++j)              // N += P V
+          umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8,
+                  umma_smem_desc(sb + kFwV + j * 2048, kBox, 1024, kSwizzle128B), idPV, 1);
+        umma_commit(&bars[fN + st]);
+        umma_commit(&bars[fEmptyV + st]);
+        if (!next_issued) {
+          if (!mbar_wait(&bars[fFull + ((c + 1) & 1)], ((c + 1) >> 1) & 1)) { tc_fail(5); break; }
           tc_fence_after_sync();
           issue_A(c + 1);
         }
-        // N = Q St^T: needs the exported state of all earlier chunks, and N read out by the epilogue
-        if (!mbar_wait(&bars[kBarSt], c & 1)) { tc_fail(4); break; }
-        if (c > 0 && !mbar_wait(&bars[kBarNFree], (c - 1) & 1)) { tc_fail(5); break; }
-        tc_fence_after_sync();
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t kk = (j >> 2) * kBoxQK + (j & 3) * 32;
-          umma_ss(tmem + kColN, umma_smem_desc(sb + kOffQ + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sbase + kOffSt + (j >> 2) * kBoxSt + (j & 3) * 32, 0, 1024, kSwizzle128B), idN, j > 0);
-        }
-        // N += P V
-        if (!mbar_wait(&bars[kBarP + st], (c >> 1) & 1)) { tc_fail(6); break; }
-        tc_fence_after_sync();
-        for (int j = 0; j < 8; ++j)
-          umma_ts(tmem + kColN, tmem + kColA + st * 128 + j * 8,
-                  umma_smem_desc(sb + kOffV + j * 2048, kBoxQK, 1024, kSwizzle128B), idPV, 1);
-        umma_commit(&bars[kBarN]);
-        // [S|z] += K^T [V|1]
-        const bool fresh = (c == 0 && s_in == nullptr);
-        for (int j = 0; j < 8; ++j)
-          umma_ss(tmem + kColS, umma_smem_desc(sb + kOffK + j * 2048, kBoxQK, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kOffV + j * 2048, (kOffOnes - (st * kStage + kOffV)), 1024, kSwizzle128B), idS,
-                  (fresh && j == 0) ? 0 : 1);
-        umma_commit(&bars[kBarS]);
-        umma_commit(&bars[kBarEmpty + st]);
       }
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;                 // TMEM lane quarter this warp may touch
-    const int row = quarter * 32 + lane;          // token row in the chunk / state row k
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ score group: P = mask(A), row sums
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int etid = tid - 64;                    // 0..127
-    // state entering this run of tokens -> TMEM (fp32) and its fp16 transpose -> shared memory
-    {
-      unsigned char* st_tile = sm + kOffSt;
-      if (s_in) {
-        for (int c0 = 0; c0 < 128; c0 += 16) {
-          uint32_t r[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int n = c0 + i;
-            float val = n < kD ? s_in[(size_t)row * kD + n] : (n == kD ? z_in[row] : 0.f);
-            r[i] = __float_as_uint(val);
-            if (n < 80) {
-              const __half hv = __float2half_rn(val);
-              *reinterpret_cast<__half*>(st_tile + (row >> 6) * kBoxSt + sw128_offset(n, row & 63)) = hv;
-            }
-          }
-          tmem_st16(tmem + lane_addr + kColS + c0, r);
-        }
-        tmem_st_wait();
-      } else {
-        for (int i = etid; i < (int)(2 * kBoxSt / 16); i += 128) *reinterpret_cast<uint4*>(st_tile + i * 16) = make_uint4(0, 0, 0, 0);
-      }
-      fence_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[kBarSt]);
-    }
-    bool ok = true;
-    uint32_t epi_phase = 0;
-    for (int c = 0; ok && c < nchunk; ++c) {
+    for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
-      const uint32_t colA = kColA + st * 128;
-      // ---- P = mask(A) (fp16, packed, over the first 64 columns of the A buffer) and row sums
-      if (!mbar_wait(&bars[kBarA + st], (c >> 1) & 1)) { tc_fail(7); ok = false; break; }
+      const uint32_t colA = fColA + st * 128;
+      if (!mbar_wait(&bars[fA + st], (c >> 1) & 1)) { tc_fail(7); break; }
+      // rs[st] of chunk c-2 must have been read by the output group
+      if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(8); break; }
       tc_fence_after_sync();
       float rowsum = 0.f;
 #pragma unroll
@@ -224,47 +214,77 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         tmem_st16(tmem + lane_addr + colA + piece * 16, p);
       }
+      rs[st * 128 + row] = rowsum;
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(&bars[kBarP + st]);
-      // ---- N: numerator (64 columns) and q.z_prev (column 64)
-      if (!mbar_wait(&bars[kBarN], c & 1)) { tc_fail(8); ok = false; break; }
-      tc_fence_after_sync();
-      uint32_t nn[64], nz[16];
-      tmem_ld32(tmem + lane_addr + kColN, nn);
-      tmem_ld32(tmem + lane_addr + kColN + 32, nn + 32);
-      tmem_ld16(tmem + lane_addr + kColN + 64, nz);
-      tmem_ld_wait();
+      mbar_arrive(&bars[fP + st]);
+    }
+  } else {
+    // ------------------------------------------------------------------ output / state group
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // token row in the chunk / state row k
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int ytid = tid - 192;                   // 0..127
+    unsigned char* s_tile = sm + kFwS;
+    // state entering this run of tokens -> TMEM (fp32) and the fp16 operand tile
+    {
+      uint32_t r[80];
+#pragma unroll
+      for (int n = 0; n < 64; ++n) r[n] = s_in ? __float_as_uint(s_in[(size_t)row * kD + n]) : 0u;
+      r[64] = z_in ? __float_as_uint(z_in[row]) : 0u;
+#pragma unroll
+      for (int n = 65; n < 80; ++n) r[n] = 0u;
+      store_state_row(s_tile, row, r);
+#pragma unroll
+      for (int ch = 1; ch < 8; ++ch) *reinterpret_cast<uint4*>(s_tile + kBox + row_chunk1(row, ch)) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(s_tile + kBox + row_chunk1(row, 0)) = make_uint4(pack_half2(__uint_as_float(r[64]), 0.f), 0, 0, 0);
+      if (s_in) {
+#pragma unroll
+        for (int c0 = 0; c0 < 80; c0 += 16) tmem_st16(tmem + lane_addr + fColS + c0, r + c0);
+        tmem_st_wait();
+      }
+      fence_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&bars[kBarNFree]);
-      // ---- export the updated state for the next chunk (critical path of the scan)
-      if (!mbar_wait(&bars[kBarS], c & 1)) { tc_fail(9); ok = false; break; }
+      mbar_arrive(&bars[fSt]);
+    }
+    bool ok = true;
+    uint32_t y_phase = 0;
+    for (int c = 0; ok && c < nchunk; ++c) {
+      const int st = c & 1;
+      // ---- the state after this chunk -> operand tile for the next chunk (the serial chain of the scan)
+      if (!mbar_wait(&bars[fS], c & 1)) { tc_fail(9); ok = false; break; }
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
-        unsigned char* st_col = sm + kOffSt + (row >> 6) * kBoxSt;
-#pragma unroll
-        for (int c0 = 0; c0 < 80; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem + lane_addr + kColS + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int n = c0 + i;
-            if (n <= kD)
-              *reinterpret_cast<__half*>(st_col + sw128_offset(n, row & 63)) = __float2half_rn(__uint_as_float(r[i]));
-          }
-        }
+        uint32_t r[80];
+        tmem_ld32(tmem + lane_addr + fColS, r);
+        tmem_ld32(tmem + lane_addr + fColS + 32, r + 32);
+        tmem_ld16(tmem + lane_addr + fColS + 64, r + 64);
+        tmem_ld_wait();
+        store_state_row(s_tile, row, r);
+        *reinterpret_cast<uint4*>(s_tile + kBox + row_chunk1(row, 0)) = make_uint4(pack_half2(__uint_as_float(r[64]), 0.f), 0, 0, 0);
         fence_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(&bars[kBarSt]);
+        mbar_arrive(&bars[fSt]);
       }
+      // ---- N: numerator (64 columns) and q.z_prev (column 64); row sum from the score group
+      if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(10); ok = false; break; }
+      if (!mbar_wait(&bars[fN + st], (c >> 1) & 1)) { tc_fail(11); ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t nn[64], nz[16];
+      tmem_ld32(tmem + lane_addr + fColN + st * 80, nn);
+      tmem_ld32(tmem + lane_addr + fColN + st * 80 + 32, nn + 32);
+      tmem_ld16(tmem + lane_addr + fColN + st * 80 + 64, nz);
+      const float rowsum = rs[st * 128 + row];
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[fNFree + st]);
       // ---- out = N / max(rowsum + q.z_prev, 1) -> staging tile -> TMA store
       const float inv = 1.f / fmaxf(rowsum + __uint_as_float(nz[0]), kEps);
-      if (c > 0) {
-        if (etid == 0) tma_store_wait_read<0>();
-        if (!epi_sync(&bars[kBarEpi], epi_phase)) { tc_fail(10); ok = false; break; }
+      if (c > 0) {                                 // the previous chunk's store must have drained the staging tile
+        if (ytid == 0) tma_store_wait_read<0>();
+        if (!epi_sync(&bars[fY], y_phase)) { tc_fail(13); ok = false; break; }
       }
-      unsigned char* orow = sm + kOffOut + row * 128;
+      unsigned char* orow = sm + kFwOut + row * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         uint4 val;
@@ -275,33 +295,33 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         *reinterpret_cast<uint4*>(orow + ((ch ^ (row & 7)) << 4)) = val;
       }
       fence_async_smem();
-      if (!epi_sync(&bars[kBarEpi], epi_phase)) { tc_fail(11); ok = false; break; }
-      if (etid == 0) {
-        tma_store_3d(&tm_o, sm + kOffOut, 0, bh, (int)(t_begin + (int64_t)c * kTC));
+      if (!epi_sync(&bars[fY], y_phase)) { tc_fail(12); ok = false; break; }
+      if (ytid == 0) {
+        tma_store_3d(&tm_o, sm + kFwOut, 0, bh, (int)(t_begin + (int64_t)c * kTC));
         tma_store_commit();
       }
     }
-    // ---- final state out (prefill -> decode hand-off, segment carry)
+    // ---- final state out (prefill -> decode hand-off, segment carry); the last wait on fS ordered it
     if (ok && s_out && seg == nseg - 1) {
-      if (nchunk == 0) {
-        for (int n = 0; n < kD; ++n) s_out[((size_t)bh * kK + row) * kD + n] = s_in ? s_in[(size_t)row * kD + n] : 0.f;
-        z_out[(size_t)bh * kK + row] = z_in ? z_in[row] : 0.f;
+      uint32_t r[80];
+      if (nchunk > 0) {
+        tmem_ld32(tmem + lane_addr + fColS, r);
+        tmem_ld32(tmem + lane_addr + fColS + 32, r + 32);
+        tmem_ld16(tmem + lane_addr + fColS + 64, r + 64);
+        tmem_ld_wait();
       } else {
-        // the last chunk's kBarS wait above already ordered the final state
-        for (int c0 = 0; c0 < 80; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem + lane_addr + kColS + c0, r);
-          tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int n = c0 + i;
-            if (n < kD) s_out[((size_t)bh * kK + row) * kD + n] = __uint_as_float(r[i]);
-            else if (n == kD) z_out[(size_t)bh * kK + row] = __uint_as_float(r[i]);
-          }
-        }
+        for (int n = 0; n < 64; ++n) r[n] = s_in ? __float_as_uint(s_in[(size_t)row * kD + n]) : 0u;
+        r[64] = z_in ? __float_as_uint(z_in[row]) : 0u;
       }
+      float4* dst = reinterpret_cast<float4*>(s_out + ((size_t)bh * kK + row) * kD);
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+        dst[n] = make_float4(__uint_as_float(r[4 * n]), __uint_as_float(r[4 * n + 1]), __uint_as_float(r[4 * n + 2]),
+                             __uint_as_float(r[4 * n + 3]));
+      z_out[(size_t)bh * kK + row] = __uint_as_float(r[64]);
     }
-    if (etid == 0) tma_store_wait<0>();
+    if (ytid == 0) tma_store_wait<0>();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -316,9 +336,9 @@ int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __ha
   if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tk, k, T, BH, kK, kTC) ||
       make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&to, out, T, BH, kD, kTC))
     return fail(RFA_EDEVICE, "causal_fwd: cuTensorMapEncodeTiled failed or is unavailable");
-  cudaError_t e = cudaFuncSetAttribute(causal_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem);
-  if (e != cudaSuccess) return fail((int)e, "causal_fwd: cannot reserve %u bytes of shared memory: %s", kTcSmem, cudaGetErrorString(e));
-  causal_fwd_tc_kernel<<<dim3(BH, nseg), kTcThreads, kTcSmem, st>>>(tq, tk, tv, to, s_seg, z_seg, s_out, z_out, T, BH, nseg, tseg);
+  cudaError_t e = cudaFuncSetAttribute(causal_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmem);
+  if (e != cudaSuccess) return fail((int)e, "causal_fwd: cannot reserve %u bytes of shared memory: %s", kFwSmem, cudaGetErrorString(e));
+  causal_fwd_tc_kernel<<<dim3(BH, nseg), kFwThreads, kFwSmem, st>>>(tq, tk, tv, to, s_seg, z_seg, s_out, z_out, T, BH, nseg, tseg);
   return check_launch("rfa_causal_fwd");
 }
 

@@ -41,6 +41,42 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 __device__ __forceinline__ float2 unpack_half2(uint32_t u) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
 }
+
+// byte offset of 16-byte chunk `ch` (0..15) of row r in a two-box [128][128] fp16 tile
+__device__ __forceinline__ uint32_t row_chunk2(int r, int ch) {
+  return (uint32_t)(ch >> 3) * kBox + (uint32_t)r * 128u + ((uint32_t)((ch & 7) ^ (r & 7)) << 4);
+}
+// same for a one-box [128][64] tile, ch in 0..7
+__device__ __forceinline__ uint32_t row_chunk1(int r, int ch) {
+  return (uint32_t)r * 128u + ((uint32_t)(ch ^ (r & 7)) << 4);
+}
+
+// fp32 state row (64 values in registers as bit patterns) -> fp16 row r of the swizzled state tile
+__device__ __forceinline__ void store_state_row(unsigned char* tile, int r, const uint32_t* v) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    uint4 p;
+    p.x = pack_half2(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]));
+    p.y = pack_half2(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]));
+    p.z = pack_half2(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]));
+    p.w = pack_half2(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]));
+    *reinterpret_cast<uint4*>(tile + row_chunk1(r, ch)) = p;
+  }
+}
+
+// sum over the chunk's rows s of X[s][col] * w[s]  (w == nullptr -> 1) for a two-box tile
+__device__ __forceinline__ float column_sum2(const unsigned char* tile, int col, const float* w) {
+  const unsigned char* base = tile + (col >> 6) * kBox + ((col & 7) << 1);
+  const int cc = (col & 63) >> 3;
+  float a = 0.f;
+#pragma unroll 8
+  for (int s = 0; s < 128; ++s) {
+    const float x = __half2float(*reinterpret_cast<const __half*>(base + s * 128 + ((cc ^ (s & 7)) << 4)));
+    a = w ? fmaf(x, w[s], a) : a + x;
+  }
+  return a;
+}
+
 #endif
 
 }  // namespace rfa
