@@ -98,12 +98,14 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      RFA_TRACE_DECL(0)
       for (int c = 0; c < nchunk; ++c) {
         const int st = c & 1;
         if (c >= 2 && !mbar_wait(&bars[fEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
         unsigned char* base = sm + st * kFwStage;
         const int t0 = (int)(t_begin + (int64_t)c * kTC);
         uint64_t* fb = &bars[fFull + st];
+        RFA_TRACE_EV(1, c);
         mbar_arrive_expect_tx(fb, 4 * kBox);
         tma_load_3d(base + kFwQ, &tm_q, fb, 0, bh, t0);
         tma_load_3d(base + kFwQ + kBox, &tm_q, fb, 64, bh, t0);
@@ -117,6 +119,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      RFA_TRACE_DECL(1)
       constexpr uint32_t idA = umma_idesc_f16(128, 128, false, false);   // Q K^T
       constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);    // Q [S|z]   (B MN-major)
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V       (B MN-major)
@@ -139,9 +142,11 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int st = c & 1;
         const uint32_t sb = sbase + st * kFwStage;
         // the state before this chunk is in the operand tile, and the output group has let go of S
+        RFA_TRACE_EV(10, c);
         if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); break; }
         if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); break; }
         tc_fence_after_sync();
+        RFA_TRACE_EV(11, c);
         for (int j = 0; j < 8; ++j) {            // N = Q [S|z]_prev
           const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
           umma_ss(tmem + fColN + st * 80, umma_smem_desc(sb + kFwQ + kk, 0, 1024, kSwizzle128B),
@@ -155,6 +160,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                   umma_smem_desc(sb + kFwV + j * 2048, kFwOnes - (st * kFwStage + kFwV), 1024, kSwizzle128B), idS,
                   (fresh && j == 0) ? 0 : 1);
         umma_commit(&bars[fS]);
+        RFA_TRACE_EV(12, c);
         umma_commit(&bars[fEmpty + st]);         // Q and K of this stage have been read for the last time
         // next chunk's scores as early as its Q, K are there, so the score group never starves --
         // but never hold back this chunk's P V (and with it the release of V) for a load in flight
@@ -164,7 +170,9 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           issue_A(c + 1);
           next_issued = true;
         }
+        RFA_TRACE_EV(13, c);
         if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); break; }
+        RFA_TRACE_EV(14, c);
         tc_fence_after_sync();
         for (int j = 0; j < 8; ++j)              // N += P V
           umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8,
@@ -183,10 +191,13 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    RFA_TRACE_DECL(2)
     for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t colA = fColA + st * 128;
+      if (lane == 0 && warp == 5) RFA_TRACE_EV(20, c);
       if (!mbar_wait(&bars[fA + st], (c >> 1) & 1)) { tc_fail(7); break; }
+      if (lane == 0 && warp == 5) RFA_TRACE_EV(21, c);
       // rs[st] of chunk c-2 must have been read by the output group
       if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(8); break; }
       tc_fence_after_sync();
@@ -218,6 +229,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[fP + st]);
+      if (lane == 0 && warp == 5) RFA_TRACE_EV(22, c);
     }
   } else {
     // ------------------------------------------------------------------ output / state group
@@ -249,10 +261,13 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     bool ok = true;
     uint32_t y_phase = 0;
+    RFA_TRACE_DECL(3)
     for (int c = 0; ok && c < nchunk; ++c) {
       const int st = c & 1;
       // ---- the state after this chunk -> operand tile for the next chunk (the serial chain of the scan)
+      if (ytid == 0) RFA_TRACE_EV(30, c);
       if (!mbar_wait(&bars[fS], c & 1)) { tc_fail(9); ok = false; break; }
+      if (ytid == 0) RFA_TRACE_EV(31, c);
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
         uint32_t r[80];
@@ -267,9 +282,11 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive(&bars[fSt]);
       }
       // ---- N: numerator (64 columns) and q.z_prev (column 64); row sum from the score group
+      if (ytid == 0) RFA_TRACE_EV(32, c);
       if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(10); ok = false; break; }
       if (!mbar_wait(&bars[fN + st], (c >> 1) & 1)) { tc_fail(11); ok = false; break; }
       tc_fence_after_sync();
+      if (ytid == 0) RFA_TRACE_EV(33, c);
       uint32_t nn[64], nz[16];
       tmem_ld32(tmem + lane_addr + fColN + st * 80, nn);
       tmem_ld32(tmem + lane_addr + fColN + st * 80 + 32, nn + 32);
@@ -299,6 +316,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (ytid == 0) {
         tma_store_3d(&tm_o, sm + kFwOut, 0, bh, (int)(t_begin + (int64_t)c * kTC));
         tma_store_commit();
+        RFA_TRACE_EV(34, c);
       }
     }
     // ---- final state out (prefill -> decode hand-off, segment carry); the last wait on fS ordered it
@@ -343,5 +361,15 @@ int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __ha
 }
 
 int tc_status_causal_fwd() { return tc_status_read_clear(); }
+
+#ifdef RFA_TRACE
+extern "C" int rfa_trace_dump(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+  static unsigned long long zeros[4 * 1024 * 2];
+  cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
+  return 4 * 1024;
+}
+#endif
 
 }  // namespace rfa

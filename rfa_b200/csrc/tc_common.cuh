@@ -26,6 +26,27 @@ static int tc_status_read_clear() {
 }
 
 #ifdef __CUDACC__
+// Optional event trace of CTA (0,0) for tuning (compile with -DRFA_TRACE): each record is
+// (event id, chunk, globaltimer ns).  Not part of normal builds.
+#ifdef RFA_TRACE
+// four roles x 1024 records, store-only (no atomics, nothing waits on the stores)
+static __device__ unsigned long long g_trace[4 * 1024 * 2];
+__device__ __forceinline__ void trace_ev(int role, int& n, int id, int chunk) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && n < 1024) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_trace[(role * 1024 + n) * 2] = ((unsigned long long)id << 32) | (unsigned int)chunk;
+    g_trace[(role * 1024 + n) * 2 + 1] = t;
+    ++n;
+  }
+}
+#define RFA_TRACE_DECL(role) const int trace_role_ = (role); int trace_n_ = 0;
+#define RFA_TRACE_EV(id, chunk) trace_ev(trace_role_, trace_n_, (id), (chunk))
+#else
+#define RFA_TRACE_DECL(role)
+#define RFA_TRACE_EV(id, chunk) ((void)0)
+#endif
+
 // Barrier among the 128 epilogue threads built on an mbarrier so that it, too, is bounded.
 __device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase) {
   mbar_arrive(bar);
