@@ -25,6 +25,7 @@ int check_launch(const char* what) {
 
 int tc_status_causal_fwd();
 int tc_status_causal_bwd();
+int tc_status_causal_bwd_kv();
 
 }  // namespace rfa
 
@@ -36,6 +37,7 @@ extern "C" int rfa_debug_status(void) {
   const int f = rfa::tc_status_causal_fwd(), b = rfa::tc_status_causal_bwd();
   if (f) return f < 0 ? f : 100 + f;
   if (b) return b < 0 ? b : 200 + b;
+  if (const int kv = rfa::tc_status_causal_bwd_kv()) return kv < 0 ? kv : 300 + kv;
   return 0;
 }
 

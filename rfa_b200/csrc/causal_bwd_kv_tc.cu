@@ -1,0 +1,374 @@
+// Causal RFA backward, sweep 2 (reverse in time) on tcgen05 tensor cores: grad_k, grad_v
+// (upstream cuda/backward.cu:373-451, kv_backward; math in rfa.py:96-101), chunks of 128 tokens.
+//
+// Per chunk, with gs = g/den and gz from sweep 1 (workspace), dS/dz the reverse running state:
+//     At  = K Q^T        -> Pt  = At[s][t]  for t >= s            fp16, kept in TMEM
+//     dAt = V gs^T       -> (dAt + gz_t)[s][t] for t >= s         fp16, kept in TMEM
+//     dV  = Pt gs + K dS                                  -> grad_v
+//     dK  = dAt Q + V dS^T + dz^T                         -> grad_k
+//     dS += Q^T gs,   dz += Q^T gz
+// The score matrices are computed TRANSPOSED (keys on the TMEM lanes) so that their fp16
+// versions can stay in tensor memory as the A operands of the dK / dV products.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 score group
+// (scales g in place, packs Pt and dAt), warps 6..9 output/state group (grad_k, grad_v,
+// state export, dz).  The score group of chunk i+1 overlaps the output group of chunk i.
+// All waits are bounded.
+#include "tc_common.cuh"
+
+namespace rfa {
+
+constexpr int kKvThreads = 320;
+
+constexpr uint32_t kvQ = 0, kvK = 2 * kBox, kvV = 4 * kBox, kvG = 5 * kBox, kvStage = 6 * kBox;   // 98304 per stage
+constexpr uint32_t kvS = 2 * kvStage;            // dS as an operand: [128 k][64 n] fp16, swizzled
+constexpr uint32_t kvDz = kvS + kBox;            // fp32 [128]
+constexpr uint32_t kvGz = kvDz + 512;            // fp32 [2][128]: gz of the chunk's query rows
+constexpr uint32_t kvBar = kvGz + 1024;
+constexpr uint32_t kvSmem = kvBar + 256 + 1024;
+
+constexpr uint32_t kvColAt = 0, kvColDAt = 128, kvColDK = 256, kvColDV = 384, kvColDS = 448;
+enum { vFull = 0, vEmpty = 2, vAt = 4, vG = 5, vDAt = 7, vP = 8, vDA16 = 9, vDK = 10, vDV = 11, vDKFree = 12, vDVFree = 13,
+       vS = 14, vSt = 15, vY = 16, vNum = 17 };
+// vG is one barrier per stage: the output group waits on it late in a chunk, when the score group may already
+// have completed the next chunk's phase; with one barrier per stage a waiter is never two phases behind.
+
+__global__ void __launch_bounds__(kKvThreads, 1)
+causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
+                        const __grid_constant__ CUtensorMap tm_gk, const __grid_constant__ CUtensorMap tm_gv,
+                        const float* __restrict__ ws_den, const float* __restrict__ ws_gz,
+                        const float* __restrict__ ds_seg, const float* __restrict__ dz_seg,
+                        int64_t T, int BH, int nseg, int64_t tseg) {
+  extern __shared__ unsigned char kv_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(kv_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kvBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + vNum);
+  float* dzs = reinterpret_cast<float*>(sm + kvDz);
+  float* gz_buf = reinterpret_cast<float*>(sm + kvGz);
+  const uint32_t sbase = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x, seg = blockIdx.y;
+  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
+  const int nchunk = (int)((t_end - t_begin + kTC - 1) / kTC);
+  const size_t slot = (size_t)bh * nseg + seg;
+  const float* ds_in = ds_seg ? ds_seg + slot * kK * kD : nullptr;
+  const float* dz_in = dz_seg ? dz_seg + slot * kK : nullptr;
+
+  if (tid == 0) {
+    mbar_init(&bars[vFull], 1); mbar_init(&bars[vFull + 1], 1);
+    mbar_init(&bars[vEmpty], 128); mbar_init(&bars[vEmpty + 1], 128);
+    mbar_init(&bars[vAt], 1); mbar_init(&bars[vG], 128); mbar_init(&bars[vG + 1], 128); mbar_init(&bars[vDAt], 1); mbar_init(&bars[vP], 128);
+    mbar_init(&bars[vDA16], 128); mbar_init(&bars[vDK], 1); mbar_init(&bars[vDV], 1);
+    mbar_init(&bars[vDKFree], 128); mbar_init(&bars[vDVFree], 128); mbar_init(&bars[vS], 1);
+    mbar_init(&bars[vSt], 128); mbar_init(&bars[vY], 128);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
+    tma_prefetch_desc(&tm_gk); tma_prefetch_desc(&tm_gv);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
+    if (lane == 0) {
+      for (int i = 0; i < nchunk; ++i) {
+        const int st = i & 1;
+        if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
+        unsigned char* base = sm + st * kvStage;
+        const int t0 = (int)(t_begin + (int64_t)(nchunk - 1 - i) * kTC);
+        uint64_t* fb = &bars[vFull + st];
+        mbar_arrive_expect_tx(fb, kvStage);
+        tma_load_3d(base + kvG, &tm_g, fb, 0, bh, t0);
+        tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
+        tma_load_3d(base + kvK + kBox, &tm_k, fb, 64, bh, t0);
+        tma_load_3d(base + kvQ, &tm_q, fb, 0, bh, t0);
+        tma_load_3d(base + kvQ + kBox, &tm_q, fb, 64, bh, t0);
+        tma_load_3d(base + kvV, &tm_v, fb, 0, bh, t0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // K Q^T ; V gs^T ; V dS^T
+      constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dAt Q            (B MN-major)
+      constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // Pt gs ; K dS     (B MN-major)
+      constexpr uint32_t idMM64 = umma_idesc_f16(128, 64, true, true);    // Q^T gs           (A, B MN-major)
+      const uint32_t sS = sbase + kvS;
+      auto issue_At = [&](int i) {                                        // At = K Q^T
+        const uint32_t sb = sbase + (i & 1) * kvStage;
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
+          umma_ss(tmem + kvColAt, umma_smem_desc(sb + kvK + kk, 0, 1024, kSwizzle128B),
+                  umma_smem_desc(sb + kvQ + kk, 0, 1024, kSwizzle128B), idKK, j > 0);
+        }
+        umma_commit(&bars[vAt]);
+      };
+      bool ok = true;
+      if (nchunk > 0) {
+        ok = mbar_wait(&bars[vFull], 0);
+        if (ok) { tc_fence_after_sync(); issue_At(0); } else tc_fail(2);
+      }
+      for (int i = 0; ok && i < nchunk; ++i) {
+        const int st = i & 1;
+        const uint32_t sb = sbase + st * kvStage;
+        const uint32_t ph = i & 1;
+        if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(3); break; }
+        tc_fence_after_sync();
+        for (int j = 0; j < 4; ++j)              // dAt = V gs^T
+          umma_ss(tmem + kvColDAt, umma_smem_desc(sb + kvV + j * 32, 0, 1024, kSwizzle128B),
+                  umma_smem_desc(sb + kvG + j * 32, 0, 1024, kSwizzle128B), idKK, j > 0);
+        umma_commit(&bars[vDAt]);
+        if (!mbar_wait(&bars[vP], ph)) { tc_fail(4); break; }
+        if (!mbar_wait(&bars[vSt], ph)) { tc_fail(5); break; }
+        if (i > 0 && !mbar_wait(&bars[vDVFree], (i - 1) & 1)) { tc_fail(6); break; }
+        tc_fence_after_sync();
+        for (int j = 0; j < 8; ++j)              // dV = Pt gs
+          umma_ts(tmem + kvColDV, tmem + kvColAt + j * 8, umma_smem_desc(sb + kvG + j * 2048, kBox, 1024, kSwizzle128B), idKM64, j > 0);
+        for (int j = 0; j < 8; ++j) {            // dV += K dS_next     (dS tile as [K = k rows][N = n])
+          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
+          umma_ss(tmem + kvColDV, umma_smem_desc(sb + kvK + kk, 0, 1024, kSwizzle128B),
+                  umma_smem_desc(sS + j * 2048, kBox, 1024, kSwizzle128B), idKM64, 1);
+        }
+        umma_commit(&bars[vDV]);
+        // the next chunk's scores as soon as its tiles are in (Pt of this chunk has been consumed above)
+        bool next_issued = (i + 1 >= nchunk);
+        if (!next_issued && mbar_try_wait(&bars[vFull + ((i + 1) & 1)], ((i + 1) >> 1) & 1)) {
+          tc_fence_after_sync();
+          issue_At(i + 1);
+          next_issued = true;
+        }
+        if (!mbar_wait(&bars[vDA16], ph)) { tc_fail(7); break; }
+        if (i > 0 && !mbar_wait(&bars[vDKFree], (i - 1) & 1)) { tc_fail(8); break; }
+        tc_fence_after_sync();
+        for (int j = 0; j < 8; ++j)              // dK = dAt Q
+          umma_ts(tmem + kvColDK, tmem + kvColDAt + j * 8, umma_smem_desc(sb + kvQ + j * 2048, kBox, 1024, kSwizzle128B), idKM128, j > 0);
+        for (int j = 0; j < 4; ++j)              // dK += V dS_next^T   (dS tile as [N = k rows][K = n])
+          umma_ss(tmem + kvColDK, umma_smem_desc(sb + kvV + j * 32, 0, 1024, kSwizzle128B),
+                  umma_smem_desc(sS + j * 32, 0, 1024, kSwizzle128B), idKK, 1);
+        umma_commit(&bars[vDK]);
+        const bool fresh = (i == 0 && ds_in == nullptr);
+        for (int j = 0; j < 8; ++j)              // dS += Q^T gs
+          umma_ss(tmem + kvColDS, umma_smem_desc(sb + kvQ + j * 2048, kBox, 1024, kSwizzle128B),
+                  umma_smem_desc(sb + kvG + j * 2048, kBox, 1024, kSwizzle128B), idMM64, (fresh && j == 0) ? 0 : 1);
+        umma_commit(&bars[vS]);
+        if (!next_issued) {
+          if (!mbar_wait(&bars[vFull + ((i + 1) & 1)], ((i + 1) >> 1) & 1)) { tc_fail(9); break; }
+          tc_fence_after_sync();
+          issue_At(i + 1);
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ score group
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // query row t (scaling g) / key row s (packing)
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    for (int i = 0; i < nchunk; ++i) {
+      const int st = i & 1;
+      const uint32_t ph = i & 1;
+      unsigned char* stage = sm + st * kvStage;
+      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
+      float* gzs = gz_buf + (i & 1) * 128;
+      // ---- gs = g / den over the staged g tile; gz of this thread's query row
+      float inv = 1.f, gz = 0.f;
+      if (t0 + row < t_end) {
+        inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
+        gz = ws_gz[(size_t)bh * T + t0 + row];
+      }
+      if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
+      {
+        unsigned char* grow = stage + kvG;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
+          uint4 u = *p;
+          float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
+          u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
+          u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
+          *p = u;
+        }
+        gzs[row] = gz;
+      }
+      fence_async_smem();
+      mbar_arrive(&bars[vG + st]);
+      // ---- Pt[s][t] = At[s][t] for t >= s  (fp16 over the first 64 columns)
+      if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        uint32_t p[16];
+        if (piece >= quarter) {
+          uint32_t a[32];
+          tmem_ld32(tmem + lane_addr + kvColAt + piece * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float x0 = __uint_as_float(a[e]), x1 = __uint_as_float(a[e + 1]);
+            if (piece == quarter) {
+              if (e < lane) x0 = 0.f;
+              if (e + 1 < lane) x1 = 0.f;
+            }
+            p[e >> 1] = pack_half2(x0, x1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) p[e] = 0u;
+        }
+        tmem_st16(tmem + lane_addr + kvColAt + piece * 16, p);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[vP]);
+      // ---- dAt[s][t] = (v_s . gs_t + gz_t) for t >= s; gz of all rows is there once vG completed
+      if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(12); break; }
+      if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        uint32_t p[16];
+        if (piece >= quarter) {
+          uint32_t a[32];
+          tmem_ld32(tmem + lane_addr + kvColDAt + piece * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float4 gz4 = *reinterpret_cast<const float4*>(gzs + piece * 32 + e);
+            float x0 = __uint_as_float(a[e]) + gz4.x, x1 = __uint_as_float(a[e + 1]) + gz4.y;
+            float x2 = __uint_as_float(a[e + 2]) + gz4.z, x3 = __uint_as_float(a[e + 3]) + gz4.w;
+            if (piece == quarter) {
+              if (e < lane) x0 = 0.f;
+              if (e + 1 < lane) x1 = 0.f;
+              if (e + 2 < lane) x2 = 0.f;
+              if (e + 3 < lane) x3 = 0.f;
+            }
+            p[e >> 1] = pack_half2(x0, x1);
+            p[(e >> 1) + 1] = pack_half2(x2, x3);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) p[e] = 0u;
+        }
+        tmem_st16(tmem + lane_addr + kvColDAt + piece * 16, p);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[vDA16]);
+    }
+  } else {
+    // ------------------------------------------------------------------ output / state group
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // key row s of the chunk / state row k
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int ytid = tid - 192;
+    unsigned char* s_tile = sm + kvS;
+    {
+      uint32_t r[64];
+#pragma unroll
+      for (int n = 0; n < 64; ++n) r[n] = ds_in ? __float_as_uint(ds_in[(size_t)row * kD + n]) : 0u;
+      store_state_row(s_tile, row, r);
+      if (ds_in) {
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + kvColDS + c0, r + c0);
+        tmem_st_wait();
+      }
+      dzs[row] = dz_in ? dz_in[row] : 0.f;
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[vSt]);
+    }
+    bool ok = true;
+    uint32_t y_phase = 0;
+    for (int i = 0; ok && i < nchunk; ++i) {
+      const int st = i & 1;
+      const uint32_t ph = i & 1;
+      unsigned char* stage = sm + st * kvStage;
+      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
+      const float* gzs = gz_buf + (i & 1) * 128;
+      // dzs of the previous chunk is final for every thread
+      if (!epi_sync(&bars[vY], y_phase)) { tc_fail(14); ok = false; break; }
+      // ---- all MMAs of this chunk are complete once the state MMA is: K and V tiles become staging
+      if (!mbar_wait(&bars[vS], ph)) { tc_fail(15); ok = false; break; }
+      tc_fence_after_sync();
+      // ---- reverse state after this chunk -> fp16 operand tile (the serial chain of the scan)
+      if (i + 1 < nchunk) {
+        uint32_t r[64];
+        tmem_ld32(tmem + lane_addr + kvColDS, r);
+        tmem_ld32(tmem + lane_addr + kvColDS + 32, r + 32);
+        tmem_ld_wait();
+        store_state_row(s_tile, row, r);
+        fence_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[vSt]);
+      }
+      // ---- grad_v -> V tile
+      {
+        uint32_t r[64];
+        tmem_ld32(tmem + lane_addr + kvColDV, r);
+        tmem_ld32(tmem + lane_addr + kvColDV + 32, r + 32);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[vDVFree]);
+        store_state_row(stage + kvV, row, r);
+      }
+      // ---- grad_k = dK + dz_next -> K tile
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        uint32_t a[32];
+        tmem_ld32(tmem + lane_addr + kvColDK + piece * 32, a);
+        tmem_ld_wait();
+        if (piece == 3) { tc_fence_before_sync(); mbar_arrive(&bars[vDKFree]); }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k0 = piece * 32 + j * 8;
+          const float4 z0 = *reinterpret_cast<const float4*>(dzs + k0), z1 = *reinterpret_cast<const float4*>(dzs + k0 + 4);
+          uint4 u;
+          u.x = pack_half2(__uint_as_float(a[j * 8 + 0]) + z0.x, __uint_as_float(a[j * 8 + 1]) + z0.y);
+          u.y = pack_half2(__uint_as_float(a[j * 8 + 2]) + z0.z, __uint_as_float(a[j * 8 + 3]) + z0.w);
+          u.z = pack_half2(__uint_as_float(a[j * 8 + 4]) + z1.x, __uint_as_float(a[j * 8 + 5]) + z1.y);
+          u.w = pack_half2(__uint_as_float(a[j * 8 + 6]) + z1.z, __uint_as_float(a[j * 8 + 7]) + z1.w);
+          *reinterpret_cast<uint4*>(stage + kvK + row_chunk2(row, piece * 4 + j)) = u;
+        }
+      }
+      fence_async_smem();
+      if (!epi_sync(&bars[vY], y_phase)) { tc_fail(16); ok = false; break; }   // staging complete; dzs reads done
+      if (ytid == 0) {
+        tma_store_3d(&tm_gk, stage + kvK, 0, bh, (int)t0);
+        tma_store_3d(&tm_gk, stage + kvK + kBox, 64, bh, (int)t0);
+        tma_store_3d(&tm_gv, stage + kvV, 0, bh, (int)t0);
+        tma_store_commit();
+      }
+      // ---- dz += Q^T gz   (vG completed long ago; waiting on it here orders this thread after the writes of gz)
+      if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
+      dzs[row] += column_sum2(stage + kvQ, row, gzs);
+      if (ytid == 0) tma_store_wait_read<0>();
+      mbar_arrive(&bars[vEmpty + st]);
+    }
+    if (ytid == 0) tma_store_wait<0>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gk, __half* gv,
+                            const float* ws_den, const float* ws_gz, const float* ds_seg, const float* dz_seg,
+                            int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st) {
+  CUtensorMap tq, tk, tv, tg, tgk, tgv;
+  if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tk, k, T, BH, kK, kTC) ||
+      make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&tg, g, T, BH, kD, kTC) ||
+      make_tmap_rows(&tgk, gk, T, BH, kK, kTC) || make_tmap_rows(&tgv, gv, T, BH, kD, kTC))
+    return fail(RFA_EDEVICE, "causal_bwd_kv: cuTensorMapEncodeTiled failed or is unavailable");
+  cudaError_t e = cudaFuncSetAttribute(causal_bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kvSmem);
+  if (e != cudaSuccess) return fail((int)e, "causal_bwd_kv: cannot reserve %u bytes of shared memory: %s", kvSmem, cudaGetErrorString(e));
+  causal_bwd_kv_tc_kernel<<<dim3(BH, nseg), kKvThreads, kvSmem, st>>>(tq, tk, tv, tg, tgk, tgv, ws_den, ws_gz, ds_seg, dz_seg,
+                                                                     T, BH, nseg, tseg);
+  return check_launch("rfa_causal_bwd_kv");
+}
+
+int tc_status_causal_bwd_kv() { return tc_status_read_clear(); }
+
+}  // namespace rfa

@@ -381,306 +381,6 @@ int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, co
 }
 
 
-// ===========================================================================
-// sweep 2
-// ===========================================================================
-constexpr uint32_t k2ColAt = 0, k2ColDAt = 128, k2ColDK = 256, k2ColDV = 384, k2ColDS = 448;
-enum { cFull = 0, cEmpty = 2, cAt = 4, cG = 5, cDAt = 6, cP = 7, cDA16 = 8, cDK = 9, cDV = 10, cS = 11, cSt = 12, cEpi = 13, cNum = 14 };
-
-__global__ void __launch_bounds__(kBwThreads, 1)
-causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
-                        const __grid_constant__ CUtensorMap tm_gk, const __grid_constant__ CUtensorMap tm_gv,
-                        const float* __restrict__ ws_den, const float* __restrict__ ws_gz,
-                        const float* __restrict__ ds_seg, const float* __restrict__ dz_seg,
-                        int64_t T, int BH, int nseg, int64_t tseg) {
-  extern __shared__ unsigned char bw_raw[];
-  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(bw_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBwBar);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cNum);
-  float* dzs = reinterpret_cast<float*>(sm + kBwZ);
-  float* gz_buf = reinterpret_cast<float*>(sm + kBwGz);
-  const uint32_t sbase = smem_u32(sm);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.x, seg = blockIdx.y;
-  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
-  const int nchunk = (int)((t_end - t_begin + kTC - 1) / kTC);
-  const size_t slot = (size_t)bh * nseg + seg;
-  const float* ds_in = ds_seg ? ds_seg + slot * kK * kD : nullptr;
-  const float* dz_in = dz_seg ? dz_seg + slot * kK : nullptr;
-
-  if (tid == 0) {
-    mbar_init(&bars[cFull], 1); mbar_init(&bars[cFull + 1], 1);
-    mbar_init(&bars[cEmpty], 129); mbar_init(&bars[cEmpty + 1], 129);
-    mbar_init(&bars[cAt], 1); mbar_init(&bars[cG], 128); mbar_init(&bars[cDAt], 1); mbar_init(&bars[cP], 128);
-    mbar_init(&bars[cDA16], 128); mbar_init(&bars[cDK], 1); mbar_init(&bars[cDV], 1); mbar_init(&bars[cS], 1);
-    mbar_init(&bars[cSt], 128); mbar_init(&bars[cEpi], 128);
-    mbar_fence_init();
-    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
-    tma_prefetch_desc(&tm_gk); tma_prefetch_desc(&tm_gv);
-  }
-  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int i = 0; i < nchunk; ++i) {            // chunks in reverse time order
-        const int st = i & 1;
-        if (i >= 2 && !mbar_wait(&bars[cEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(21); break; }
-        unsigned char* base = sm + st * kBwStage;
-        const int t0 = (int)(t_begin + (int64_t)(nchunk - 1 - i) * kTC);
-        uint64_t* fb = &bars[cFull + st];
-        mbar_arrive_expect_tx(fb, kBwStage);
-        tma_load_3d(base + kBwQ, &tm_q, fb, 0, bh, t0);
-        tma_load_3d(base + kBwQ + kBox, &tm_q, fb, 64, bh, t0);
-        tma_load_3d(base + kBwK, &tm_k, fb, 0, bh, t0);
-        tma_load_3d(base + kBwK + kBox, &tm_k, fb, 64, bh, t0);
-        tma_load_3d(base + kBwV, &tm_v, fb, 0, bh, t0);
-        tma_load_3d(base + kBwG, &tm_g, fb, 0, bh, t0);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // K Q^T ; V gs^T ; V dS^T
-      constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dAt Q            (B MN-major)
-      constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // Pt gs ; K dS     (B MN-major)
-      constexpr uint32_t idMM64 = umma_idesc_f16(128, 64, true, true);    // Q^T gs           (A, B MN-major)
-      const uint32_t sS = sbase + kBwS;
-      for (int i = 0; i < nchunk; ++i) {
-        const int st = i & 1;
-        const uint32_t sb = sbase + st * kBwStage;
-        const uint32_t ph = i & 1;
-        if (!mbar_wait(&bars[cFull + st], (i >> 1) & 1)) { tc_fail(22); break; }
-        tc_fence_after_sync();
-        for (int j = 0; j < 8; ++j) {            // At = K Q^T
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + k2ColAt, umma_smem_desc(sb + kBwK + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kBwQ + kk, 0, 1024, kSwizzle128B), idKK, j > 0);
-        }
-        umma_commit(&bars[cAt]);
-        if (!mbar_wait(&bars[cG], ph)) { tc_fail(23); break; }
-        tc_fence_after_sync();
-        for (int j = 0; j < 4; ++j)              // dAt = V gs^T
-          umma_ss(tmem + k2ColDAt, umma_smem_desc(sb + kBwV + j * 32, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kBwG + j * 32, 0, 1024, kSwizzle128B), idKK, j > 0);
-        umma_commit(&bars[cDAt]);
-        if (!mbar_wait(&bars[cP], ph)) { tc_fail(24); break; }
-        if (!mbar_wait(&bars[cDA16], ph)) { tc_fail(25); break; }
-        if (!mbar_wait(&bars[cSt], ph)) { tc_fail(26); break; }
-        tc_fence_after_sync();
-        for (int j = 0; j < 8; ++j)              // dK = dAt Q
-          umma_ts(tmem + k2ColDK, tmem + k2ColDAt + j * 8, umma_smem_desc(sb + kBwQ + j * 2048, kBox, 1024, kSwizzle128B), idKM128, j > 0);
-        for (int j = 0; j < 4; ++j)              // dK += V dS_next^T   (dS tile as [N = k rows][K = n])
-          umma_ss(tmem + k2ColDK, umma_smem_desc(sb + kBwV + j * 32, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sS + j * 32, 0, 1024, kSwizzle128B), idKK, 1);
-        umma_commit(&bars[cDK]);
-        for (int j = 0; j < 8; ++j)              // dV = Pt gs
-          umma_ts(tmem + k2ColDV, tmem + k2ColAt + j * 8, umma_smem_desc(sb + kBwG + j * 2048, kBox, 1024, kSwizzle128B), idKM64, j > 0);
-        for (int j = 0; j < 8; ++j) {            // dV += K dS_next     (dS tile as [K = k rows][N = n])
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + k2ColDV, umma_smem_desc(sb + kBwK + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sS + j * 2048, kBox, 1024, kSwizzle128B), idKM64, 1);
-        }
-        umma_commit(&bars[cDV]);
-        const bool fresh = (i == 0 && ds_in == nullptr);
-        for (int j = 0; j < 8; ++j)              // dS += Q^T gs
-          umma_ss(tmem + k2ColDS, umma_smem_desc(sb + kBwQ + j * 2048, kBox, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kBwG + j * 2048, kBox, 1024, kSwizzle128B), idMM64, (fresh && j == 0) ? 0 : 1);
-        umma_commit(&bars[cS]);
-        umma_commit(&bars[cEmpty + st]);
-      }
-    }
-  } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;           // key row s of the chunk / state row k
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int etid = tid - 64;
-    unsigned char* s_tile = sm + kBwS;
-    {
-      uint32_t r[64];
-#pragma unroll
-      for (int n = 0; n < 64; ++n) r[n] = ds_in ? __float_as_uint(ds_in[(size_t)row * kD + n]) : 0u;
-      store_state_row(s_tile, row, r);
-      if (ds_in) {
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + k2ColDS + c0, r + c0);
-        tmem_st_wait();
-      }
-      dzs[row] = dz_in ? dz_in[row] : 0.f;
-      fence_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[cSt]);
-    }
-    bool ok = true;
-    uint32_t epi_phase = 0;
-    for (int i = 0; ok && i < nchunk; ++i) {
-      const int st = i & 1;
-      const uint32_t ph = i & 1;
-      unsigned char* stage = sm + st * kBwStage;
-      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
-      float* gzs = gz_buf + (i & 1) * 128;       // a slow thread may still read the previous chunk's values
-      if (!mbar_wait(&bars[cFull + st], (i >> 1) & 1)) { tc_fail(27); ok = false; break; }
-      // ---- gs = g / den over the staged g tile; gz of this thread's query row
-      {
-        float inv = 1.f, gz = 0.f;
-        if (t0 + row < t_end) {
-          inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
-          gz = ws_gz[(size_t)bh * T + t0 + row];
-        }
-        unsigned char* grow = stage + kBwG;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
-          uint4 u = *p;
-          float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
-          u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
-          u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
-          *p = u;
-        }
-        gzs[row] = gz;
-      }
-      fence_async_smem();
-      mbar_arrive(&bars[cG]);
-      if (!epi_sync(&bars[cEpi], epi_phase)) { tc_fail(28); ok = false; break; }   // gzs complete; dzs of the previous chunk final
-      // ---- Pt[s][t] = At[s][t] for t >= s  (fp16 over the first 64 columns)
-      if (!mbar_wait(&bars[cAt], ph)) { tc_fail(29); ok = false; break; }
-      tc_fence_after_sync();
-#pragma unroll
-      for (int piece = 0; piece < 4; ++piece) {
-        uint32_t p[16];
-        if (piece >= quarter) {
-          uint32_t a[32];
-          tmem_ld32(tmem + lane_addr + k2ColAt + piece * 32, a);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float x0 = __uint_as_float(a[e]), x1 = __uint_as_float(a[e + 1]);
-            if (piece == quarter) {
-              if (e < lane) x0 = 0.f;
-              if (e + 1 < lane) x1 = 0.f;
-            }
-            p[e >> 1] = pack_half2(x0, x1);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) p[e] = 0u;
-        }
-        tmem_st16(tmem + lane_addr + k2ColAt + piece * 16, p);
-      }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[cP]);
-      // ---- dAt[s][t] = (v_s . gs_t + gz_t) for t >= s
-      if (!mbar_wait(&bars[cDAt], ph)) { tc_fail(30); ok = false; break; }
-      tc_fence_after_sync();
-#pragma unroll
-      for (int piece = 0; piece < 4; ++piece) {
-        uint32_t p[16];
-        if (piece >= quarter) {
-          uint32_t a[32];
-          tmem_ld32(tmem + lane_addr + k2ColDAt + piece * 32, a);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            const float4 gz4 = *reinterpret_cast<const float4*>(gzs + piece * 32 + e);
-            float x0 = __uint_as_float(a[e]) + gz4.x, x1 = __uint_as_float(a[e + 1]) + gz4.y;
-            float x2 = __uint_as_float(a[e + 2]) + gz4.z, x3 = __uint_as_float(a[e + 3]) + gz4.w;
-            if (piece == quarter) {
-              if (e < lane) x0 = 0.f;
-              if (e + 1 < lane) x1 = 0.f;
-              if (e + 2 < lane) x2 = 0.f;
-              if (e + 3 < lane) x3 = 0.f;
-            }
-            p[e >> 1] = pack_half2(x0, x1);
-            p[(e >> 1) + 1] = pack_half2(x2, x3);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) p[e] = 0u;
-        }
-        tmem_st16(tmem + lane_addr + k2ColDAt + piece * 16, p);
-      }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[cDA16]);
-      // ---- reverse state after this chunk -> fp16 operand tile (critical path of the scan)
-      if (!mbar_wait(&bars[cS], ph)) { tc_fail(31); ok = false; break; }
-      tc_fence_after_sync();
-      // all MMAs of this chunk are complete: K and V tiles may now be reused as staging
-      // ---- grad_v -> V tile
-      {
-        uint32_t r[64];
-        tmem_ld32(tmem + lane_addr + k2ColDV, r);
-        tmem_ld32(tmem + lane_addr + k2ColDV + 32, r + 32);
-        tmem_ld_wait();
-        store_state_row(stage + kBwV, row, r);
-      }
-      // ---- grad_k = dK + dz_next -> K tile
-#pragma unroll
-      for (int piece = 0; piece < 4; ++piece) {
-        uint32_t a[32];
-        tmem_ld32(tmem + lane_addr + k2ColDK + piece * 32, a);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int k0 = piece * 32 + j * 8;
-          const float4 z0 = *reinterpret_cast<const float4*>(dzs + k0), z1 = *reinterpret_cast<const float4*>(dzs + k0 + 4);
-          uint4 u;
-          u.x = pack_half2(__uint_as_float(a[j * 8 + 0]) + z0.x, __uint_as_float(a[j * 8 + 1]) + z0.y);
-          u.y = pack_half2(__uint_as_float(a[j * 8 + 2]) + z0.z, __uint_as_float(a[j * 8 + 3]) + z0.w);
-          u.z = pack_half2(__uint_as_float(a[j * 8 + 4]) + z1.x, __uint_as_float(a[j * 8 + 5]) + z1.y);
-          u.w = pack_half2(__uint_as_float(a[j * 8 + 6]) + z1.z, __uint_as_float(a[j * 8 + 7]) + z1.w);
-          *reinterpret_cast<uint4*>(stage + kBwK + row_chunk2(row, piece * 4 + j)) = u;
-        }
-      }
-      // ---- dS tile for the next (earlier) chunk
-      if (i + 1 < nchunk) {
-        uint32_t r[64];
-        tmem_ld32(tmem + lane_addr + k2ColDS, r);
-        tmem_ld32(tmem + lane_addr + k2ColDS + 32, r + 32);
-        tmem_ld_wait();
-        store_state_row(s_tile, row, r);
-      }
-      fence_async_smem();
-      tc_fence_before_sync();
-      if (i + 1 < nchunk) mbar_arrive(&bars[cSt]);
-      if (!epi_sync(&bars[cEpi], epi_phase)) { tc_fail(32); ok = false; break; }   // staging complete; dzs reads done
-      if (etid == 0) {
-        tma_store_3d(&tm_gk, stage + kBwK, 0, bh, (int)t0);
-        tma_store_3d(&tm_gk, stage + kBwK + kBox, 64, bh, (int)t0);
-        tma_store_3d(&tm_gv, stage + kBwV, 0, bh, (int)t0);
-        tma_store_commit();
-      }
-      // ---- dz += Q^T gz
-      dzs[row] += column_sum2(stage + kBwQ, row, gzs);
-      if (etid == 0) tma_store_wait_read<0>();
-      mbar_arrive(&bars[cEmpty + st]);
-    }
-    if (etid == 0) tma_store_wait<0>();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
-}
-
-int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gk, __half* gv,
-                            const float* ws_den, const float* ws_gz, const float* ds_seg, const float* dz_seg,
-                            int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st) {
-  CUtensorMap tq, tk, tv, tg, tgk, tgv;
-  if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tk, k, T, BH, kK, kTC) ||
-      make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&tg, g, T, BH, kD, kTC) ||
-      make_tmap_rows(&tgk, gk, T, BH, kK, kTC) || make_tmap_rows(&tgv, gv, T, BH, kD, kTC))
-    return fail(RFA_EDEVICE, "causal_bwd_kv: cuTensorMapEncodeTiled failed or is unavailable");
-  cudaError_t e = cudaFuncSetAttribute(causal_bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwSmem);
-  if (e != cudaSuccess) return fail((int)e, "causal_bwd_kv: cannot reserve %u bytes of shared memory: %s", kBwSmem, cudaGetErrorString(e));
-  causal_bwd_kv_tc_kernel<<<dim3(BH, nseg), kBwThreads, kBwSmem, st>>>(tq, tk, tv, tg, tgk, tgv, ws_den, ws_gz, ds_seg, dz_seg,
-                                                                      T, BH, nseg, tseg);
-  return check_launch("rfa_causal_bwd_kv");
-}
-
 int tc_status_causal_bwd() { return tc_status_read_clear(); }
 
 }  // namespace rfa

@@ -59,4 +59,5 @@ def _device_health(request):
     yield
     if request.node.get_closest_marker("gpu") and torch.cuda.is_available():
         from rfa_b200 import _lib
-        assert _lib.load().rfa_debug_status() == 0, "a bounded wait inside a kernel ran out"
+        status = _lib.load().rfa_debug_status()
+        assert status == 0, f"a bounded wait inside a kernel ran out (site code {status})"
