@@ -75,12 +75,15 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
     if (lane == 0) {
+      RFA_TRACE_DECL(0)
       for (int i = 0; i < nchunk; ++i) {
         const int st = i & 1;
+        RFA_TRACE_EV(1, i);
         if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
         unsigned char* base = sm + st * kvStage;
         const int t0 = (int)(t_begin + (int64_t)(nchunk - 1 - i) * kTC);
         uint64_t* fb = &bars[vFull + st];
+        RFA_TRACE_EV(2, i);
         mbar_arrive_expect_tx(fb, kvStage);
         tma_load_3d(base + kvG, &tm_g, fb, 0, bh, t0);
         tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
@@ -93,18 +96,30 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      RFA_TRACE_DECL(1)
       constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // K Q^T ; V gs^T ; V dS^T
       constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dAt Q            (B MN-major)
       constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // Pt gs ; K dS     (B MN-major)
       constexpr uint32_t idMM64 = umma_idesc_f16(128, 64, true, true);    // Q^T gs           (A, B MN-major)
-      const uint32_t sS = sbase + kvS;
+      // operand descriptors per stage (the shared-memory layout is static); a k-step is an add
+      uint64_t dQk[2], dQm[2], dKk[2], dVk[2], dGk[2], dGm[2];
+#pragma unroll
+      for (int s2 = 0; s2 < 2; ++s2) {
+        const uint32_t sb = sbase + s2 * kvStage;
+        dQk[s2] = umma_smem_desc(sb + kvQ, 0, 1024, kSwizzle128B);       // Q  K-major  [t][k]
+        dQm[s2] = umma_smem_desc(sb + kvQ, kBox, 1024, kSwizzle128B);    // Q  MN-major (rows = contraction t)
+        dKk[s2] = umma_smem_desc(sb + kvK, 0, 1024, kSwizzle128B);       // K  K-major  [s][k]
+        dVk[s2] = umma_smem_desc(sb + kvV, 0, 1024, kSwizzle128B);       // V  K-major  [s][n]
+        dGk[s2] = umma_smem_desc(sb + kvG, 0, 1024, kSwizzle128B);       // gs K-major  [t][n]
+        dGm[s2] = umma_smem_desc(sb + kvG, kBox, 1024, kSwizzle128B);    // gs MN-major (rows = contraction t)
+      }
+      const uint64_t dSk = umma_smem_desc(sbase + kvS, 0, 1024, kSwizzle128B);      // dS as [N = k rows][K = n]
+      const uint64_t dSm = umma_smem_desc(sbase + kvS, kBox, 1024, kSwizzle128B);   // dS as [K = k rows][N = n]
       auto issue_At = [&](int i) {                                        // At = K Q^T
-        const uint32_t sb = sbase + (i & 1) * kvStage;
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + kvColAt, umma_smem_desc(sb + kvK + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kvQ + kk, 0, 1024, kSwizzle128B), idKK, j > 0);
-        }
+        const int s2 = i & 1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          umma_ss(tmem + kvColAt, dKk[s2] + kstep_kmajor(j, kBox), dQk[s2] + kstep_kmajor(j, kBox), idKK, j > 0);
         umma_commit(&bars[vAt]);
       };
       bool ok = true;
@@ -114,25 +129,28 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       for (int i = 0; ok && i < nchunk; ++i) {
         const int st = i & 1;
-        const uint32_t sb = sbase + st * kvStage;
         const uint32_t ph = i & 1;
+        RFA_TRACE_EV(10, i);
         if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(3); break; }
+        RFA_TRACE_EV(11, i);
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 4; ++j)              // dAt = V gs^T
-          umma_ss(tmem + kvColDAt, umma_smem_desc(sb + kvV + j * 32, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kvG + j * 32, 0, 1024, kSwizzle128B), idKK, j > 0);
+          umma_ss(tmem + kvColDAt, dVk[st] + kstep_kmajor(j, kBox), dGk[st] + kstep_kmajor(j, kBox), idKK, j > 0);
         umma_commit(&bars[vDAt]);
+        RFA_TRACE_EV(12, i);
         if (!mbar_wait(&bars[vP], ph)) { tc_fail(4); break; }
+        RFA_TRACE_EV(13, i);
         if (!mbar_wait(&bars[vSt], ph)) { tc_fail(5); break; }
         if (i > 0 && !mbar_wait(&bars[vDVFree], (i - 1) & 1)) { tc_fail(6); break; }
+        RFA_TRACE_EV(14, i);
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // dV = Pt gs
-          umma_ts(tmem + kvColDV, tmem + kvColAt + j * 8, umma_smem_desc(sb + kvG + j * 2048, kBox, 1024, kSwizzle128B), idKM64, j > 0);
-        for (int j = 0; j < 8; ++j) {            // dV += K dS_next     (dS tile as [K = k rows][N = n])
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + kvColDV, umma_smem_desc(sb + kvK + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sS + j * 2048, kBox, 1024, kSwizzle128B), idKM64, 1);
-        }
+          umma_ts(tmem + kvColDV, tmem + kvColAt + j * 8, dGm[st] + kstep_mnmajor(j), idKM64, j > 0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)              // dV += K dS_next     (dS tile as [K = k rows][N = n])
+          umma_ss(tmem + kvColDV, dKk[st] + kstep_kmajor(j, kBox), dSm + kstep_mnmajor(j), idKM64, 1);
         umma_commit(&bars[vDV]);
         // the next chunk's scores as soon as its tiles are in (Pt of this chunk has been consumed above)
         bool next_issued = (i + 1 >= nchunk);
@@ -141,20 +159,24 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           issue_At(i + 1);
           next_issued = true;
         }
+        RFA_TRACE_EV(15, i);
         if (!mbar_wait(&bars[vDA16], ph)) { tc_fail(7); break; }
+        RFA_TRACE_EV(16, i);
         if (i > 0 && !mbar_wait(&bars[vDKFree], (i - 1) & 1)) { tc_fail(8); break; }
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // dK = dAt Q
-          umma_ts(tmem + kvColDK, tmem + kvColDAt + j * 8, umma_smem_desc(sb + kvQ + j * 2048, kBox, 1024, kSwizzle128B), idKM128, j > 0);
+          umma_ts(tmem + kvColDK, tmem + kvColDAt + j * 8, dQm[st] + kstep_mnmajor(j), idKM128, j > 0);
+#pragma unroll
         for (int j = 0; j < 4; ++j)              // dK += V dS_next^T   (dS tile as [N = k rows][K = n])
-          umma_ss(tmem + kvColDK, umma_smem_desc(sb + kvV + j * 32, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sS + j * 32, 0, 1024, kSwizzle128B), idKK, 1);
+          umma_ss(tmem + kvColDK, dVk[st] + kstep_kmajor(j, kBox), dSk + kstep_kmajor(j, kBox), idKK, 1);
         umma_commit(&bars[vDK]);
         const bool fresh = (i == 0 && ds_in == nullptr);
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // dS += Q^T gs
-          umma_ss(tmem + kvColDS, umma_smem_desc(sb + kvQ + j * 2048, kBox, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kvG + j * 2048, kBox, 1024, kSwizzle128B), idMM64, (fresh && j == 0) ? 0 : 1);
+          umma_ss(tmem + kvColDS, dQm[st] + kstep_mnmajor(j), dGm[st] + kstep_mnmajor(j), idMM64, (fresh && j == 0) ? 0 : 1);
         umma_commit(&bars[vS]);
+        RFA_TRACE_EV(17, i);
         if (!next_issued) {
           if (!mbar_wait(&bars[vFull + ((i + 1) & 1)], ((i + 1) >> 1) & 1)) { tc_fail(9); break; }
           tc_fence_after_sync();
@@ -167,6 +189,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // query row t (scaling g) / key row s (packing)
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    RFA_TRACE_DECL(2)
     for (int i = 0; i < nchunk; ++i) {
       const int st = i & 1;
       const uint32_t ph = i & 1;
@@ -179,7 +202,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
         gz = ws_gz[(size_t)bh * T + t0 + row];
       }
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(20, i);
       if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(21, i);
       {
         unsigned char* grow = stage + kvG;
 #pragma unroll
@@ -196,7 +221,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       fence_async_smem();
       mbar_arrive(&bars[vG + st]);
       // ---- Pt[s][t] = At[s][t] for t >= s  (fp16 over the first 64 columns)
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(22, i);
       if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(23, i);
       tc_fence_after_sync();
 #pragma unroll
       for (int piece = 0; piece < 4; ++piece) {
@@ -225,7 +252,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       mbar_arrive(&bars[vP]);
       // ---- dAt[s][t] = (v_s . gs_t + gz_t) for t >= s; gz of all rows is there once vG completed
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(12); break; }
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(24, i);
       if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(25, i);
       tc_fence_after_sync();
 #pragma unroll
       for (int piece = 0; piece < 4; ++piece) {
@@ -257,6 +286,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vDA16]);
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(26, i);
     }
   } else {
     // ------------------------------------------------------------------ output / state group
@@ -282,6 +312,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     }
     bool ok = true;
     uint32_t y_phase = 0;
+    RFA_TRACE_DECL(3)
     for (int i = 0; ok && i < nchunk; ++i) {
       const int st = i & 1;
       const uint32_t ph = i & 1;
@@ -291,7 +322,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       // dzs of the previous chunk is final for every thread
       if (!epi_sync(&bars[vY], y_phase)) { tc_fail(14); ok = false; break; }
       // ---- all MMAs of this chunk are complete once the state MMA is: K and V tiles become staging
+      if (ytid == 0) RFA_TRACE_EV(30, i);
       if (!mbar_wait(&bars[vS], ph)) { tc_fail(15); ok = false; break; }
+      if (ytid == 0) RFA_TRACE_EV(31, i);
       tc_fence_after_sync();
       // ---- reverse state after this chunk -> fp16 operand tile (the serial chain of the scan)
       if (i + 1 < nchunk) {
@@ -304,6 +337,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tc_fence_before_sync();
         mbar_arrive(&bars[vSt]);
       }
+      if (ytid == 0) RFA_TRACE_EV(32, i);
       // ---- grad_v -> V tile
       {
         uint32_t r[64];
@@ -334,6 +368,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
       }
       fence_async_smem();
+      if (ytid == 0) RFA_TRACE_EV(33, i);
       if (!epi_sync(&bars[vY], y_phase)) { tc_fail(16); ok = false; break; }   // staging complete; dzs reads done
       if (ytid == 0) {
         tma_store_3d(&tm_gk, stage + kvK, 0, bh, (int)t0);
@@ -344,7 +379,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       // ---- dz += Q^T gz   (vG completed long ago; waiting on it here orders this thread after the writes of gz)
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
       dzs[row] += column_sum2(stage + kvQ, row, gzs);
+      if (ytid == 0) RFA_TRACE_EV(34, i);
       if (ytid == 0) tma_store_wait_read<0>();
+      if (ytid == 0) RFA_TRACE_EV(35, i);
       mbar_arrive(&bars[vEmpty + st]);
     }
     if (ytid == 0) tma_store_wait<0>();
@@ -370,5 +407,7 @@ int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, c
 }
 
 int tc_status_causal_bwd_kv() { return tc_status_read_clear(); }
+
+RFA_TRACE_DUMP_FN(rfa_trace_dump_kv)
 
 }  // namespace rfa

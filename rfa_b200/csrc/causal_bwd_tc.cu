@@ -101,52 +101,64 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);     // P V ; Q S        (B MN-major)
       constexpr uint32_t idDAK = umma_idesc_f16(128, 128, false, true);   // dA K             (B MN-major)
       constexpr uint32_t idKtV = umma_idesc_f16(128, 64, true, true);     // K^T V ; Q^T gs   (A, B MN-major)
-      const uint32_t sS = sbase + kBwS;
+      // operand descriptors per stage (the shared-memory layout is static); a k-step is an add
+      uint64_t dQk[2], dQm[2], dKk[2], dKm[2], dVk[2], dVm[2], dGk[2], dGm[2];
+#pragma unroll
+      for (int s2 = 0; s2 < 2; ++s2) {
+        const uint32_t sb = sbase + s2 * kBwStage;
+        dQk[s2] = umma_smem_desc(sb + kBwQ, 0, 1024, kSwizzle128B);       // Q  K-major
+        dQm[s2] = umma_smem_desc(sb + kBwQ, kBox, 1024, kSwizzle128B);    // Q  MN-major (rows = contraction t)
+        dKk[s2] = umma_smem_desc(sb + kBwK, 0, 1024, kSwizzle128B);       // K  K-major
+        dKm[s2] = umma_smem_desc(sb + kBwK, kBox, 1024, kSwizzle128B);    // K  MN-major (rows = contraction s)
+        dVk[s2] = umma_smem_desc(sb + kBwV, 0, 1024, kSwizzle128B);       // V  K-major
+        dVm[s2] = umma_smem_desc(sb + kBwV, kBox, 1024, kSwizzle128B);    // V  MN-major
+        dGk[s2] = umma_smem_desc(sb + kBwG, 0, 1024, kSwizzle128B);       // gs K-major
+        dGm[s2] = umma_smem_desc(sb + kBwG, kBox, 1024, kSwizzle128B);    // gs MN-major
+      }
+      const uint64_t dSk = umma_smem_desc(sbase + kBwS, 0, 1024, kSwizzle128B);      // S as [N = k rows][K = n]
+      const uint64_t dSm = umma_smem_desc(sbase + kBwS, kBox, 1024, kSwizzle128B);   // S as [K = k rows][N = n]
       for (int c = 0; c < nchunk; ++c) {
         const int st = c & 1;
-        const uint32_t sb = sbase + st * kBwStage;
         const uint32_t ph = c & 1;
         if (!mbar_wait(&bars[bFull + st], (c >> 1) & 1)) { tc_fail(2); break; }
         tc_fence_after_sync();
-        for (int j = 0; j < 8; ++j) {            // A = Q K^T
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + q1ColA, umma_smem_desc(sb + kBwQ + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kBwK + kk, 0, 1024, kSwizzle128B), idQK, j > 0);
-        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)              // A = Q K^T
+          umma_ss(tmem + q1ColA, dQk[st] + kstep_kmajor(j, kBox), dKk[st] + kstep_kmajor(j, kBox), idQK, j > 0);
         umma_commit(&bars[bA]);
         if (!mbar_wait(&bars[bP], ph)) { tc_fail(3); break; }
         if (!mbar_wait(&bars[bSt], ph)) { tc_fail(4); break; }
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // N = P V
-          umma_ts(tmem + q1ColN, tmem + q1ColA + j * 8, umma_smem_desc(sb + kBwV + j * 2048, kBox, 1024, kSwizzle128B), idPV, j > 0);
-        for (int j = 0; j < 8; ++j) {            // N += Q S_prev   (S tile [k rows][n]: B MN-major over k)
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + q1ColN, umma_smem_desc(sb + kBwQ + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sS + j * 2048, kBox, 1024, kSwizzle128B), idPV, 1);
-        }
+          umma_ts(tmem + q1ColN, tmem + q1ColA + j * 8, dVm[st] + kstep_mnmajor(j), idPV, j > 0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)              // N += Q S_prev   (S tile [k rows][n]: B MN-major over k)
+          umma_ss(tmem + q1ColN, dQk[st] + kstep_kmajor(j, kBox), dSm + kstep_mnmajor(j), idPV, 1);
         umma_commit(&bars[bN]);
         if (!mbar_wait(&bars[bG], ph)) { tc_fail(5); break; }
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 4; ++j)              // dA = gs V^T   (contraction over d = 64)
-          umma_ss(tmem + q1ColA, umma_smem_desc(sb + kBwG + j * 32, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kBwV + j * 32, 0, 1024, kSwizzle128B), idQK, j > 0);
+          umma_ss(tmem + q1ColA, dGk[st] + kstep_kmajor(j, kBox), dVk[st] + kstep_kmajor(j, kBox), idQK, j > 0);
         umma_commit(&bars[bDA]);
         if (want_dseg)
+#pragma unroll
           for (int j = 0; j < 8; ++j)            // dSseg += Q^T gs
-            umma_ss(tmem + q1ColDS, umma_smem_desc(sb + kBwQ + j * 2048, kBox, 1024, kSwizzle128B),
-                    umma_smem_desc(sb + kBwG + j * 2048, kBox, 1024, kSwizzle128B), idKtV, (c > 0 || j > 0) ? 1 : 0);
+            umma_ss(tmem + q1ColDS, dQm[st] + kstep_mnmajor(j), dGm[st] + kstep_mnmajor(j), idKtV, (c > 0 || j > 0) ? 1 : 0);
         if (!mbar_wait(&bars[bDA16], ph)) { tc_fail(6); break; }
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // dQ = dA K
-          umma_ts(tmem + q1ColDQ, tmem + q1ColA + j * 8, umma_smem_desc(sb + kBwK + j * 2048, kBox, 1024, kSwizzle128B), idDAK, j > 0);
+          umma_ts(tmem + q1ColDQ, tmem + q1ColA + j * 8, dKm[st] + kstep_mnmajor(j), idDAK, j > 0);
+#pragma unroll
         for (int j = 0; j < 4; ++j)              // dQ += gs S_prev^T   (S tile as [N = k rows][K = n])
-          umma_ss(tmem + q1ColDQ, umma_smem_desc(sb + kBwG + j * 32, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sS + j * 32, 0, 1024, kSwizzle128B), idQK, 1);
+          umma_ss(tmem + q1ColDQ, dGk[st] + kstep_kmajor(j, kBox), dSk + kstep_kmajor(j, kBox), idQK, 1);
         umma_commit(&bars[bDQ]);
         const bool fresh = (c == 0 && s_in == nullptr);
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // S += K^T V
-          umma_ss(tmem + q1ColS, umma_smem_desc(sb + kBwK + j * 2048, kBox, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kBwV + j * 2048, kBox, 1024, kSwizzle128B), idKtV, (fresh && j == 0) ? 0 : 1);
+          umma_ss(tmem + q1ColS, dKm[st] + kstep_mnmajor(j), dVm[st] + kstep_mnmajor(j), idKtV, (fresh && j == 0) ? 0 : 1);
         umma_commit(&bars[bS]);
         umma_commit(&bars[bEmpty + st]);
       }

@@ -124,14 +124,24 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);    // Q [S|z]   (B MN-major)
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V       (B MN-major)
       constexpr uint32_t idS = umma_idesc_f16(128, 80, true, true);      // K^T [V|1] (A, B MN-major)
+      // operand descriptors per stage (the shared-memory layout is static)
+      uint64_t dQ[2], dK[2], dKt[2], dV[2], dV1[2];
+#pragma unroll
+      for (int s2 = 0; s2 < 2; ++s2) {
+        const uint32_t sb = sbase + s2 * kFwStage;
+        dQ[s2] = umma_smem_desc(sb + kFwQ, 0, 1024, kSwizzle128B);                        // Q, K-major
+        dK[s2] = umma_smem_desc(sb + kFwK, 0, 1024, kSwizzle128B);                        // K, K-major
+        dKt[s2] = umma_smem_desc(sb + kFwK, kBox, 1024, kSwizzle128B);                    // K^T, MN-major
+        dV[s2] = umma_smem_desc(sb + kFwV, kBox, 1024, kSwizzle128B);                     // V, MN-major (N = 64)
+        dV1[s2] = umma_smem_desc(sb + kFwV, kFwOnes - (s2 * kFwStage + kFwV), 1024, kSwizzle128B);   // [V|1], MN-major (N = 80)
+      }
+      const uint64_t dS = umma_smem_desc(sbase + kFwS, kBox, 1024, kSwizzle128B);         // state tile, MN-major (N = 80)
       auto issue_A = [&](int c) {
-        const uint32_t sb = sbase + (c & 1) * kFwStage;
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + fColA + (c & 1) * 128, umma_smem_desc(sb + kFwQ + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kFwK + kk, 0, 1024, kSwizzle128B), idA, j > 0);
-        }
-        umma_commit(&bars[fA + (c & 1)]);
+        const int s2 = c & 1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          umma_ss(tmem + fColA + s2 * 128, dQ[s2] + kstep_kmajor(j, kBox), dK[s2] + kstep_kmajor(j, kBox), idA, j > 0);
+        umma_commit(&bars[fA + s2]);
       };
       bool ok = true;
       if (nchunk > 0) {
@@ -140,25 +150,22 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       for (int c = 0; ok && c < nchunk; ++c) {
         const int st = c & 1;
-        const uint32_t sb = sbase + st * kFwStage;
         // the state before this chunk is in the operand tile, and the output group has let go of S
         RFA_TRACE_EV(10, c);
         if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); break; }
         if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); break; }
         tc_fence_after_sync();
         RFA_TRACE_EV(11, c);
-        for (int j = 0; j < 8; ++j) {            // N = Q [S|z]_prev
-          const uint32_t kk = (j >> 2) * kBox + (j & 3) * 32;
-          umma_ss(tmem + fColN + st * 80, umma_smem_desc(sb + kFwQ + kk, 0, 1024, kSwizzle128B),
-                  umma_smem_desc(sbase + kFwS + j * 2048, kBox, 1024, kSwizzle128B), idQS, j > 0);
-        }
         if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }
         tc_fence_after_sync();
         const bool fresh = (c == 0 && s_in == nullptr);
-        for (int j = 0; j < 8; ++j)              // [S|z] += K^T [V|1]
-          umma_ss(tmem + fColS, umma_smem_desc(sb + kFwK + j * 2048, kBox, 1024, kSwizzle128B),
-                  umma_smem_desc(sb + kFwV + j * 2048, kFwOnes - (st * kFwStage + kFwV), 1024, kSwizzle128B), idS,
-                  (fresh && j == 0) ? 0 : 1);
+        // N = Q [S|z]_prev  and  [S|z] += K^T [V|1], interleaved: two independent accumulator chains
+        // keep the tensor pipe busy where one chain of small MMAs would wait on itself
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          umma_ss(tmem + fColN + st * 80, dQ[st] + kstep_kmajor(j, kBox), dS + kstep_mnmajor(j), idQS, j > 0);
+          umma_ss(tmem + fColS, dKt[st] + kstep_mnmajor(j), dV1[st] + kstep_mnmajor(j), idS, (fresh && j == 0) ? 0 : 1);
+        }
         umma_commit(&bars[fS]);
         RFA_TRACE_EV(12, c);
         umma_commit(&bars[fEmpty + st]);         // Q and K of this stage have been read for the last time
@@ -174,9 +181,9 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); break; }
         RFA_TRACE_EV(14, c);
         tc_fence_after_sync();
+#pragma unroll
         for (int j = 0; j < 8; ++j)              // N += P V
-          umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8,
-                  umma_smem_desc(sb + kFwV + j * 2048, kBox, 1024, kSwizzle128B), idPV, 1);
+          umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8, dV[st] + kstep_mnmajor(j), idPV, 1);
         umma_commit(&bars[fN + st]);
         umma_commit(&bars[fEmptyV + st]);
         if (!next_issued) {
@@ -362,14 +369,6 @@ int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __ha
 
 int tc_status_causal_fwd() { return tc_status_read_clear(); }
 
-#ifdef RFA_TRACE
-extern "C" int rfa_trace_dump(unsigned long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
-  static unsigned long long zeros[4 * 1024 * 2];
-  cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
-  return 4 * 1024;
-}
-#endif
+RFA_TRACE_DUMP_FN(rfa_trace_dump)
 
 }  // namespace rfa

@@ -165,6 +165,16 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo,
   return d;
 }
 
+// Descriptors are built once per operand tile; a k-step only moves the 14-bit start-address field
+// (units of 16 bytes), which is a plain add on the 64-bit value.  Issuing an MMA then costs a few
+// instructions; the tensor pipe accepts one MMA every ~60 cycles at best, so the issue loop must be tight.
+//   K-major operand, two 64-wide boxes `box` bytes apart: k-step j (16 halves) of 8
+__device__ __forceinline__ constexpr uint64_t kstep_kmajor(int j, uint32_t box) {
+  return (uint64_t)(((j >> 2) * box + (j & 3) * 32) >> 4);
+}
+//   MN-major operand: k-step j covers 16 rows of 128 bytes
+__device__ __forceinline__ constexpr uint64_t kstep_mnmajor(int j) { return (uint64_t)((j * 2048) >> 4); }
+
 // Instruction descriptor, kind::f16: fp16 A and B, fp32 accumulator, dense.
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N, bool a_mn_major, bool b_mn_major) {
   return (1u << 4)                               // D format: f32

@@ -42,7 +42,17 @@ __device__ __forceinline__ void trace_ev(int role, int& n, int id, int chunk) {
 }
 #define RFA_TRACE_DECL(role) const int trace_role_ = (role); int trace_n_ = 0;
 #define RFA_TRACE_EV(id, chunk) trace_ev(trace_role_, trace_n_, (id), (chunk))
+// defines  extern "C" int NAME(unsigned long long* out)  copying this translation unit's records (4*1024 pairs)
+#define RFA_TRACE_DUMP_FN(NAME)                                      \
+  extern "C" int NAME(unsigned long long* out) {                     \
+    static unsigned long long zeros[4 * 1024 * 2];                   \
+    cudaDeviceSynchronize();                                         \
+    cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));             \
+    cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));               \
+    return 4 * 1024;                                                 \
+  }
 #else
+#define RFA_TRACE_DUMP_FN(NAME)
 #define RFA_TRACE_DECL(role)
 #define RFA_TRACE_EV(id, chunk) ((void)0)
 #endif
