@@ -378,7 +378,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       // ---- dz += Q^T gz   (vG completed long ago; waiting on it here orders this thread after the writes of gz)
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
-      dzs[row] += column_sum2(stage + kvQ, row, gzs);
+      dzs[row] += column_sum2(stage + kvQ, quarter, lane, gzs);
       if (ytid == 0) RFA_TRACE_EV(34, i);
       if (ytid == 0) tma_store_wait_read<0>();
       if (ytid == 0) RFA_TRACE_EV(35, i);

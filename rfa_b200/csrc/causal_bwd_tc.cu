@@ -276,7 +276,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_arrive(&bars[bG]);
       if (want_dseg) {                               // dzseg += Q^T gz, while Q is still intact
         if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(11); ok = false; break; }
-        dz_acc += column_sum2(stage + kBwQ, row, gzs);
+        dz_acc += column_sum2(stage + kBwQ, quarter, lane, gzs);
       }
       // ---- dA = mask(gs V^T + gz) -> fp16 over the P columns
       if (!mbar_wait(&bars[bDA], ph)) { tc_fail(12); ok = false; break; }
@@ -334,7 +334,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tma_store_commit();
       }
       // ---- z += colsum(K)   (every thread is past its reads of zs for this chunk)
-      zs[row] += column_sum2(stage + kBwK, row, nullptr);
+      zs[row] += column_sum2(stage + kBwK, quarter, lane, nullptr);
       // ---- state after this chunk -> fp16 operand tile
       if (!mbar_wait(&bars[bS], ph)) { tc_fail(15); ok = false; break; }
       tc_fence_after_sync();

@@ -95,19 +95,37 @@ __device__ __forceinline__ void store_state_row(unsigned char* tile, int r, cons
   }
 }
 
-// sum over the chunk's rows s of X[s][col] * w[s]  (w == nullptr -> 1) for a two-box tile
-__device__ __forceinline__ float column_sum2(const unsigned char* tile, int col, const float* w) {
-  const unsigned char* base = tile + (col >> 6) * kBox + ((col & 7) << 1);
-  const int cc = (col & 63) >> 3;
-  float a = 0.f;
-#pragma unroll 8
-  for (int s = 0; s < 128; ++s) {
-    const float x = __half2float(*reinterpret_cast<const __half*>(base + s * 128 + ((cc ^ (s & 7)) << 4)));
-    a = w ? fmaf(x, w[s], a) : a + x;
+// Column sums of a two-box [128 rows][128 cols] fp16 tile: returns sum_s X[s][col] * w[s]
+// (w == nullptr -> 1) for col = quarter * 32 + lane.  Warp-cooperative: a warp covers 32 columns;
+// lane = 8 * c4 + rg reads the 16-byte chunk (4 * quarter + c4) of rows rg, rg + 8, ... (conflict-free,
+// 16 loads of 8 values), the 8 row groups are then combined with shuffles.
+__device__ __forceinline__ float column_sum2(const unsigned char* tile, int quarter, int lane, const float* w) {
+  const int rg = lane & 7, cc = 4 * quarter + (lane >> 3);
+  const unsigned char* base = tile + (cc >> 3) * kBox + (((cc & 7) ^ rg) << 4) + rg * 128;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll 4
+  for (int j = 0; j < 16; ++j) {
+    const uint4 u = *reinterpret_cast<const uint4*>(base + j * 1024);
+    const float wv = w ? w[rg + 8 * j] : 1.f;
+    const float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
+    acc[0] = fmaf(f0.x, wv, acc[0]); acc[1] = fmaf(f0.y, wv, acc[1]);
+    acc[2] = fmaf(f1.x, wv, acc[2]); acc[3] = fmaf(f1.y, wv, acc[3]);
+    acc[4] = fmaf(f2.x, wv, acc[4]); acc[5] = fmaf(f2.y, wv, acc[5]);
+    acc[6] = fmaf(f3.x, wv, acc[6]); acc[7] = fmaf(f3.y, wv, acc[7]);
   }
-  return a;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 4);
+  }
+  float r = acc[0];                      // column 8 * cc + rg  ==  32 * quarter + lane
+#pragma unroll
+  for (int e = 1; e < 8; ++e) r = (rg == e) ? acc[e] : r;
+  return r;
 }
-
 #endif
 
 }  // namespace rfa
