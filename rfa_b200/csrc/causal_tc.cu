@@ -17,6 +17,8 @@
 // TMEM buffers each for A/P and N, so the score group works one chunk ahead of the output
 // group.  The only per-chunk serial chain is  state MMA -> state export -> next state MMA.
 // All waits are bounded.
+#include <type_traits>
+
 #include "tc_common.cuh"
 
 namespace rfa {
@@ -124,47 +126,40 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);    // Q [S|z]   (B MN-major)
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V       (B MN-major)
       constexpr uint32_t idS = umma_idesc_f16(128, 80, true, true);      // K^T [V|1] (A, B MN-major)
-      // operand descriptors per stage (the shared-memory layout is static)
-      uint64_t dQ[2], dK[2], dKt[2], dV[2], dV1[2];
+      // Operand descriptors (the shared-memory layout is static).  The chunk loop is unrolled by two so that
+      // the stage is a compile-time constant: every descriptor is a register, every k-step an immediate add.
+      const uint64_t dQ0 = umma_smem_desc(sbase + kFwQ, 0, 1024, kSwizzle128B), dQ1 = dQ0 + (kFwStage >> 4);      // Q, K-major
+      const uint64_t dK0 = umma_smem_desc(sbase + kFwK, 0, 1024, kSwizzle128B), dK1 = dK0 + (kFwStage >> 4);      // K, K-major
+      const uint64_t dKt0 = umma_smem_desc(sbase + kFwK, kBox, 1024, kSwizzle128B), dKt1 = dKt0 + (kFwStage >> 4);  // K^T, MN-major
+      const uint64_t dV0 = umma_smem_desc(sbase + kFwV, kBox, 1024, kSwizzle128B), dV1 = dV0 + (kFwStage >> 4);   // V, MN-major (N = 64)
+      const uint64_t dW0 = umma_smem_desc(sbase + kFwV, kFwOnes - kFwV, 1024, kSwizzle128B);                      // [V|1], MN-major (N = 80)
+      const uint64_t dW1 = umma_smem_desc(sbase + kFwStage + kFwV, kFwOnes - (kFwStage + kFwV), 1024, kSwizzle128B);
+      const uint64_t dS = umma_smem_desc(sbase + kFwS, kBox, 1024, kSwizzle128B);                                 // state tile, MN-major (N = 80)
+      auto issue_A = [&](auto STC) {
+        constexpr int s2 = decltype(STC)::value;
+        const uint64_t q = s2 ? dQ1 : dQ0, k = s2 ? dK1 : dK0;
 #pragma unroll
-      for (int s2 = 0; s2 < 2; ++s2) {
-        const uint32_t sb = sbase + s2 * kFwStage;
-        dQ[s2] = umma_smem_desc(sb + kFwQ, 0, 1024, kSwizzle128B);                        // Q, K-major
-        dK[s2] = umma_smem_desc(sb + kFwK, 0, 1024, kSwizzle128B);                        // K, K-major
-        dKt[s2] = umma_smem_desc(sb + kFwK, kBox, 1024, kSwizzle128B);                    // K^T, MN-major
-        dV[s2] = umma_smem_desc(sb + kFwV, kBox, 1024, kSwizzle128B);                     // V, MN-major (N = 64)
-        dV1[s2] = umma_smem_desc(sb + kFwV, kFwOnes - (s2 * kFwStage + kFwV), 1024, kSwizzle128B);   // [V|1], MN-major (N = 80)
-      }
-      const uint64_t dS = umma_smem_desc(sbase + kFwS, kBox, 1024, kSwizzle128B);         // state tile, MN-major (N = 80)
-      auto issue_A = [&](int c) {
-        const int s2 = c & 1;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma_ss(tmem + fColA + s2 * 128, dQ[s2] + kstep_kmajor(j, kBox), dK[s2] + kstep_kmajor(j, kBox), idA, j > 0);
+        for (int j = 0; j < 8; ++j) umma_ss(tmem + fColA + s2 * 128, q + kstep_kmajor(j, kBox), k + kstep_kmajor(j, kBox), idA, j > 0);
         umma_commit(&bars[fA + s2]);
       };
-      bool ok = true;
-      if (nchunk > 0) {
-        ok = mbar_wait(&bars[fFull + 0], 0);
-        if (ok) { tc_fence_after_sync(); issue_A(0); } else tc_fail(2);
-      }
-      for (int c = 0; ok && c < nchunk; ++c) {
-        const int st = c & 1;
+      // one chunk; returns false after a timed-out wait
+      auto chunk = [&](auto STC, int c) -> bool {
+        constexpr int st = decltype(STC)::value;
+        const uint64_t q = st ? dQ1 : dQ0, kt = st ? dKt1 : dKt0, v = st ? dV1 : dV0, w = st ? dW1 : dW0;
         // the state before this chunk is in the operand tile, and the output group has let go of S
         RFA_TRACE_EV(10, c);
-        if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); break; }
-        if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); break; }
+        if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); return false; }
+        if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); return false; }
         tc_fence_after_sync();
         RFA_TRACE_EV(11, c);
-        if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }
+        if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); return false; }
         tc_fence_after_sync();
-        const bool fresh = (c == 0 && s_in == nullptr);
-        // N = Q [S|z]_prev  and  [S|z] += K^T [V|1], interleaved: two independent accumulator chains
-        // keep the tensor pipe busy where one chain of small MMAs would wait on itself
+        const uint32_t fresh_acc = (c == 0 && s_in == nullptr) ? 0u : 1u;
+        // N = Q [S|z]_prev  and  [S|z] += K^T [V|1]
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          umma_ss(tmem + fColN + st * 80, dQ[st] + kstep_kmajor(j, kBox), dS + kstep_mnmajor(j), idQS, j > 0);
-          umma_ss(tmem + fColS, dKt[st] + kstep_mnmajor(j), dV1[st] + kstep_mnmajor(j), idS, (fresh && j == 0) ? 0 : 1);
+          umma_ss(tmem + fColN + st * 80, q + kstep_kmajor(j, kBox), dS + kstep_mnmajor(j), idQS, j > 0);
+          umma_ss(tmem + fColS, kt + kstep_mnmajor(j), w + kstep_mnmajor(j), idS, j == 0 ? fresh_acc : 1u);
         }
         umma_commit(&bars[fS]);
         RFA_TRACE_EV(12, c);
@@ -172,26 +167,38 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // next chunk's scores as early as its Q, K are there, so the score group never starves --
         // but never hold back this chunk's P V (and with it the release of V) for a load in flight
         bool next_issued = (c + 1 >= nchunk);
-        if (!next_issued && mbar_try_wait(&bars[fFull + ((c + 1) & 1)], ((c + 1) >> 1) & 1)) {
+        if (!next_issued && mbar_try_wait(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
           tc_fence_after_sync();
-          issue_A(c + 1);
+          issue_A(std::integral_constant<int, st ^ 1>{});
           next_issued = true;
         }
         RFA_TRACE_EV(13, c);
-        if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); break; }
+        if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); return false; }
         RFA_TRACE_EV(14, c);
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j)              // N += P V
-          umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8, dV[st] + kstep_mnmajor(j), idPV, 1);
+          umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8, v + kstep_mnmajor(j), idPV, 1);
         umma_commit(&bars[fN + st]);
         umma_commit(&bars[fEmptyV + st]);
         if (!next_issued) {
-          if (!mbar_wait(&bars[fFull + ((c + 1) & 1)], ((c + 1) >> 1) & 1)) { tc_fail(5); break; }
+          if (!mbar_wait(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) { tc_fail(5); return false; }
           tc_fence_after_sync();
-          issue_A(c + 1);
+          issue_A(std::integral_constant<int, st ^ 1>{});
         }
+        return true;
+      };
+      bool ok = true;
+      RFA_TRACE_EV(91, 0); RFA_TRACE_CLOCK(90);
+      if (nchunk > 0) {
+        ok = mbar_wait(&bars[fFull + 0], 0);
+        if (ok) { tc_fence_after_sync(); issue_A(std::integral_constant<int, 0>{}); } else tc_fail(2);
       }
+      for (int c = 0; ok && c < nchunk; c += 2) {
+        ok = chunk(std::integral_constant<int, 0>{}, c);
+        if (ok && c + 1 < nchunk) ok = chunk(std::integral_constant<int, 1>{}, c + 1);
+      }
+      RFA_TRACE_EV(93, 0); RFA_TRACE_CLOCK(92);
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ score group: P = mask(A), row sums

@@ -40,6 +40,14 @@ __device__ __forceinline__ void trace_ev(int role, int& n, int id, int chunk) {
     ++n;
   }
 }
+__device__ __forceinline__ void trace_clock(int role, int& n, int id) {      // SM cycle counter instead of the ns timer
+  if (blockIdx.x == 0 && blockIdx.y == 0 && n < 1024) {
+    g_trace[(role * 1024 + n) * 2] = ((unsigned long long)id << 32);
+    g_trace[(role * 1024 + n) * 2 + 1] = (unsigned long long)clock64();
+    ++n;
+  }
+}
+#define RFA_TRACE_CLOCK(id) trace_clock(trace_role_, trace_n_, (id))
 #define RFA_TRACE_DECL(role) const int trace_role_ = (role); int trace_n_ = 0;
 #define RFA_TRACE_EV(id, chunk) trace_ev(trace_role_, trace_n_, (id), (chunk))
 // defines  extern "C" int NAME(unsigned long long* out)  copying this translation unit's records (4*1024 pairs)
@@ -52,6 +60,7 @@ __device__ __forceinline__ void trace_ev(int role, int& n, int id, int chunk) {
     return 4 * 1024;                                                 \
   }
 #else
+#define RFA_TRACE_CLOCK(id)
 #define RFA_TRACE_DUMP_FN(NAME)
 #define RFA_TRACE_DECL(role)
 #define RFA_TRACE_EV(id, chunk) ((void)0)
