@@ -166,6 +166,26 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def upstream_cuda_leg(q, k, v, up, stream, ours_ms):
+    """Upstream's own CUDA kernels (oracle/_ref, compiled unmodified for this GPU) on the same inputs."""
+    try:
+        from oracle import ref_cuda
+        mod = ref_cuda.load()
+        if mod is None:
+            return {"unavailable": "oracle/_ref/rfa_cuda_ref.so not built"}
+        legacy = torch.cuda.default_stream()          # upstream launches on the legacy default stream
+        with torch.cuda.stream(legacy):
+            for _ in range(2):
+                mod.forward(q, k, v); mod.backward(q, k, v, up)
+            ms_f = timed(lambda: mod.forward(q, k, v), 5, legacy)
+            ms_b = timed(lambda: mod.backward(q, k, v, up), 5, legacy)
+        return {"fwd_ms": ms_f, "bwd_ms": ms_b, "tokens_per_s": TOKENS_PER_STEP / ((ms_f + ms_b) * 1e-3),
+                "speedup_of_new_kernels": (ms_f + ms_b) / ours_ms,
+                "note": "includes upstream's own output allocation + zero fill, as its API does"}
+    except Exception as e:  # noqa: BLE001
+        return {"error": repr(e)}
+
+
 def extras(device, stream, hbm):
     """Secondary measurements: decode (config 4), cross attention (config 3), feature map."""
     from rfa_b200 import ops
@@ -378,6 +398,7 @@ def main():
                                     "seconds": dt}
             if not args.no_extras:
                 line["extra"] = extras(device, stream, hbm)
+                line["extra"]["upstream_cuda_kernels"] = upstream_cuda_leg(q, k, v, up, stream, ms_per_step)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
