@@ -1,0 +1,503 @@
+// Causal RFA backward, sweep 1 (forward in time) on tcgen05 tensor cores: grad_q, plus the
+// per-token scalars den and gz that sweep 2 needs (upstream cuda/backward.cu:303-371, q_backward;
+// math in rfa.py:79-94), chunks of 128 tokens.
+//
+// Per chunk, with S/z the state of all earlier tokens:
+//     A   = Q K^T              -> P = mask(A) fp16 (TMEM), rowsum
+//     N   = P V + Q S          -> den = max(rowsum + q.z, 1), out = N/den
+//     gs  = g/den (fp16, over the staged g tile),  gz = -(g.out)/den * [rowsum + q.z > 1]
+//     dA  = gs V^T             -> mask(dA + gz) fp16 (TMEM, over P)
+//     dQ  = gs S^T + dA K (+ gz z^T added in the epilogue)            -> grad_q
+//     S  += K^T V,  z += colsum(K);   optionally  dSseg += Q^T gs, dzseg += Q^T gz
+// S and dSseg are fp32 TMEM accumulators; z is fp32 in shared memory (CUDA-core update).
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 score group
+// (P, den/gz/gs, dA), warps 6..9 output/state group (grad_q, state export, z).  The score tile
+// A/P/N/dA is double-buffered in TMEM and the score group is software-pipelined (gs of chunk c,
+// then P of chunk c+1, then dA of chunk c) so that it always has work while the tensor pipe
+// runs the products it is waiting for.  All waits are bounded.
+#include <type_traits>
+
+#include "tc_common.cuh"
+
+namespace rfa {
+
+constexpr int kBqThreads = 320;
+
+constexpr uint32_t bqQ = 0, bqK = 2 * kBox, bqV = 4 * kBox, bqG = 5 * kBox, bqStage = 6 * kBox;   // 98304 per stage
+constexpr uint32_t bqS = 2 * bqStage;            // S as an operand: [128 k][64 n] fp16, swizzled
+constexpr uint32_t bqZ = bqS + kBox;             // fp32 [3][128]: z before chunk c lives in buffer c % 3 (readers of version c,
+                                                 // c + 1 and the writer of version c + 2 can be active at once)
+constexpr uint32_t bqGz = bqZ + 1536;            // fp32 [2][128]: gz of chunk c's rows in buffer c & 1
+constexpr uint32_t bqBar = bqGz + 1024;
+constexpr uint32_t bqSmem = bqBar + 256 + 1024;
+
+// TMEM: two score buffers (A -> P in columns 0..63, N in columns 64..127, then dA -> fp16 dA in 0..63)
+constexpr uint32_t bqColA = 0, bqColDQ = 256, bqColS = 384, bqColDS = 448;
+enum { qFull = 0, qEmpty = 2, qA = 4, qP = 6, qN = 8, qG = 10, qDA = 12, qDA16 = 14, qZ = 16, qDQ = 18, qDQFree = 19,
+       qS = 20, qSt = 21, qY = 22, qNum = 23 };
+
+__global__ void __launch_bounds__(kBqThreads, 1)
+causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
+                       __half* __restrict__ gq_ptr,
+                       const float* __restrict__ s_seg, const float* __restrict__ z_seg,
+                       float* __restrict__ ws_den, float* __restrict__ ws_gz,
+                       float* __restrict__ ds_seg, float* __restrict__ dz_seg,
+                       int64_t T, int BH, int nseg, int64_t tseg) {
+  extern __shared__ unsigned char bq_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(bq_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + bqBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + qNum);
+  float* z_buf = reinterpret_cast<float*>(sm + bqZ);
+  float* gz_buf = reinterpret_cast<float*>(sm + bqGz);
+  const uint32_t sbase = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x, seg = blockIdx.y;
+  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
+  const int nchunk = (int)((t_end - t_begin + kTC - 1) / kTC);
+  const size_t slot = (size_t)bh * nseg + seg;
+  const float* s_in = s_seg ? s_seg + slot * kK * kD : nullptr;
+  const float* z_in = z_seg ? z_seg + slot * kK : nullptr;
+  const bool want_dseg = ds_seg != nullptr;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[qFull + i], 1);
+      mbar_init(&bars[qEmpty + i], 129);      // the MMA issuer's commit + the output group's last reads
+      mbar_init(&bars[qA + i], 1);
+      mbar_init(&bars[qP + i], 128);
+      mbar_init(&bars[qN + i], 1);
+      mbar_init(&bars[qG + i], 128);
+      mbar_init(&bars[qDA + i], 1);
+      mbar_init(&bars[qDA16 + i], 128);
+      mbar_init(&bars[qZ + i], 128);
+    }
+    mbar_init(&bars[qDQ], 1); mbar_init(&bars[qDQFree], 128); mbar_init(&bars[qS], 1);
+    mbar_init(&bars[qSt], 128); mbar_init(&bars[qY], 128);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      RFA_TRACE_DECL(0)
+      for (int c = 0; c < nchunk; ++c) {
+        const int st = c & 1;
+        RFA_TRACE_EV(1, c);
+        if (c >= 2 && !mbar_wait(&bars[qEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
+        unsigned char* base = sm + st * bqStage;
+        const int t0 = (int)(t_begin + (int64_t)c * kTC);
+        uint64_t* fb = &bars[qFull + st];
+        RFA_TRACE_EV(2, c);
+        mbar_arrive_expect_tx(fb, bqStage);
+        tma_load_3d(base + bqQ, &tm_q, fb, 0, bh, t0);
+        tma_load_3d(base + bqQ + kBox, &tm_q, fb, 64, bh, t0);
+        tma_load_3d(base + bqK, &tm_k, fb, 0, bh, t0);
+        tma_load_3d(base + bqK + kBox, &tm_k, fb, 64, bh, t0);
+        tma_load_3d(base + bqV, &tm_v, fb, 0, bh, t0);
+        tma_load_3d(base + bqG, &tm_g, fb, 0, bh, t0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      RFA_TRACE_DECL(1)
+      constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // Q K^T ; gs V^T ; gs S^T
+      constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // P V ; Q S        (B MN-major)
+      constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dA K             (B MN-major)
+      constexpr uint32_t idMM64 = umma_idesc_f16(128, 64, true, true);    // K^T V ; Q^T gs   (A, B MN-major)
+      constexpr uint64_t kSt = bqStage >> 4;
+      const uint64_t dQk = umma_smem_desc(sbase + bqQ, 0, 1024, kSwizzle128B), dQm = umma_smem_desc(sbase + bqQ, kBox, 1024, kSwizzle128B);
+      const uint64_t dKk = umma_smem_desc(sbase + bqK, 0, 1024, kSwizzle128B), dKm = umma_smem_desc(sbase + bqK, kBox, 1024, kSwizzle128B);
+      const uint64_t dVk = umma_smem_desc(sbase + bqV, 0, 1024, kSwizzle128B), dVm = umma_smem_desc(sbase + bqV, kBox, 1024, kSwizzle128B);
+      const uint64_t dGk = umma_smem_desc(sbase + bqG, 0, 1024, kSwizzle128B), dGm = umma_smem_desc(sbase + bqG, kBox, 1024, kSwizzle128B);
+      const uint64_t dSk = umma_smem_desc(sbase + bqS, 0, 1024, kSwizzle128B);      // S as [N = k rows][K = n]
+      const uint64_t dSm = umma_smem_desc(sbase + bqS, kBox, 1024, kSwizzle128B);   // S as [K = k rows][N = n]
+      // A = Q K^T of chunk c into score buffer c & 1
+      auto issue_scores = [&](auto STC) {
+        constexpr int st = decltype(STC)::value;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          umma_ss(tmem + bqColA + st * 128, dQk + st * kSt + kstep_kmajor(j, kBox), dKk + st * kSt + kstep_kmajor(j, kBox), idKK, j > 0);
+        umma_commit(&bars[qA + st]);
+      };
+      // N = P V + Q S of chunk c into columns 64..127 of its score buffer
+      auto issue_n = [&](auto STC, int c) -> bool {
+        constexpr int st = decltype(STC)::value;
+        RFA_TRACE_EV(10, c);
+        if (!mbar_wait(&bars[qP + st], (c >> 1) & 1)) { tc_fail(2); return false; }
+        RFA_TRACE_EV(11, c);
+        if (!mbar_wait(&bars[qSt], c & 1)) { tc_fail(3); return false; }
+        tc_fence_after_sync();
+        RFA_TRACE_EV(12, c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          umma_ts(tmem + bqColA + st * 128 + 64, tmem + bqColA + st * 128 + j * 8, dVm + st * kSt + kstep_mnmajor(j), idKM64, j > 0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          umma_ss(tmem + bqColA + st * 128 + 64, dQk + st * kSt + kstep_kmajor(j, kBox), dSm + kstep_mnmajor(j), idKM64, 1);
+        umma_commit(&bars[qN + st]);
+        RFA_TRACE_EV(13, c);
+        return true;
+      };
+      auto chunk = [&](auto STC, int c) -> bool {
+        constexpr int st = decltype(STC)::value;
+        using Other = std::integral_constant<int, st ^ 1>;
+        RFA_TRACE_EV(14, c);
+        if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(4); return false; }
+        RFA_TRACE_EV(15, c);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)              // dA = gs V^T   (contraction over d = 64)
+          umma_ss(tmem + bqColA + st * 128, dGk + st * kSt + kstep_kmajor(j, kBox), dVk + st * kSt + kstep_kmajor(j, kBox), idKK, j > 0);
+        umma_commit(&bars[qDA + st]);
+        if (c > 0 && !mbar_wait(&bars[qDQFree], (c - 1) & 1)) { tc_fail(5); return false; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)              // dQ = gs S_prev^T   (S tile as [N = k rows][K = n])
+          umma_ss(tmem + bqColDQ, dGk + st * kSt + kstep_kmajor(j, kBox), dSk + kstep_kmajor(j, kBox), idKK, j > 0);
+        const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)              // S += K^T V   (after the last read of the S tile for this chunk)
+          umma_ss(tmem + bqColS, dKm + st * kSt + kstep_mnmajor(j), dVm + st * kSt + kstep_mnmajor(j), idMM64, j == 0 ? acc0 : 1u);
+        umma_commit(&bars[qS]);
+        RFA_TRACE_EV(16, c);
+        if (want_dseg) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)            // dSseg += Q^T gs
+            umma_ss(tmem + bqColDS, dQm + st * kSt + kstep_mnmajor(j), dGm + st * kSt + kstep_mnmajor(j), idMM64, (c > 0 || j > 0) ? 1u : 0u);
+        }
+        // scores of chunk c + 1 as soon as its tiles are in (its buffer was freed by the dQ product of chunk
+        // c - 1) -- but without blocking: this chunk must not wait for the next chunk's load
+        bool scores_issued = (c + 1 >= nchunk) || c == 0;
+        if (!scores_issued && mbar_try_wait(&bars[qFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
+          tc_fence_after_sync();
+          issue_scores(Other{});
+          scores_issued = true;
+        }
+        RFA_TRACE_EV(19, c);
+        if (!mbar_wait(&bars[qDA16 + st], (c >> 1) & 1)) { tc_fail(6); return false; }
+        RFA_TRACE_EV(20, c);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)              // dQ += dA K
+          umma_ts(tmem + bqColDQ, tmem + bqColA + st * 128 + j * 8, dKm + st * kSt + kstep_mnmajor(j), idKM128, 1);
+        umma_commit(&bars[qDQ]);
+        umma_commit(&bars[qEmpty + st]);         // every MMA that reads this stage has been issued
+        if (c + 1 < nchunk) {
+          if (!scores_issued) {
+            RFA_TRACE_EV(17, c);
+            if (!mbar_wait(&bars[qFull + (st ^ 1)], ((c + 1) >> 1) & 1)) { tc_fail(7); return false; }
+            RFA_TRACE_EV(18, c);
+            tc_fence_after_sync();
+            issue_scores(Other{});
+          }
+          if (!issue_n(Other{}, c + 1)) return false;
+        }
+        RFA_TRACE_EV(21, c);
+        return true;
+      };
+      bool ok = nchunk > 0;
+      if (ok) {
+        ok = mbar_wait(&bars[qFull], 0);
+        if (ok) { tc_fence_after_sync(); issue_scores(std::integral_constant<int, 0>{}); } else tc_fail(8);
+      }
+      if (ok && nchunk > 1) {
+        ok = mbar_wait(&bars[qFull + 1], 0);
+        if (ok) { tc_fence_after_sync(); issue_scores(std::integral_constant<int, 1>{}); } else tc_fail(9);
+      }
+      if (ok) ok = issue_n(std::integral_constant<int, 0>{}, 0);
+      for (int c = 0; ok && c < nchunk; c += 2) {
+        ok = chunk(std::integral_constant<int, 0>{}, c);
+        if (ok && c + 1 < nchunk) ok = chunk(std::integral_constant<int, 1>{}, c + 1);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ score group
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // token row of the chunk
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    bool ok = true;
+    RFA_TRACE_DECL(2)
+    const bool tr = (warp == 5 && lane == 0);
+    // P = mask(A) fp16 + row sum; then q . z_prev in fp32 from this thread's own Q row
+    auto do_p = [&](int c, float& rowsum, float& qz) {
+      const int st = c & 1;
+      const uint32_t colA = bqColA + st * 128;
+      unsigned char* stage = sm + st * bqStage;
+      const float* zs = z_buf + (c % 3) * 128;
+      if (tr) RFA_TRACE_EV(30, c);
+      if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(10); ok = false; return; }
+      if (tr) RFA_TRACE_EV(31, c);
+      if (!mbar_wait(&bars[qZ + (c & 1)], (c >> 1) & 1)) { tc_fail(11); ok = false; return; }
+      if (tr) RFA_TRACE_EV(32, c);
+      if (!mbar_wait(&bars[qA + st], (c >> 1) & 1)) { tc_fail(12); ok = false; return; }
+      if (tr) RFA_TRACE_EV(33, c);
+      tc_fence_after_sync();
+      rowsum = 0.f;
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        uint32_t p[16];
+        if (piece <= quarter) {
+          uint32_t a[32];
+          tmem_ld32(tmem + lane_addr + colA + piece * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = __uint_as_float(a[i]), x1 = __uint_as_float(a[i + 1]);
+            if (piece == quarter) {
+              if (i > lane) x0 = 0.f;
+              if (i + 1 > lane) x1 = 0.f;
+            }
+            rowsum += x0 + x1;
+            p[i >> 1] = pack_half2(x0, x1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) p[i] = 0u;
+        }
+        tmem_st16(tmem + lane_addr + colA + piece * 16, p);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[qP + st]);
+      if (tr) RFA_TRACE_EV(34, c);
+      // q . z_prev while the tensor pipe computes N from the P just handed over
+      qz = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint4 u = *reinterpret_cast<const uint4*>(stage + bqQ + row_chunk2(row, ch));
+        const float4 z0 = *reinterpret_cast<const float4*>(zs + ch * 8), z1 = *reinterpret_cast<const float4*>(zs + ch * 8 + 4);
+        float2 f;
+        f = unpack_half2(u.x); qz = fmaf(f.x, z0.x, qz); qz = fmaf(f.y, z0.y, qz);
+        f = unpack_half2(u.y); qz = fmaf(f.x, z0.z, qz); qz = fmaf(f.y, z0.w, qz);
+        f = unpack_half2(u.z); qz = fmaf(f.x, z1.x, qz); qz = fmaf(f.y, z1.y, qz);
+        f = unpack_half2(u.w); qz = fmaf(f.x, z1.z, qz); qz = fmaf(f.y, z1.w, qz);
+      }
+    };
+    // den, gz, gs
+    auto do_g = [&](int c, float rowsum, float qz, float& gz) {
+      const int st = c & 1;
+      unsigned char* stage = sm + st * bqStage;
+      const int64_t t0 = t_begin + (int64_t)c * kTC;
+      if (tr) RFA_TRACE_EV(35, c);
+      if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(13); ok = false; return; }
+      if (tr) RFA_TRACE_EV(36, c);
+      tc_fence_after_sync();
+      uint32_t nn[64];
+      tmem_ld32(tmem + lane_addr + bqColA + st * 128 + 64, nn);
+      tmem_ld32(tmem + lane_addr + bqColA + st * 128 + 96, nn + 32);
+      tmem_ld_wait();
+      const float raw = rowsum + qz;
+      const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
+      float go = 0.f;
+      unsigned char* grow = stage + bqG;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
+        uint4 u = *p;
+        float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
+        go = fmaf(f0.x, __uint_as_float(nn[ch * 8 + 0]), go); go = fmaf(f0.y, __uint_as_float(nn[ch * 8 + 1]), go);
+        go = fmaf(f1.x, __uint_as_float(nn[ch * 8 + 2]), go); go = fmaf(f1.y, __uint_as_float(nn[ch * 8 + 3]), go);
+        go = fmaf(f2.x, __uint_as_float(nn[ch * 8 + 4]), go); go = fmaf(f2.y, __uint_as_float(nn[ch * 8 + 5]), go);
+        go = fmaf(f3.x, __uint_as_float(nn[ch * 8 + 6]), go); go = fmaf(f3.y, __uint_as_float(nn[ch * 8 + 7]), go);
+        u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
+        u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
+        *p = u;
+      }
+      go *= inv;                                   // g . out
+      gz = raw > kEps ? -go * inv : 0.f;           // strict >, upstream rfa.py:91
+      if (t0 + row < t_end) {
+        ws_den[(size_t)bh * T + t0 + row] = dn;
+        ws_gz[(size_t)bh * T + t0 + row] = gz;
+      }
+      gz_buf[(c & 1) * 128 + row] = gz;
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[qG + st]);
+      if (tr) RFA_TRACE_EV(37, c);
+    };
+    // dA = mask(gs V^T + gz) -> fp16 over the P columns
+    auto do_da = [&](int c, float gz) {
+      const int st = c & 1;
+      const uint32_t colA = bqColA + st * 128;
+      if (tr) RFA_TRACE_EV(38, c);
+      if (!mbar_wait(&bars[qDA + st], (c >> 1) & 1)) { tc_fail(14); ok = false; return; }
+      if (tr) RFA_TRACE_EV(39, c);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        uint32_t p[16];
+        if (piece <= quarter) {
+          uint32_t a[32];
+          tmem_ld32(tmem + lane_addr + colA + piece * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = __uint_as_float(a[i]) + gz, x1 = __uint_as_float(a[i + 1]) + gz;
+            if (piece == quarter) {
+              if (i > lane) x0 = 0.f;
+              if (i + 1 > lane) x1 = 0.f;
+            }
+            p[i >> 1] = pack_half2(x0, x1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) p[i] = 0u;
+        }
+        tmem_st16(tmem + lane_addr + colA + piece * 16, p);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[qDA16 + st]);
+      if (tr) RFA_TRACE_EV(40, c);
+    };
+    float rs_cur = 0.f, qz_cur = 0.f;
+    if (nchunk > 0) do_p(0, rs_cur, qz_cur);
+    for (int c = 0; ok && c < nchunk; ++c) {
+      float gz = 0.f, rs_nxt = 0.f, qz_nxt = 0.f;
+      do_g(c, rs_cur, qz_cur, gz);
+      if (ok) do_da(c, gz);
+      if (ok && c + 1 < nchunk) do_p(c + 1, rs_nxt, qz_nxt);
+      rs_cur = rs_nxt;
+      qz_cur = qz_nxt;
+    }
+  } else {
+    // ------------------------------------------------------------------ output / state group
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // token row of the chunk / state row k
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int ytid = tid - 192;
+    unsigned char* s_tile = sm + bqS;
+    (void)ytid;
+    {
+      uint32_t r[64];
+#pragma unroll
+      for (int n = 0; n < 64; ++n) r[n] = s_in ? __float_as_uint(s_in[(size_t)row * kD + n]) : 0u;
+      store_state_row(s_tile, row, r);
+      if (s_in) {
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + bqColS + c0, r + c0);
+        tmem_st_wait();
+      }
+      z_buf[row] = z_in ? z_in[row] : 0.f;
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[qSt]);
+      mbar_arrive(&bars[qZ + 0]);
+    }
+    bool ok = true;
+    float dz_acc = 0.f;
+    RFA_TRACE_DECL(3)
+    const bool tr = (ytid == 0);
+    for (int c = 0; ok && c < nchunk; ++c) {
+      const int st = c & 1;
+      const uint32_t ph = c & 1;
+      unsigned char* stage = sm + st * bqStage;
+      const int64_t t0 = t_begin + (int64_t)c * kTC;
+      const float* zs = z_buf + (c % 3) * 128;
+      const float* gzs = gz_buf + (c & 1) * 128;
+      // ---- z before the next chunk = z + colsum(K): needs only the staged K tile
+      if (tr) RFA_TRACE_EV(50, c);
+      if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); ok = false; break; }
+      if (tr) RFA_TRACE_EV(51, c);
+      z_buf[((c + 1) % 3) * 128 + row] = zs[row] + column_sum2(stage + bqK, quarter, lane, nullptr);
+      mbar_arrive(&bars[qZ + ((c + 1) & 1)]);
+      // ---- the state after this chunk -> fp16 operand tile (the serial chain of the scan)
+      if (tr) RFA_TRACE_EV(52, c);
+      if (!mbar_wait(&bars[qS], ph)) { tc_fail(16); ok = false; break; }
+      if (tr) RFA_TRACE_EV(53, c);
+      tc_fence_after_sync();
+      if (c + 1 < nchunk) {
+        uint32_t r[64];
+        tmem_ld32(tmem + lane_addr + bqColS, r);
+        tmem_ld32(tmem + lane_addr + bqColS + 32, r + 32);
+        tmem_ld_wait();
+        store_state_row(s_tile, row, r);
+        fence_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[qSt]);
+      }
+      // gz of every row of this chunk is in shared memory once qG completed (it did: the state MMA waited on it)
+      if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(17); ok = false; break; }
+      if (want_dseg) dz_acc += column_sum2(stage + bqQ, quarter, lane, gzs);      // dzseg += Q^T gz
+      const float gz = gzs[row];
+      mbar_arrive(&bars[qEmpty + st]);             // this group's last read of the stage's tiles
+      // ---- grad_q = dQ + gz z_prev^T -> fp16, written straight from registers (one 256-byte row per thread)
+      if (tr) RFA_TRACE_EV(54, c);
+      if (!mbar_wait(&bars[qDQ], ph)) { tc_fail(18); ok = false; break; }
+      if (tr) RFA_TRACE_EV(55, c);
+      tc_fence_after_sync();
+      const bool live = t0 + row < t_end;
+      __half* grow = reinterpret_cast<__half*>(gq_ptr) + ((size_t)(t0 + row) * BH + bh) * kK;
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+        uint32_t a[32];
+        tmem_ld32(tmem + lane_addr + bqColDQ + piece * 32, a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k0 = piece * 32 + j * 8;
+          const float4 z0 = *reinterpret_cast<const float4*>(zs + k0), z1 = *reinterpret_cast<const float4*>(zs + k0 + 4);
+          uint4 u;
+          u.x = pack_half2(fmaf(gz, z0.x, __uint_as_float(a[j * 8 + 0])), fmaf(gz, z0.y, __uint_as_float(a[j * 8 + 1])));
+          u.y = pack_half2(fmaf(gz, z0.z, __uint_as_float(a[j * 8 + 2])), fmaf(gz, z0.w, __uint_as_float(a[j * 8 + 3])));
+          u.z = pack_half2(fmaf(gz, z1.x, __uint_as_float(a[j * 8 + 4])), fmaf(gz, z1.y, __uint_as_float(a[j * 8 + 5])));
+          u.w = pack_half2(fmaf(gz, z1.z, __uint_as_float(a[j * 8 + 6])), fmaf(gz, z1.w, __uint_as_float(a[j * 8 + 7])));
+          if (live) *reinterpret_cast<uint4*>(grow + k0) = u;
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&bars[qDQFree]);                 // after the last read of dQ and of this chunk's z, gz
+      if (tr) RFA_TRACE_EV(57, c);
+    }
+    if (ok && want_dseg) {
+      uint32_t r[64];
+      if (nchunk > 0) {
+        tmem_ld32(tmem + lane_addr + bqColDS, r);
+        tmem_ld32(tmem + lane_addr + bqColDS + 32, r + 32);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int n = 0; n < 64; ++n) r[n] = 0u;
+      }
+      float4* dst = reinterpret_cast<float4*>(ds_seg + (slot * kK + row) * kD);
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+        dst[n] = make_float4(__uint_as_float(r[4 * n]), __uint_as_float(r[4 * n + 1]), __uint_as_float(r[4 * n + 2]),
+                             __uint_as_float(r[4 * n + 3]));
+      dz_seg[slot * kK + row] = dz_acc;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------
+int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gq,
+                           const float* s_seg, const float* z_seg, float* ws_den, float* ws_gz, float* ds_seg,
+                           float* dz_seg, int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st) {
+  CUtensorMap tq, tk, tv, tg;
+  if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tk, k, T, BH, kK, kTC) ||
+      make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&tg, g, T, BH, kD, kTC))
+    return fail(RFA_EDEVICE, "causal_bwd_q: cuTensorMapEncodeTiled failed or is unavailable");
+  cudaError_t e = cudaFuncSetAttribute(causal_bwd_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bqSmem);
+  if (e != cudaSuccess) return fail((int)e, "causal_bwd_q: cannot reserve %u bytes of shared memory: %s", bqSmem, cudaGetErrorString(e));
+  causal_bwd_q_tc_kernel<<<dim3(BH, nseg), kBqThreads, bqSmem, st>>>(tq, tk, tv, tg, gq, s_seg, z_seg, ws_den, ws_gz, ds_seg,
+                                                                    dz_seg, T, BH, nseg, tseg);
+  return check_launch("rfa_causal_bwd_q");
+}
+
+int tc_status_causal_bwd() { return tc_status_read_clear(); }
+
+RFA_TRACE_DUMP_FN(rfa_trace_dump_q)
+
+}  // namespace rfa
