@@ -31,11 +31,19 @@ def test_same_answers_as_upstream_kernels_on_upstream_check_shapes(dev, upstream
     torch.cuda.synchronize()
     out = ops.causal_fwd(q, k, v)
     gq, gk, gv = ops.causal_bwd(q, k, v, up)
-    # upstream checks the forward on the first fixture (test_forward) and the gradients on the second
-    # (test_backward, unit-norm rows); hold each to what upstream itself checks
-    pairs = [(out, ref_out)] if name == "causal_fwd_gradcheck" else [(out, ref_out), (gq, ref_gq), (gk, ref_gk), (gv, ref_gv)]
-    for a, b in pairs:
-        assert ((a.float() - b.float()) ** 2 < 1e-4).all()
+    # Upstream's criterion (grad_check.py:13-14) is |difference| < 1e-2 against its fp32 twin.  On the
+    # unit-norm fixture both kernel sets meet it against each other.  On the first fixture (unnormalised
+    # rows, outputs up to 6) upstream's own fp16-accumulating kernel is 0.038 away from its fp32 twin --
+    # it fails its own check there -- so the new kernels are held to: inside the criterion against fp32,
+    # and no further from upstream's kernel than upstream's kernel is from fp32.
+    if name == "causal_bwd_gradcheck":
+        for a, b in ((out, ref_out), (gq, ref_gq), (gk, ref_gk), (gv, ref_gv)):
+            assert ((a.float() - b.float()) ** 2 < 1e-4).all()
+    else:
+        want = g["attn"].to(dev)
+        mine, theirs = (out.float() - want).abs().max(), (ref_out.float() - want).abs().max()
+        assert mine < 1e-2 and mine <= theirs
+        assert (out.float() - ref_out.float()).abs().max() <= mine + theirs
 
 
 def test_upstream_kernels_drift_where_new_kernels_do_not(dev, upstream):
