@@ -9,15 +9,29 @@
 
 namespace rfa {
 
-constexpr int kDecodeThreads = 256;
+constexpr int kDecodeThreads = 128;   // 7 CTAs per SM at <= 72 registers: 1024 (batch, head) pairs fit in one wave of 148 SMs
+
+constexpr int kDecodePrefetch = 8;   // state rows per thread fetched before the prologue (all of them at K=128, d=64)
+
+// Issue this thread's first state loads; they fly while the prologue (inputs, feature map) runs.
+template <typename TState>
+__device__ __forceinline__ void decode_prefetch(const TState* __restrict__ S, int K, int d, float4 (&buf)[kDecodePrefetch]) {
+  const int d4 = d >> 2, rows = kDecodeThreads / d4;
+  const int c = threadIdx.x % d4, r0 = threadIdx.x / d4;
+#pragma unroll
+  for (int u = 0; u < kDecodePrefetch; ++u) {
+    const int k = r0 + u * rows;
+    buf[u] = k < K ? load4(S + (size_t)k * d + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
 
 // Shared tail of both decode kernels.  pq/pk hold phi_q/phi_k (K floats each) in
-// shared memory, vs holds v (d floats).
+// shared memory, vs holds v (d floats); buf holds the prefetched state rows.
 template <typename TIn, typename TState>
 __device__ __forceinline__ void decode_body(const float* pq, const float* pk, const float* vs,
                                             TState* __restrict__ S, TState* __restrict__ z,
                                             TIn* __restrict__ out, float4* red, float* den_s,
-                                            int K, int d) {
+                                            int K, int d, float4 (&buf)[kDecodePrefetch]) {
   const int tid = threadIdx.x;
   const int d4 = d >> 2;                       // float4 columns per state row
   const int rows = kDecodeThreads / d4;        // state rows covered per pass
@@ -38,8 +52,19 @@ __device__ __forceinline__ void decode_body(const float* pq, const float* pk, co
   const float4 v4 = *reinterpret_cast<const float4*>(vs + 4 * c);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   TState* Sc = S + 4 * c;
-  int k = r0;
-  // four independent 16-byte loads in flight per thread
+#pragma unroll
+  for (int u = 0; u < kDecodePrefetch; ++u) {
+    const int kk = r0 + u * rows;
+    if (kk < K) {
+      const float a = pk[kk], b = pq[kk];
+      float4 t = buf[u];
+      t.x = fmaf(a, v4.x, t.x); t.y = fmaf(a, v4.y, t.y); t.z = fmaf(a, v4.z, t.z); t.w = fmaf(a, v4.w, t.w);
+      store4(Sc + (size_t)kk * d, t);
+      acc.x = fmaf(b, t.x, acc.x); acc.y = fmaf(b, t.y, acc.y); acc.z = fmaf(b, t.z, acc.z); acc.w = fmaf(b, t.w, acc.w);
+    }
+  }
+  int k = r0 + kDecodePrefetch * rows;
+  // beyond the prefetched rows: four independent 16-byte loads in flight per thread
   for (; k + 3 * rows < K; k += 4 * rows) {
     float4 s[4];
 #pragma unroll
@@ -78,7 +103,7 @@ __device__ __forceinline__ void decode_body(const float* pq, const float* pk, co
 }
 
 template <typename TIn, typename TState>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, 7)
 decode_step_kernel(const TIn* __restrict__ phi_q, const TIn* __restrict__ phi_k,
                    const TIn* __restrict__ v, TState* __restrict__ S, TState* __restrict__ z,
                    TIn* __restrict__ out, int K, int d) {
@@ -89,19 +114,21 @@ decode_step_kernel(const TIn* __restrict__ phi_q, const TIn* __restrict__ phi_k,
   float* vs = pk + K;                                                // d
   float* den_s = vs + d;
   const size_t bh = blockIdx.x;
+  float4 buf[kDecodePrefetch];
+  decode_prefetch(S + bh * (size_t)K * d, K, d, buf);
   for (int i = threadIdx.x; i < K; i += kDecodeThreads) {
     pq[i] = to_f(phi_q[bh * K + i]);
     pk[i] = to_f(phi_k[bh * K + i]);
   }
   for (int i = threadIdx.x; i < d; i += kDecodeThreads) vs[i] = to_f(v[bh * d + i]);
   __syncthreads();
-  decode_body<TIn, TState>(pq, pk, vs, S + bh * (size_t)K * d, z + bh * K, out + bh * d, red, den_s, K, d);
+  decode_body<TIn, TState>(pq, pk, vs, S + bh * (size_t)K * d, z + bh * K, out + bh * d, red, den_s, K, d, buf);
 }
 
 // Raw q,k in; the feature map (normalise, project with this head's W, sin|cos, scale)
 // is applied in the prologue (upstream utils.py:100-120).
 template <typename TIn, typename TState>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, 7)
 decode_step_fused_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
                          const TIn* __restrict__ v, const float* __restrict__ w, float scale,
                          TState* __restrict__ S, TState* __restrict__ z, TIn* __restrict__ out,
@@ -118,6 +145,8 @@ decode_step_fused_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
   const size_t bh = blockIdx.x;
   const int h = (int)(bh % H);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float4 buf[kDecodePrefetch];
+  decode_prefetch(S + bh * (size_t)K * d, K, d, buf);
   for (int i = tid; i < d; i += kDecodeThreads) vs[i] = to_f(v[bh * d + i]);
   if (warp < 2) {            // warp 0 normalises q, warp 1 normalises k
     const TIn* src = (warp == 0 ? q : k) + bh * d;
@@ -129,22 +158,37 @@ decode_step_fused_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
     for (int i = lane; i < d; i += 32) dst[i] *= inv;
   }
   __syncthreads();
-  // one warp per projection row j: coalesced read of W[h][j][:], used for both vectors
+  // Projections u = W_h xhat for both vectors with the whole CTA: a group of 4 (8, 16) lanes owns one row j
+  // and reads it as contiguous float4's; partial dot products are combined with shuffles; then one thread
+  // per (vector, j) takes the sine and cosine.  us[] holds the 2*D projections in between.
+  float* us = xk + d;
   const float* wh = w + (size_t)h * D * d;
-  for (int j = warp; j < D; j += kDecodeThreads / 32) {
-    float uq = 0.f, uk = 0.f;
-    for (int i = lane; i < d; i += 32) {
-      const float wv = wh[(size_t)j * d + i];
-      uq = fmaf(wv, xq[i], uq);
-      uk = fmaf(wv, xk[i], uk);
+  {
+    const int per = kDecodeThreads / D >= 16 ? 16 : (kDecodeThreads / D >= 8 ? 8 : (kDecodeThreads / D >= 4 ? 4 : (kDecodeThreads / D >= 2 ? 2 : 1)));
+    const int rows_per_pass = kDecodeThreads / per;
+    const int sub = tid % per;
+    for (int j = tid / per; j < D; j += rows_per_pass) {
+      float uq = 0.f, uk = 0.f;
+      for (int i = sub * 4; i < d; i += per * 4) {
+        const float4 wv = *reinterpret_cast<const float4*>(wh + (size_t)j * d + i);
+        uq = fmaf(wv.x, xq[i], uq); uq = fmaf(wv.y, xq[i + 1], uq); uq = fmaf(wv.z, xq[i + 2], uq); uq = fmaf(wv.w, xq[i + 3], uq);
+        uk = fmaf(wv.x, xk[i], uk); uk = fmaf(wv.y, xk[i + 1], uk); uk = fmaf(wv.z, xk[i + 2], uk); uk = fmaf(wv.w, xk[i + 3], uk);
+      }
+      for (int o = per >> 1; o > 0; o >>= 1) {
+        uq += __shfl_xor_sync(0xffffffffu, uq, o);
+        uk += __shfl_xor_sync(0xffffffffu, uk, o);
+      }
+      if (sub == 0) { us[j] = uq; us[D + j] = uk; }
     }
-    uq = warp_sum(uq);
-    uk = warp_sum(uk);
-    if (lane == 0) {
-      float s_, c_;
-      sincosf(uq, &s_, &c_); pq[j] = scale * s_; pq[D + j] = scale * c_;
-      sincosf(uk, &s_, &c_); pk[j] = scale * s_; pk[D + j] = scale * c_;
-    }
+  }
+  __syncthreads();
+  for (int t = tid; t < 2 * D; t += kDecodeThreads) {
+    float s_, c_;
+    sincosf(us[t], &s_, &c_);
+    float* dst = t < D ? pq : pk;
+    const int j = t < D ? t : t - D;
+    dst[j] = scale * s_;
+    dst[D + j] = scale * c_;
   }
   __syncthreads();
   if (sizeof(TIn) == 2) {    // features are handed over in the I/O precision, as the unfused path does
@@ -154,7 +198,7 @@ decode_step_fused_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
     }
     __syncthreads();
   }
-  decode_body<TIn, TState>(pq, pk, vs, S + bh * (size_t)K * d, z + bh * K, out + bh * d, red, den_s, K, d);
+  decode_body<TIn, TState>(pq, pk, vs, S + bh * (size_t)K * d, z + bh * K, out + bh * d, red, den_s, K, d, buf);
 }
 
 static int check_decode_geometry(int BH, int K, int d) {
@@ -195,11 +239,12 @@ extern "C" int rfa_decode_step_fused(const void* q, const void* k, const void* v
                                      void* out, int BH, int H, int D, int d, rfa_stream_t stream) {
   RFA_REQUIRE(q && k && v && w && s && z && out, RFA_EINVAL, "decode_fused: null pointer");
   RFA_REQUIRE(H > 0 && D > 0, RFA_EINVAL, "decode_fused: H=%d D=%d must be positive", H, D);
+  RFA_REQUIRE(D % 8 == 0, RFA_EUNSUPPORTED, "decode_fused: proj_dim %d must be a multiple of 8", D);
   if (int e = check_decode_geometry(BH, 2 * D, d)) return e;
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(s) && aligned16(z) && aligned16(out) && aligned16(w),
               RFA_EALIGN, "decode_fused: pointers must be 16-byte aligned");
   const int K = 2 * D;
-  const size_t smem = kDecodeThreads * sizeof(float4) + (2 * K + 3 * d + 4) * sizeof(float);
+  const size_t smem = kDecodeThreads * sizeof(float4) + (2 * K + 3 * d + 4 + 2 * D) * sizeof(float);
   cudaStream_t st = as_stream(stream);
 #define RFA_LAUNCH(TI, TS)                                                                        \
   decode_step_fused_kernel<TI, TS><<<BH, kDecodeThreads, smem, st>>>(                             \
