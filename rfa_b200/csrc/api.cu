@@ -26,6 +26,7 @@ int check_launch(const char* what) {
 int tc_status_causal_fwd();
 int tc_status_causal_bwd();
 int tc_status_causal_bwd_kv();
+int tc_status_cross();
 
 }  // namespace rfa
 
@@ -38,6 +39,7 @@ extern "C" int rfa_debug_status(void) {
   if (f) return f < 0 ? f : 100 + f;
   if (b) return b < 0 ? b : 200 + b;
   if (const int kv = rfa::tc_status_causal_bwd_kv()) return kv < 0 ? kv : 300 + kv;
+  if (const int x = rfa::tc_status_cross()) return x < 0 ? x : 400 + x;
   return 0;
 }
 

@@ -1,7 +1,7 @@
-// Host orchestration of causal RFA (segment planning, workspace, boundary-state scan; the
-// chunk kernels themselves are the tcgen05 kernels in causal_tc.cu / causal_bwd_tc.cu), the
-// state-reduction and scan kernels, and the cross-attention kernels (K = 128, d = 64, fp16
-// I/O, fp32 arithmetic and fp32 state).
+// Host side of the attention entry points: argument checks, segment planning, workspace, the
+// boundary-state scan.  The kernels themselves are the tcgen05 kernels in causal_tc.cu,
+// causal_bwd_q_tc.cu, causal_bwd_kv_tc.cu and cross_tc.cu (K = 128, d = 64, fp16 I/O, fp32
+// accumulation and fp32 state).
 //
 // Notation per (batch, head):  S = sum k v^T [K,d],  z = sum k [K]  (upstream rfa.py:57-64).
 // With few (batch, head) pairs a sequence is cut into segments that run as separate CTAs;
@@ -34,6 +34,15 @@ int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, co
 int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gk, __half* gv,
                             const float* ws_den, const float* ws_gz, const float* ds_seg, const float* dz_seg,
                             int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st);
+
+// tensor-core state reduction and cross-attention kernels (cross_tc.cu)
+int launch_cross_state_fwd_tc(const __half* k, const __half* v, const uint8_t* pad_mask, float* s, float* z, int64_t T, int BH,
+                              int H, int nseg, int64_t tseg, cudaStream_t st);
+int launch_cross_query_fwd_tc(const __half* q, const float* s, const float* z, __half* out, int64_t T, int BH, cudaStream_t st);
+int launch_cross_query_bwd_tc(const __half* q, const float* s, const float* z, const __half* g, __half* gq, float* d_s, float* d_z,
+                              int64_t T, int BH, cudaStream_t st);
+int launch_cross_state_bwd_tc(const __half* k, const __half* v, const uint8_t* pad_mask, const float* d_s, const float* d_z,
+                              __half* gk, __half* gv, int64_t T, int BH, int H, cudaStream_t st);
 
 static CausalPlan plan_causal(int64_t T, int BH) {
   CausalPlan p{1, ((T + kSegAlign - 1) / kSegAlign) * kSegAlign};
@@ -75,41 +84,6 @@ static CausalWs carve_ws(void* base, int64_t T, int BH, const CausalPlan& p) {
   return w;
 }
 
-// ---------------------------------------------------------------------------
-// state reduction over a run of tokens (cross-attention S,z and segment totals)
-// grid (BH, nseg).  pad_mask [B][T] (non-zero = padding) zeroes k rows.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
-segment_state_kernel(const __half* __restrict__ k, const __half* __restrict__ v,
-                     const uint8_t* __restrict__ pad_mask, float* __restrict__ s_out,
-                     float* __restrict__ z_out, int64_t T, int BH, int H, int nseg, int64_t tseg) {
-  extern __shared__ __align__(16) float sm[];
-  float* Ks = sm;
-  float* Vs = Ks + kC * kLK;
-  float* St = Vs + kC * kLD;
-  float* zs = St + kK * kLD;
-  const int bh = blockIdx.x, seg = blockIdx.y;
-  const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
-  load_state(St, zs, nullptr, nullptr);
-  for (int64_t t0 = t_begin; t0 < t_end; t0 += kC) {
-    const int valid = (int)min((int64_t)kC, t_end - t0);
-    __syncthreads();
-    stage_rows<kK>(Ks, kLK, k + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kD>(Vs, kLD, v + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    __syncthreads();
-    if (pad_mask) {
-      const uint8_t* m = pad_mask + (size_t)(bh / H) * T + t0;
-      for (int idx = threadIdx.x; idx < valid * kK; idx += kThreads)
-        if (m[idx / kK]) Ks[(idx / kK) * kLK + (idx % kK)] = 0.f;
-      __syncthreads();
-    }
-    accumulate_state(St, zs, Ks, Vs, nullptr);
-  }
-  __syncthreads();
-  const size_t slot = (size_t)bh * nseg + seg;
-  store_state(s_out + slot * kK * kD, z_out + slot * kK, St, zs);
-}
-
 // In-place exclusive scan over the segment axis of seg [BH][nseg][n] (forward or
 // reverse order), seeded with carry [BH][n] (may be null); optionally also the plain
 // sum over segments into total [BH][n].
@@ -132,168 +106,8 @@ __global__ void scan_states_kernel(float* __restrict__ seg, const float* __restr
 }
 
 // ---------------------------------------------------------------------------
-// cross attention, query side.  grid (chunks, BH)
-//   out_t = phi_q_t . S / max(|phi_q_t . z|, 1)      (upstream cross_attention.py:266-269)
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
-cross_query_fwd_kernel(const __half* __restrict__ q, const float* __restrict__ s, const float* __restrict__ z,
-                       __half* __restrict__ out, int64_t T, int BH) {
-  extern __shared__ __align__(16) float sm[];
-  float* Qs = sm;
-  float* Ns = Qs + kC * kLK;
-  float* St = Ns + kC * kLD;
-  float* zs = St + kK * kLD;
-  float* den = zs + kK;
-  const int bh = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t t0 = (int64_t)blockIdx.x * kC;
-  const int valid = (int)min((int64_t)kC, T - t0);
-  load_state(St, zs, s + (size_t)bh * kK * kD, z + (size_t)bh * kK);
-  stage_rows<kK>(Qs, kLK, q + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-  __syncthreads();
-  tile_gemm<4, 4>(kC, kD, kK,
-                  [&](int r, int l) { return Qs[r * kLK + l]; },
-                  [&](int l, int j) { return St[l * kLD + j]; },
-                  [&](int r, int j, float a) { Ns[r * kLD + j] = a; });
-  for (int r = warp; r < kC; r += kThreads / 32) {
-    float p = 0.f;
-#pragma unroll
-    for (int l = lane; l < kK; l += 32) p = fmaf(Qs[r * kLK + l], zs[l], p);
-    p = warp_sum(p);
-    if (lane == 0) den[r] = fmaxf(fabsf(p), kEps);
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < kC * (kD / 8); idx += kThreads) {
-    const int r = idx / (kD / 8), c = (idx % (kD / 8)) * 8;
-    if (r >= valid) continue;
-    const float inv = 1.f / den[r];
-    float f[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = Ns[r * kLD + c + e] * inv;
-    store8(out + ((size_t)(t0 + r) * BH + bh) * kD + c, f);
-  }
-}
-
-// Query-side backward: one CTA per (batch, head) walks all query chunks and keeps
-// dS, dz on chip.  With raw = phi_q.z, den = max(|raw|,1):
-//   gs = g/den,  gr = -(g.out)/den * sign(raw) * [|raw| > 1]
-//   g_phi_q = gs S^T + gr z^T,   dS = sum_t phi_q_t (x) gs_t,   dz = sum_t gr_t phi_q_t
-__global__ void __launch_bounds__(kThreads)
-cross_query_bwd_kernel(const __half* __restrict__ q, const float* __restrict__ s, const float* __restrict__ z,
-                       const __half* __restrict__ g, __half* __restrict__ gq, float* __restrict__ d_s,
-                       float* __restrict__ d_z, int64_t T, int BH) {
-  extern __shared__ __align__(16) float sm[];
-  float* Qs = sm;
-  float* Ds = Qs + kC * kLK;
-  float* Gs = Ds + kC * kLK;
-  float* Ns = Gs + kC * kLD;
-  float* St = Ns + kC * kLD;
-  float* dSt = St + kK * kLD;
-  float* zs = dSt + kK * kLD;
-  float* dzs = zs + kK;
-  float* den = dzs + kK;
-  float* grs = den + kC;
-  const int bh = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  load_state(St, zs, s + (size_t)bh * kK * kD, z + (size_t)bh * kK);
-  load_state(dSt, dzs, nullptr, nullptr);
-  for (int64_t t0 = 0; t0 < T; t0 += kC) {
-    const int valid = (int)min((int64_t)kC, T - t0);
-    __syncthreads();
-    stage_rows<kK>(Qs, kLK, q + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-    stage_rows<kD>(Gs, kLD, g + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-    __syncthreads();
-    tile_gemm<4, 4>(kC, kD, kK,
-                    [&](int r, int l) { return Qs[r * kLK + l]; },
-                    [&](int l, int j) { return St[l * kLD + j]; },
-                    [&](int r, int j, float a) { Ns[r * kLD + j] = a; });
-    for (int r = warp; r < kC; r += kThreads / 32) {
-      float p = 0.f;
-#pragma unroll
-      for (int l = lane; l < kK; l += 32) p = fmaf(Qs[r * kLK + l], zs[l], p);
-      p = warp_sum(p);
-      if (lane == 0) den[r] = p;
-    }
-    __syncthreads();
-    for (int r = warp; r < kC; r += kThreads / 32) {
-      const float raw = den[r];
-      const float dn = fmaxf(fabsf(raw), kEps), inv = 1.f / dn;
-      const float g0 = Gs[r * kLD + lane], g1 = Gs[r * kLD + lane + 32];
-      float go = g0 * Ns[r * kLD + lane] + g1 * Ns[r * kLD + lane + 32];
-      go = warp_sum(go) * inv;
-      const float grv = fabsf(raw) > kEps ? (raw > 0.f ? -go * inv : go * inv) : 0.f;
-      Gs[r * kLD + lane] = g0 * inv;
-      Gs[r * kLD + lane + 32] = g1 * inv;
-      __syncwarp();
-      if (lane == 0) grs[r] = grv;
-    }
-    __syncthreads();
-    tile_gemm<4, 8>(kC, kK, kD,
-                    [&](int r, int l) { return Gs[r * kLD + l]; },
-                    [&](int l, int c) { return St[c * kLD + l]; },
-                    [&](int r, int c, float a) { Ds[r * kLK + c] = fmaf(grs[r], zs[c], a); });
-    __syncthreads();
-    unstage_rows<kK>(gq + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, Ds, kLK, valid);
-    accumulate_state(dSt, dzs, Qs, Gs, grs);
-  }
-  __syncthreads();
-  store_state(d_s + (size_t)bh * kK * kD, d_z + (size_t)bh * kK, dSt, dzs);
-}
-
-// Key-side backward of the state reduction.  grid (chunks, BH)
-//   g_phi_k[s] = dS v_s + dz  (zero at padded keys),   g_v[s] = dS^T phi_k[s] (masked phi_k)
-__global__ void __launch_bounds__(kThreads)
-cross_state_bwd_kernel(const __half* __restrict__ k, const __half* __restrict__ v,
-                       const uint8_t* __restrict__ pad_mask, const float* __restrict__ d_s,
-                       const float* __restrict__ d_z, __half* __restrict__ gk, __half* __restrict__ gv,
-                       int64_t T, int BH, int H) {
-  extern __shared__ __align__(16) float sm[];
-  float* Ks = sm;
-  float* Ds = Ks + kC * kLK;
-  float* Vs = Ds + kC * kLK;
-  float* Os = Vs + kC * kLD;
-  float* dSt = Os + kC * kLD;
-  float* dzs = dSt + kK * kLD;
-  float* keep = dzs + kK;      // 1 = real key, 0 = padding
-  const int bh = blockIdx.y;
-  const int64_t t0 = (int64_t)blockIdx.x * kC;
-  const int valid = (int)min((int64_t)kC, T - t0);
-  load_state(dSt, dzs, d_s + (size_t)bh * kK * kD, d_z + (size_t)bh * kK);
-  stage_rows<kK>(Ks, kLK, k + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, valid);
-  stage_rows<kD>(Vs, kLD, v + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, valid);
-  if (threadIdx.x < kC) {
-    const int r = threadIdx.x;
-    keep[r] = (r < valid && !(pad_mask && pad_mask[(size_t)(bh / H) * T + t0 + r])) ? 1.f : 0.f;
-  }
-  __syncthreads();
-  tile_gemm<4, 8>(kC, kK, kD,
-                  [&](int r, int l) { return Vs[r * kLD + l]; },
-                  [&](int l, int c) { return dSt[c * kLD + l]; },
-                  [&](int r, int c, float a) { Ds[r * kLK + c] = keep[r] * (a + dzs[c]); });
-  tile_gemm<4, 4>(kC, kD, kK,
-                  [&](int r, int l) { return Ks[r * kLK + l]; },
-                  [&](int l, int j) { return dSt[l * kLD + j]; },
-                  [&](int r, int j, float a) { Os[r * kLD + j] = keep[r] * a; });
-  __syncthreads();
-  unstage_rows<kK>(gk + ((size_t)t0 * BH + bh) * kK, (size_t)BH * kK, Ds, kLK, valid);
-  unstage_rows<kD>(gv + ((size_t)t0 * BH + bh) * kD, (size_t)BH * kD, Os, kLD, valid);
-}
-
-// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-constexpr size_t kSmemState = (size_t)(kC * kLK + kC * kLD + kK * kLD + kK) * sizeof(float);
-constexpr size_t kSmemXqFwd = (size_t)(kC * kLK + kC * kLD + kK * kLD + kK + kC) * sizeof(float);
-constexpr size_t kSmemXqBwd = (size_t)(2 * kC * kLK + 2 * kC * kLD + 2 * kK * kLD + 2 * kK + 2 * kC) * sizeof(float);
-constexpr size_t kSmemXsBwd = (size_t)(2 * kC * kLK + 2 * kC * kLD + kK * kLD + kK + kC) * sizeof(float);
-
-template <class Kern>
-static int opt_in_smem(Kern kern, size_t bytes, const char* what) {
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  if (e != cudaSuccess) return fail((int)e, "%s: cannot reserve %zu bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
-  return 0;
-}
-
 static int check_geometry(const char* what, int64_t T, int BH, int K, int d) {
   RFA_REQUIRE(T >= 0 && BH > 0, RFA_EINVAL, "%s: T=%lld BH=%d", what, (long long)T, BH);
   RFA_REQUIRE(K == kK && d == kD, RFA_EUNSUPPORTED, "%s: only K=%d, d=%d is built (got K=%d d=%d)", what, kK, kD, K, d);
@@ -311,10 +125,7 @@ static int scan_launch(float* seg, const float* carry, float* total, int BH, int
 // Forward states entering every segment -> ws.s_seg / ws.z_seg (nseg > 1 only).
 static int build_segment_states(const __half* k, const __half* v, const float* s_in, const float* z_in,
                                 const CausalWs& ws, const CausalPlan& p, int64_t T, int BH, cudaStream_t st) {
-  if (int e = opt_in_smem(segment_state_kernel, kSmemState, "segment_state")) return e;
-  segment_state_kernel<<<dim3(BH, p.nseg), kThreads, kSmemState, st>>>(k, v, nullptr, ws.s_seg, ws.z_seg, T, BH, 1,
-                                                                      p.nseg, p.tseg);
-  if (int e = check_launch("segment_state")) return e;
+  if (int e = launch_cross_state_fwd_tc(k, v, nullptr, ws.s_seg, ws.z_seg, T, BH, 1, p.nseg, p.tseg, st)) return e;
   if (int e = scan_launch(ws.s_seg, s_in, nullptr, BH, p.nseg, kK * kD, 0, 1, st)) return e;
   return scan_launch(ws.z_seg, z_in, nullptr, BH, p.nseg, kK, 0, 1, st);
 }
@@ -454,12 +265,13 @@ extern "C" int rfa_cross_state_fwd(const void* phi_k, const void* v, const uint8
   RFA_REQUIRE(phi_k && v && s && z, RFA_EINVAL, "cross_state_fwd: null pointer");
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(s) && aligned16(z), RFA_EALIGN,
               "cross_state_fwd: 16-byte alignment required");
-  cudaStream_t st = as_stream(stream);
-  if (int e = opt_in_smem(segment_state_kernel, kSmemState, "cross_state_fwd")) return e;
-  const int64_t tseg = ((T + kC - 1) / kC) * kC;
-  segment_state_kernel<<<dim3(BH, 1), kThreads, kSmemState, st>>>((const __half*)phi_k, (const __half*)v, pad_mask, s, z, T,
-                                                                  BH, H, 1, tseg > 0 ? tseg : kC);
-  return check_launch("rfa_cross_state_fwd");
+  if (T == 0) {
+    cudaMemsetAsync(s, 0, (size_t)BH * kK * kD * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(z, 0, (size_t)BH * kK * sizeof(float), as_stream(stream));
+    return check_launch("rfa_cross_state_fwd(T=0)");
+  }
+  const int64_t tseg = ((T + kSegAlign - 1) / kSegAlign) * kSegAlign;
+  return launch_cross_state_fwd_tc((const __half*)phi_k, (const __half*)v, pad_mask, s, z, T, BH, H, 1, tseg, as_stream(stream));
 }
 
 extern "C" int rfa_cross_state_bwd(const void* phi_k, const void* v, const uint8_t* pad_mask, const float* d_s,
@@ -472,11 +284,8 @@ extern "C" int rfa_cross_state_bwd(const void* phi_k, const void* v, const uint8
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(d_s) && aligned16(d_z) && aligned16(g_phi_k) && aligned16(g_v),
               RFA_EALIGN, "cross_state_bwd: 16-byte alignment required");
   if (T == 0) return 0;
-  if (int e = opt_in_smem(cross_state_bwd_kernel, kSmemXsBwd, "cross_state_bwd")) return e;
-  const unsigned chunks = (unsigned)((T + kC - 1) / kC);
-  cross_state_bwd_kernel<<<dim3(chunks, BH), kThreads, kSmemXsBwd, as_stream(stream)>>>(
-      (const __half*)phi_k, (const __half*)v, pad_mask, d_s, d_z, (__half*)g_phi_k, (__half*)g_v, T, BH, H);
-  return check_launch("rfa_cross_state_bwd");
+  return launch_cross_state_bwd_tc((const __half*)phi_k, (const __half*)v, pad_mask, d_s, d_z, (__half*)g_phi_k, (__half*)g_v, T, BH,
+                                   H, as_stream(stream));
 }
 
 extern "C" int rfa_cross_query_fwd(const void* phi_q, const float* s, const float* z, void* out,
@@ -486,11 +295,7 @@ extern "C" int rfa_cross_query_fwd(const void* phi_q, const float* s, const floa
   RFA_REQUIRE(aligned16(phi_q) && aligned16(s) && aligned16(z) && aligned16(out), RFA_EALIGN,
               "cross_query_fwd: 16-byte alignment required");
   if (T == 0) return 0;
-  if (int e = opt_in_smem(cross_query_fwd_kernel, kSmemXqFwd, "cross_query_fwd")) return e;
-  const unsigned chunks = (unsigned)((T + kC - 1) / kC);
-  cross_query_fwd_kernel<<<dim3(chunks, BH), kThreads, kSmemXqFwd, as_stream(stream)>>>((const __half*)phi_q, s, z,
-                                                                                       (__half*)out, T, BH);
-  return check_launch("rfa_cross_query_fwd");
+  return launch_cross_query_fwd_tc((const __half*)phi_q, s, z, (__half*)out, T, BH, as_stream(stream));
 }
 
 extern "C" int rfa_cross_query_bwd(const void* phi_q, const float* s, const float* z, const void* g,
@@ -500,8 +305,10 @@ extern "C" int rfa_cross_query_bwd(const void* phi_q, const float* s, const floa
   RFA_REQUIRE(phi_q && s && z && g && g_phi_q && d_s && d_z, RFA_EINVAL, "cross_query_bwd: null pointer");
   RFA_REQUIRE(aligned16(phi_q) && aligned16(s) && aligned16(z) && aligned16(g) && aligned16(g_phi_q) && aligned16(d_s) &&
                   aligned16(d_z), RFA_EALIGN, "cross_query_bwd: 16-byte alignment required");
-  if (int e = opt_in_smem(cross_query_bwd_kernel, kSmemXqBwd, "cross_query_bwd")) return e;
-  cross_query_bwd_kernel<<<BH, kThreads, kSmemXqBwd, as_stream(stream)>>>((const __half*)phi_q, s, z, (const __half*)g,
-                                                                        (__half*)g_phi_q, d_s, d_z, T, BH);
-  return check_launch("rfa_cross_query_bwd");
+  if (T == 0) {
+    cudaMemsetAsync(d_s, 0, (size_t)BH * kK * kD * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(d_z, 0, (size_t)BH * kK * sizeof(float), as_stream(stream));
+    return check_launch("rfa_cross_query_bwd(T=0)");
+  }
+  return launch_cross_query_bwd_tc((const __half*)phi_q, s, z, (const __half*)g, (__half*)g_phi_q, d_s, d_z, T, BH, as_stream(stream));
 }
