@@ -27,6 +27,7 @@ int tc_status_causal_fwd();
 int tc_status_causal_bwd();
 int tc_status_causal_bwd_kv();
 int tc_status_cross();
+int tc_status_feature_map();
 
 }  // namespace rfa
 
@@ -40,6 +41,7 @@ extern "C" int rfa_debug_status(void) {
   if (b) return b < 0 ? b : 200 + b;
   if (const int kv = rfa::tc_status_causal_bwd_kv()) return kv < 0 ? kv : 300 + kv;
   if (const int x = rfa::tc_status_cross()) return x < 0 ? x : 400 + x;
+  if (const int f2 = rfa::tc_status_feature_map()) return f2 < 0 ? f2 : 500 + f2;
   return 0;
 }
 

@@ -190,6 +190,9 @@ feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w,
   }
 }
 
+// tensor-core forward for fp16 rows with head_dim = proj_dim = 64 (feature_map_tc.cu)
+int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int64_t rows, int H, float scale, int sms, cudaStream_t st);
+
 static int fm_check(const void* x, const float* w, int64_t rows, int H, int d, int D) {
   RFA_REQUIRE(x && w, RFA_EINVAL, "feature_map: null pointer");
   RFA_REQUIRE(rows >= 0 && H > 0 && d > 0 && D > 0, RFA_EINVAL, "feature_map: rows=%lld H=%d d=%d D=%d",
@@ -227,6 +230,12 @@ extern "C" int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w, v
   RFA_REQUIRE(phi, RFA_EINVAL, "feature_map_fwd: null output");
   RFA_REQUIRE(aligned16(x) && aligned16(w) && aligned16(phi), RFA_EALIGN, "feature_map_fwd: 16-byte alignment required");
   if (rows == 0) return 0;
+  if (x_dtype == RFA_F16 && phi_dtype == RFA_F16 && d == 64 && D == 64) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return launch_feature_map_fwd_tc((const __half*)x, w, (__half*)phi, rows, H, scale, sms, as_stream(stream));
+  }
   size_t smem = 0;
   const int R = fm_pick_rows(D, d, false, false, &smem);
   RFA_REQUIRE(R > 0, RFA_EUNSUPPORTED, "feature_map_fwd: shared memory budget exceeded");
