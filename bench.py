@@ -268,6 +268,70 @@ def extras(device, stream, hbm):
     return out
 
 
+def run_long(args, rank, local_rank, world):
+    """Long-sequence causal fwd+bwd: batch 1, heads 32, seq 131072, sharded over heads at 2 GPUs and over
+    heads x sequence at 4 and 8 (sequence shards exchange boundary states: rfa_b200.sharded)."""
+    import torch.distributed as dist
+    from rfa_b200 import sharded
+    Hh, Tt = 32, 131072
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    g_h = 2 if world >= 2 else 1
+    g_s = world // g_h
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        for i in range(g_h):
+            grp = dist.new_group(list(range(i * g_s, (i + 1) * g_s)))
+            if rank // g_s == i:
+                group = grp
+    h_loc = Hh // g_h
+    lo, hi = sharded.shard_bounds(Tt, g_s, rank % g_s)
+    t_loc = hi - lo
+    gen = torch.Generator(device=device).manual_seed(4 + rank)
+    mk = lambda w, s: (torch.rand(t_loc, h_loc, w, device=device, generator=gen) * s).half()
+    q, k = mk(K_FEAT, 0.2).requires_grad_(True), mk(K_FEAT, 0.2).requires_grad_(True)
+    v = (torch.randn(t_loc, h_loc, D_HEAD, device=device, generator=gen)).half().requires_grad_(True)
+    up = torch.randn(t_loc, h_loc, D_HEAD, device=device, generator=gen).half()
+    stream = torch.cuda.current_stream()
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        out = sharded.sequence_sharded_causal_rfa(q, k, v, group)
+        out.backward(up)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    with ClockSampler(local_rank) as clk:
+        ms = timed(step, args.steps, stream)
+        barrier()
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        hbm, peak_src = peaks()
+        nbytes = Tt * Hh * BYTES_PATH
+        print(json.dumps({
+            "metric": "long_causal_rfa_fwd_bwd_tokens_per_s", "value": Tt / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"causal RFA fwd+bwd, B1 H{Hh} T{Tt} d64 D64 fp16", "heads_x_sequence_shards": [g_h, g_s],
+                       "l2": "9.1 GB per step, far larger than L2"},
+            "clocks": clk.summary, "gpu_launches": None,
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9 / world, "peak": hbm, "unit": "GB/s per GPU",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / world / hbm, "peak_source": peak_src, "traffic": None}}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,6 +339,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--workload", default="headline", choices=["headline", "long"],
+                    help="headline = B8 H16 T2048 (the metric's config); long = B1 H32 T131072, sequence-sharded")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -283,6 +349,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "long":
+        run_long(args, rank, local_rank, world)
         return
 
     import torch.distributed as dist

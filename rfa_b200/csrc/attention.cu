@@ -47,7 +47,7 @@ int launch_cross_state_bwd_tc(const __half* k, const __half* v, const uint8_t* p
 static CausalPlan plan_causal(int64_t T, int BH) {
   CausalPlan p{1, ((T + kSegAlign - 1) / kSegAlign) * kSegAlign};
   if (BH >= 120 || T < 1024) return p;
-  int64_t want = (148 + BH - 1) / BH;           // CTAs to cover the SMs
+  int64_t want = 148 / BH;                      // segments per head that still fit one wave of 148 SMs
   int64_t maxseg = T / 512;                     // keep segments >= 512 tokens
   int64_t n = want < maxseg ? want : maxseg;
   if (n < 1) n = 1;

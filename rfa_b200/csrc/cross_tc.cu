@@ -552,8 +552,10 @@ static int x_opt_in(Kern kern, uint32_t bytes, const char* what) {
 int launch_cross_state_fwd_tc(const __half* k, const __half* v, const uint8_t* pad_mask, float* s, float* z, int64_t T, int BH,
                               int H, int nseg, int64_t tseg, cudaStream_t st) {
   CUtensorMap tk, tv;
-  if (make_tmap_rows(&tk, k, T, BH, kK, kTC) || make_tmap_rows(&tv, v, T, BH, kD, kTC))
-    return fail(RFA_EDEVICE, "cross_state_fwd: cuTensorMapEncodeTiled failed or is unavailable");
+  const int r1 = make_tmap_rows(&tk, k, T, BH, kK, kTC), r2 = make_tmap_rows(&tv, v, T, BH, kD, kTC);
+  if (r1 || r2)
+    return fail(RFA_EDEVICE, "cross_state_fwd: cuTensorMapEncodeTiled failed or is unavailable (%d, %d; k=%p v=%p T=%lld BH=%d)", r1, r2,
+                (const void*)k, (const void*)v, (long long)T, BH);
   if (int e = x_opt_in(cross_state_fwd_tc_kernel, xs::kSmem, "cross_state_fwd")) return e;
   cross_state_fwd_tc_kernel<<<dim3(BH, nseg), kXThreads, xs::kSmem, st>>>(tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
   return check_launch("rfa_cross_state_fwd");

@@ -237,6 +237,14 @@ inline PFN_encodeTiled get_encode_tiled() {
 inline int make_tmap_rows(CUtensorMap* m, const void* base, uint64_t T, uint64_t BH, uint64_t width, uint32_t box_rows) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return -1;
+  // The encoder is a driver call and needs a context current on the calling thread.  A thread that has
+  // only ever been handed pooled memory (an autograd worker, say) may not have one bound yet: any
+  // runtime call that touches the device binds the primary context.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[3] = {width, BH, T};
   cuuint64_t strides[2] = {width * 2, BH * width * 2};
   cuuint32_t box[3] = {64, 1, box_rows};

@@ -30,6 +30,8 @@ from torch import Tensor
 def exclusive_scan_over_ranks(local: Tensor, group=None, reverse: bool = False) -> Tensor:
     """Sum of ``local`` over the ranks strictly before (``reverse``: strictly after) this
     rank in ``group``.  One all-gather of the per-rank tensors, then a local sum."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return torch.zeros_like(local)            # single process: nothing comes before or after
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     if world == 1:

@@ -278,3 +278,17 @@ def test_bad_arguments_are_rejected_without_launching(dev):
         ops.causal_fwd(q.cpu(), q.cpu(), v.cpu())
     q = torch.zeros(0, 2, 128, dtype=torch.half, device=dev)
     assert ops.causal_fwd(q, q, torch.zeros(0, 2, 64, dtype=torch.half, device=dev)).shape == (0, 2, 64)
+
+
+def test_causal_long_sequence_late_tokens(dev):
+    """T = 32768 on real features: denominators reach ~7500, g/den ~1e-4 (fp16 subnormal range).  The
+    late tokens are where rounding would show first; they are held to the same gate."""
+    T, BH = 32768, 1
+    q, k, v, g = feats(T, BH, seed=77)
+    out, gq, gk, gv = run_causal(dev, q, k, v, g)
+    ro = O.causal_forward(q.double(), k.double(), v.double(), block=256)
+    rq, rk, rv = O.causal_backward(q.double(), k.double(), v.double(), g.double(), block=256)
+    tail = slice(T - T // 8, T)
+    for name, a, b in (("out", out, ro), ("gq", gq, rq), ("gk", gk, rk), ("gv", gv, rv)):
+        assert_close(a, b, name)
+        assert_close(a[tail], b[tail], name + " (last eighth)")
