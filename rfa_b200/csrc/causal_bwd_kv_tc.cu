@@ -10,15 +10,29 @@
 // The score matrices are computed TRANSPOSED (keys on the TMEM lanes) so that their fp16
 // versions can stay in tensor memory as the A operands of the dK / dV products.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 score group
-// (scales g in place, packs Pt and dAt), warps 6..9 output/state group (grad_k, grad_v,
-// state export, dz).  The score group of chunk i+1 overlaps the output group of chunk i.
-// All waits are bounded.
+// Warp roles (352 threads): warp 0 TMA producer, warps 1 and 10 MMA issuers, warps 2..5 score
+// group (scales g in place, packs Pt and dAt), warps 6..9 output/state group (grad_k, grad_v,
+// state export, dz).  Issuing one tcgen05.mma costs the issuing thread about as long as the
+// tensor pipe needs to execute it (N <= 128), so the 48 MMAs of a chunk are split over two
+// issuers: A (At, dAt, dK) and B (dV, dS).  The products that read the exported state tile are
+// issued first in a chunk and the state update right after g is scaled, which keeps the serial
+// chain of the scan (state MMA -> export -> next chunk's readers) short.  All waits are bounded.
+#include <type_traits>
+
 #include "tc_common.cuh"
 
 namespace rfa {
 
-constexpr int kKvThreads = 320;
+constexpr int kKvThreads = 352;
+
+#ifdef RFA_TRACE
+// tuning builds only: switch parts of the kernel off (results are then wrong) to see what the chain is sensitive to
+static __device__ int g_kv_dbg;
+extern "C" int rfa_trace_set_dbg_kv(int v) { return (int)cudaMemcpyToSymbol(g_kv_dbg, &v, sizeof(int)); }
+#define KV_DBG(bit) ((kv_dbg >> (bit)) & 1)
+#else
+#define KV_DBG(bit) 0
+#endif
 
 constexpr uint32_t kvQ = 0, kvK = 2 * kBox, kvV = 4 * kBox, kvG = 5 * kBox, kvStage = 6 * kBox;   // 98304 per stage
 constexpr uint32_t kvS = 2 * kvStage;            // dS as an operand: [128 k][64 n] fp16, swizzled
@@ -29,7 +43,8 @@ constexpr uint32_t kvSmem = kvBar + 256 + 1024;
 
 constexpr uint32_t kvColAt = 0, kvColDAt = 128, kvColDK = 256, kvColDV = 384, kvColDS = 448;
 enum { vFull = 0, vEmpty = 2, vAt = 4, vG = 5, vDAt = 7, vP = 8, vDA16 = 9, vDK = 10, vDV = 11, vDKFree = 12, vDVFree = 13,
-       vS = 14, vSt = 15, vY = 16, vNum = 17 };
+       vS = 14, vSt = 15, vY = 16, vSR = 17, vNum = 18 };
+// vSR: both issuers have finished reading the exported state tile (one commit each per chunk).
 // vG is one barrier per stage: the output group waits on it late in a chunk, when the score group may already
 // have completed the next chunk's phase; with one barrier per stage a waiter is never two phases behind.
 
@@ -61,7 +76,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     mbar_init(&bars[vAt], 1); mbar_init(&bars[vG], 128); mbar_init(&bars[vG + 1], 128); mbar_init(&bars[vDAt], 1); mbar_init(&bars[vP], 128);
     mbar_init(&bars[vDA16], 128); mbar_init(&bars[vDK], 1); mbar_init(&bars[vDV], 1);
     mbar_init(&bars[vDKFree], 128); mbar_init(&bars[vDVFree], 128); mbar_init(&bars[vS], 1);
-    mbar_init(&bars[vSt], 128); mbar_init(&bars[vY], 128);
+    mbar_init(&bars[vSt], 128); mbar_init(&bars[vY], 128); mbar_init(&bars[vSR], 2);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
     tma_prefetch_desc(&tm_gk); tma_prefetch_desc(&tm_gv);
@@ -71,6 +86,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+#ifdef RFA_TRACE
+  const int kv_dbg = g_kv_dbg;
+#endif
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
@@ -84,6 +102,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const int t0 = (int)(t_begin + (int64_t)(nchunk - 1 - i) * kTC);
         uint64_t* fb = &bars[vFull + st];
         RFA_TRACE_EV(2, i);
+        if (KV_DBG(2)) { mbar_arrive(fb); continue; }
         mbar_arrive_expect_tx(fb, kvStage);
         tma_load_3d(base + kvG, &tm_g, fb, 0, bh, t0);
         tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
@@ -93,94 +112,97 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tma_load_3d(base + kvV, &tm_v, fb, 0, bh, t0);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
+      constexpr uint32_t lead = 1u;
       RFA_TRACE_DECL(1)
       constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // K Q^T ; V gs^T ; V dS^T
       constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dAt Q            (B MN-major)
       constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // Pt gs ; K dS     (B MN-major)
       constexpr uint32_t idMM64 = umma_idesc_f16(128, 64, true, true);    // Q^T gs           (A, B MN-major)
-      // operand descriptors per stage (the shared-memory layout is static); a k-step is an add
-      uint64_t dQk[2], dQm[2], dKk[2], dVk[2], dGk[2], dGm[2];
-#pragma unroll
-      for (int s2 = 0; s2 < 2; ++s2) {
-        const uint32_t sb = sbase + s2 * kvStage;
-        dQk[s2] = umma_smem_desc(sb + kvQ, 0, 1024, kSwizzle128B);       // Q  K-major  [t][k]
-        dQm[s2] = umma_smem_desc(sb + kvQ, kBox, 1024, kSwizzle128B);    // Q  MN-major (rows = contraction t)
-        dKk[s2] = umma_smem_desc(sb + kvK, 0, 1024, kSwizzle128B);       // K  K-major  [s][k]
-        dVk[s2] = umma_smem_desc(sb + kvV, 0, 1024, kSwizzle128B);       // V  K-major  [s][n]
-        dGk[s2] = umma_smem_desc(sb + kvG, 0, 1024, kSwizzle128B);       // gs K-major  [t][n]
-        dGm[s2] = umma_smem_desc(sb + kvG, kBox, 1024, kSwizzle128B);    // gs MN-major (rows = contraction t)
-      }
+      // operand descriptors of stage 0; the other stage is a constant add on the start-address field
+      const uint64_t dQk = umma_smem_desc(sbase + kvQ, 0, 1024, kSwizzle128B);       // Q  K-major  [t][k]
+      const uint64_t dQm = umma_smem_desc(sbase + kvQ, kBox, 1024, kSwizzle128B);    // Q  MN-major (rows = contraction t)
+      const uint64_t dKk = umma_smem_desc(sbase + kvK, 0, 1024, kSwizzle128B);       // K  K-major  [s][k]
+      const uint64_t dVk = umma_smem_desc(sbase + kvV, 0, 1024, kSwizzle128B);       // V  K-major  [s][n]
+      const uint64_t dGk = umma_smem_desc(sbase + kvG, 0, 1024, kSwizzle128B);       // gs K-major  [t][n]
+      const uint64_t dGm = umma_smem_desc(sbase + kvG, kBox, 1024, kSwizzle128B);    // gs MN-major (rows = contraction t)
+      constexpr uint64_t dStage = kvStage >> 4;
       const uint64_t dSk = umma_smem_desc(sbase + kvS, 0, 1024, kSwizzle128B);      // dS as [N = k rows][K = n]
       const uint64_t dSm = umma_smem_desc(sbase + kvS, kBox, 1024, kSwizzle128B);   // dS as [K = k rows][N = n]
-      auto issue_At = [&](int i) {                                        // At = K Q^T
-        const int s2 = i & 1;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma_ss(tmem + kvColAt, dKk[s2] + kstep_kmajor(j, kBox), dQk[s2] + kstep_kmajor(j, kBox), idKK, j > 0);
-        umma_commit(&bars[vAt]);
-      };
-      bool ok = true;
-      if (nchunk > 0) {
-        ok = mbar_wait(&bars[vFull], 0);
-        if (ok) { tc_fence_after_sync(); issue_At(0); } else tc_fail(2);
-      }
-      for (int i = 0; ok && i < nchunk; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = i & 1;
-        RFA_TRACE_EV(10, i);
-        if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(3); break; }
-        RFA_TRACE_EV(11, i);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 4; ++j)              // dAt = V gs^T
-          umma_ss(tmem + kvColDAt, dVk[st] + kstep_kmajor(j, kBox), dGk[st] + kstep_kmajor(j, kBox), idKK, j > 0);
-        umma_commit(&bars[vDAt]);
-        RFA_TRACE_EV(12, i);
-        if (!mbar_wait(&bars[vP], ph)) { tc_fail(4); break; }
-        RFA_TRACE_EV(13, i);
-        if (!mbar_wait(&bars[vSt], ph)) { tc_fail(5); break; }
-        if (i > 0 && !mbar_wait(&bars[vDVFree], (i - 1) & 1)) { tc_fail(6); break; }
-        RFA_TRACE_EV(14, i);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // dV = Pt gs
-          umma_ts(tmem + kvColDV, tmem + kvColAt + j * 8, dGm[st] + kstep_mnmajor(j), idKM64, j > 0);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // dV += K dS_next     (dS tile as [K = k rows][N = n])
-          umma_ss(tmem + kvColDV, dKk[st] + kstep_kmajor(j, kBox), dSm + kstep_mnmajor(j), idKM64, 1);
-        umma_commit(&bars[vDV]);
-        // the next chunk's scores as soon as its tiles are in (Pt of this chunk has been consumed above)
-        bool next_issued = (i + 1 >= nchunk);
-        if (!next_issued && mbar_try_wait(&bars[vFull + ((i + 1) & 1)], ((i + 1) >> 1) & 1)) {
-          tc_fence_after_sync();
-          issue_At(i + 1);
-          next_issued = true;
+      if (warp == 1) {
+        // ---- issuer A: At (scores of the next chunk), dAt, dK
+        auto issue_At = [&](int s2) {                                     // At = K Q^T
+          umma_chain_ss<8, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColAt, dKk + s2 * dStage, dQk + s2 * dStage, idKK, 0);
+          umma_commit(&bars[vAt]);
+        };
+        bool ok = true;
+        if (nchunk > 0) {
+          ok = mbar_wait(&bars[vFull], 0);
+          if (ok) { tc_fence_after_sync(); issue_At(0); } else tc_fail(2);
         }
-        RFA_TRACE_EV(15, i);
-        if (!mbar_wait(&bars[vDA16], ph)) { tc_fail(7); break; }
-        RFA_TRACE_EV(16, i);
-        if (i > 0 && !mbar_wait(&bars[vDKFree], (i - 1) & 1)) { tc_fail(8); break; }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // dK = dAt Q
-          umma_ts(tmem + kvColDK, tmem + kvColDAt + j * 8, dQm[st] + kstep_mnmajor(j), idKM128, j > 0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)              // dK += V dS_next^T   (dS tile as [N = k rows][K = n])
-          umma_ss(tmem + kvColDK, dVk[st] + kstep_kmajor(j, kBox), dSk + kstep_kmajor(j, kBox), idKK, 1);
-        umma_commit(&bars[vDK]);
-        const bool fresh = (i == 0 && ds_in == nullptr);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // dS += Q^T gs
-          umma_ss(tmem + kvColDS, dQm[st] + kstep_mnmajor(j), dGm[st] + kstep_mnmajor(j), idMM64, (fresh && j == 0) ? 0 : 1);
-        umma_commit(&bars[vS]);
-        RFA_TRACE_EV(17, i);
-        if (!next_issued) {
-          if (!mbar_wait(&bars[vFull + ((i + 1) & 1)], ((i + 1) >> 1) & 1)) { tc_fail(9); break; }
+#pragma unroll 1
+        for (int i = 0; ok && i < nchunk; ++i) {
+          const int st = i & 1;
+          const uint64_t so = (uint64_t)st * dStage;
+          const uint32_t ph = i & 1;
+          // dK = V dS_next^T first: it reads the state tile, which the output group wants to overwrite
+          RFA_TRACE_EV(10, i);
+          if (!mbar_wait(&bars[vSt], ph)) { tc_fail(3); break; }
+          if (i > 0 && !mbar_wait(&bars[vDKFree], (i - 1) & 1)) { tc_fail(4); break; }
           tc_fence_after_sync();
-          issue_At(i + 1);
+          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDK, dVk + so, dSk, idKK, 0);
+          umma_commit(&bars[vSR]);
+          RFA_TRACE_EV(11, i);
+          if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(5); break; }
+          tc_fence_after_sync();
+          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDAt, dVk + so, dGk + so, idKK, 0);          // dAt = V gs^T
+          umma_commit(&bars[vDAt]);
+          RFA_TRACE_EV(12, i);
+          // the next chunk's scores as soon as its tiles are in and Pt of this chunk has been consumed (dV complete)
+          bool next_issued = (i + 1 >= nchunk);
+          if (!next_issued && mbar_test(&bars[vFull + (st ^ 1)], ((i + 1) >> 1) & 1) && mbar_test(&bars[vDV], ph)) {
+            tc_fence_after_sync();
+            issue_At(st ^ 1);
+            next_issued = true;
+          }
+          if (!mbar_wait(&bars[vDA16], ph)) { tc_fail(6); break; }
+          RFA_TRACE_EV(13, i);
+          tc_fence_after_sync();
+          umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + kvColDK, tmem + kvColDAt, dQm + so, idKM128, 1);                // dK += dAt Q
+          umma_commit(&bars[vDK]);
+          RFA_TRACE_EV(14, i);
+          if (!next_issued) {
+            if (!mbar_wait(&bars[vFull + (st ^ 1)], ((i + 1) >> 1) & 1)) { tc_fail(7); break; }
+            if (!mbar_wait(&bars[vDV], ph)) { tc_fail(8); break; }
+            tc_fence_after_sync();
+            issue_At(st ^ 1);
+          }
+          RFA_TRACE_EV(15, i);
+        }
+      } else {
+        // ---- issuer B: dV and the state update
+#pragma unroll 1
+        for (int i = 0; i < nchunk; ++i) {
+          const int st = i & 1;
+          const uint64_t so = (uint64_t)st * dStage;
+          const uint32_t ph = i & 1;
+          if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(20); break; }
+          if (!mbar_wait(&bars[vSt], ph)) { tc_fail(21); break; }
+          if (i > 0 && !mbar_wait(&bars[vDVFree], (i - 1) & 1)) { tc_fail(22); break; }
+          tc_fence_after_sync();
+          umma_chain_ss<8, kStepK, kBlockK, kStepMN, kBlockMN>(lead, tmem + kvColDV, dKk + so, dSm, idKM64, 0);           // dV = K dS_next
+          umma_commit(&bars[vSR]);
+          if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(23); break; }
+          tc_fence_after_sync();
+          const bool fresh = (i == 0 && ds_in == nullptr);
+          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + kvColDS, dQm + so, dGm + so, idMM64, fresh ? 0u : 1u);   // dS += Q^T gs
+          umma_commit(&bars[vS]);
+          if (!mbar_wait(&bars[vP], ph)) { tc_fail(24); break; }
+          tc_fence_after_sync();
+          umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + kvColDV, tmem + kvColAt, dGm + so, idKM64, 1);                  // dV += Pt gs
+          umma_commit(&bars[vDV]);
         }
       }
     }
@@ -205,7 +227,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (warp == 5 && lane == 0) RFA_TRACE_EV(20, i);
       if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
       if (warp == 5 && lane == 0) RFA_TRACE_EV(21, i);
-      {
+      if (!KV_DBG(0) && !KV_DBG(5)) {
         unsigned char* grow = stage + kvG;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
@@ -225,9 +247,10 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
       if (warp == 5 && lane == 0) RFA_TRACE_EV(23, i);
       tc_fence_after_sync();
-#pragma unroll
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
+        if (KV_DBG(0)) continue;
         if (piece >= quarter) {
           uint32_t a[32];
           tmem_ld32(tmem + lane_addr + kvColAt + piece * 32, a);
@@ -256,9 +279,10 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
       if (warp == 5 && lane == 0) RFA_TRACE_EV(25, i);
       tc_fence_after_sync();
-#pragma unroll
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
+        if (KV_DBG(0)) continue;
         if (piece >= quarter) {
           uint32_t a[32];
           tmem_ld32(tmem + lane_addr + kvColDAt + piece * 32, a);
@@ -321,13 +345,15 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       const float* gzs = gz_buf + (i & 1) * 128;
       // dzs of the previous chunk is final for every thread
       if (!epi_sync(&bars[vY], y_phase)) { tc_fail(14); ok = false; break; }
-      // ---- all MMAs of this chunk are complete once the state MMA is: K and V tiles become staging
+      // ---- the state update is complete and both issuers have finished reading the old state tile
       if (ytid == 0) RFA_TRACE_EV(30, i);
       if (!mbar_wait(&bars[vS], ph)) { tc_fail(15); ok = false; break; }
+      if (!mbar_wait(&bars[vSR], ph)) { tc_fail(18); ok = false; break; }
       if (ytid == 0) RFA_TRACE_EV(31, i);
       tc_fence_after_sync();
       // ---- reverse state after this chunk -> fp16 operand tile (the serial chain of the scan)
-      if (i + 1 < nchunk) {
+      if (i + 1 < nchunk && KV_DBG(1)) { tc_fence_before_sync(); mbar_arrive(&bars[vSt]); }
+      if (i + 1 < nchunk && !KV_DBG(1)) {
         uint32_t r[64];
         tmem_ld32(tmem + lane_addr + kvColDS, r);
         tmem_ld32(tmem + lane_addr + kvColDS + 32, r + 32);
@@ -339,18 +365,26 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       if (ytid == 0) RFA_TRACE_EV(32, i);
       // ---- grad_v -> V tile
-      {
+      if (KV_DBG(1)) { mbar_arrive(&bars[vDVFree]); mbar_arrive(&bars[vDKFree]); }
+      if (!KV_DBG(1)) {
         uint32_t r[64];
+        if (!mbar_wait(&bars[vDV], ph)) { tc_fail(13); ok = false; break; }
+        tc_fence_after_sync();
         tmem_ld32(tmem + lane_addr + kvColDV, r);
         tmem_ld32(tmem + lane_addr + kvColDV + 32, r + 32);
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive(&bars[vDVFree]);
+        // issuer A's last product of the chunk is complete: nothing reads the V, K and Q tiles any more (issuer B
+        // finished with vDV), so the V and K tiles become staging
+        if (!mbar_wait(&bars[vDK], ph)) { tc_fail(19); ok = false; break; }
+        tc_fence_after_sync();
         store_state_row(stage + kvV, row, r);
       }
       // ---- grad_k = dK + dz_next -> K tile
-#pragma unroll
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
+        if (KV_DBG(1)) continue;
         uint32_t a[32];
         tmem_ld32(tmem + lane_addr + kvColDK + piece * 32, a);
         tmem_ld_wait();
@@ -370,7 +404,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       fence_async_smem();
       if (ytid == 0) RFA_TRACE_EV(33, i);
       if (!epi_sync(&bars[vY], y_phase)) { tc_fail(16); ok = false; break; }   // staging complete; dzs reads done
-      if (ytid == 0) {
+      if (ytid == 0 && !KV_DBG(1) && !KV_DBG(4)) {
         tma_store_3d(&tm_gk, stage + kvK, 0, bh, (int)t0);
         tma_store_3d(&tm_gk, stage + kvK + kBox, 64, bh, (int)t0);
         tma_store_3d(&tm_gv, stage + kvV, 0, bh, (int)t0);
@@ -378,7 +412,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       // ---- dz += Q^T gz   (vG completed long ago; waiting on it here orders this thread after the writes of gz)
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
-      dzs[row] += column_sum2(stage + kvQ, quarter, lane, gzs);
+      if (!KV_DBG(1)) dzs[row] += column_sum2(stage + kvQ, quarter, lane, gzs);
       if (ytid == 0) RFA_TRACE_EV(34, i);
       if (ytid == 0) tma_store_wait_read<0>();
       if (ytid == 0) RFA_TRACE_EV(35, i);

@@ -177,7 +177,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // scores of chunk c + 1 as soon as its tiles are in (its buffer was freed by the dQ product of chunk
         // c - 1) -- but without blocking: this chunk must not wait for the next chunk's load
         bool scores_issued = (c + 1 >= nchunk) || c == 0;
-        if (!scores_issued && mbar_try_wait(&bars[qFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
+        if (!scores_issued && mbar_test(&bars[qFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
           tc_fence_after_sync();
           issue_scores(Other{});
           scores_issued = true;

@@ -167,7 +167,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // next chunk's scores as early as its Q, K are there, so the score group never starves --
         // but never hold back this chunk's P V (and with it the release of V) for a load in flight
         bool next_issued = (c + 1 >= nchunk);
-        if (!next_issued && mbar_try_wait(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
+        if (!next_issued && mbar_test(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
           tc_fence_after_sync();
           issue_A(std::integral_constant<int, st ^ 1>{});
           next_issued = true;

@@ -66,6 +66,26 @@ __device__ __forceinline__ void trace_clock(int role, int& n, int id) {      // 
 #define RFA_TRACE_EV(id, chunk) ((void)0)
 #endif
 
+// The k-steps of one product, issued by the whole MMA warp (see umma_ss_w).  Operand k-step j sits at
+// base + (j & 3) * step + (j >> 2) * block  (descriptor units of 16 bytes): K-major two-box tiles use
+// (kStepK, kBlockK), MN-major tiles (kStepMN, kBlockMN); a packed fp16 operand in tensor memory advances
+// by 8 columns per k-step.
+constexpr uint32_t kStepK = 2, kBlockK = kBox >> 4;      // K-major operand of two 64-wide boxes
+constexpr uint32_t kStepMN = 128, kBlockMN = 512;        // MN-major operand (k-step = 16 rows of 128 bytes)
+template <int NSTEPS, uint32_t ASTEP, uint32_t ABLOCK, uint32_t BSTEP, uint32_t BBLOCK>
+__device__ __forceinline__ void umma_chain_ss(uint32_t lead, uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc_first) {
+#pragma unroll
+  for (int j = 0; j < NSTEPS; ++j)
+    umma_ss_w(lead, d_tmem, a + (uint64_t)((j & 3) * ASTEP + (j >> 2) * ABLOCK), b + (uint64_t)((j & 3) * BSTEP + (j >> 2) * BBLOCK), idesc,
+              (j > 0) ? 1u : acc_first);
+}
+template <int NSTEPS, uint32_t BSTEP, uint32_t BBLOCK>
+__device__ __forceinline__ void umma_chain_ts(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc_first) {
+#pragma unroll
+  for (int j = 0; j < NSTEPS; ++j)
+    umma_ts_w(lead, d_tmem, a_tmem + j * 8, b + (uint64_t)((j & 3) * BSTEP + (j >> 2) * BBLOCK), idesc, (j > 0) ? 1u : acc_first);
+}
+
 // Barrier among the 128 epilogue threads built on an mbarrier so that it, too, is bounded.
 __device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase) {
   mbar_arrive(bar);
