@@ -11,31 +11,36 @@
 //     S  += K^T V,  z += colsum(K);   optionally  dSseg += Q^T gs, dzseg += Q^T gz
 // S and dSseg are fp32 TMEM accumulators; z is fp32 in shared memory (CUDA-core update).
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 score group
-// (P, den/gz/gs, dA), warps 6..9 output/state group (grad_q, state export, z).  The score tile
-// A/P/N/dA is double-buffered in TMEM and the score group is software-pipelined (gs of chunk c,
-// then P of chunk c+1, then dA of chunk c) so that it always has work while the tensor pipe
-// runs the products it is waiting for.  All waits are bounded.
+// Warp roles (480 threads): warp 0 TMA producer; warps 1 and 10 MMA issuers (A: scores and N, B: dA, dQ,
+// state updates) -- issuing a tcgen05.mma costs the issuing thread about as long as the tensor pipe needs to
+// execute it, so one issuer cannot keep the pipe fed; warps 2..5 score group 1 (P, row sums, q.z); warps
+// 11..14 score group 2 (den/gz/gs, dA); warps 6..9 output/state group (grad_q, state export, z).  The score
+// tile A/P/N/dA is double-buffered in TMEM, so score group 1 works on chunk c + 1 while score group 2 and the
+// output group finish chunk c.  All waits are bounded.
 #include <type_traits>
 
 #include "tc_common.cuh"
 
 namespace rfa {
 
-constexpr int kBqThreads = 320;
+constexpr int kBqThreads = 480;
 
 constexpr uint32_t bqQ = 0, bqK = 2 * kBox, bqV = 4 * kBox, bqG = 5 * kBox, bqStage = 6 * kBox;   // 98304 per stage
 constexpr uint32_t bqS = 2 * bqStage;            // S as an operand: [128 k][64 n] fp16, swizzled
 constexpr uint32_t bqZ = bqS + kBox;             // fp32 [3][128]: z before chunk c lives in buffer c % 3 (readers of version c,
                                                  // c + 1 and the writer of version c + 2 can be active at once)
 constexpr uint32_t bqGz = bqZ + 1536;            // fp32 [2][128]: gz of chunk c's rows in buffer c & 1
-constexpr uint32_t bqBar = bqGz + 1024;
+constexpr uint32_t bqRs = bqGz + 1024;           // float2 [2][128]: (row sum of P, q.z) of chunk c's rows in buffer c & 1
+constexpr uint32_t bqBar = bqRs + 2048;
 constexpr uint32_t bqSmem = bqBar + 256 + 1024;
 
 // TMEM: two score buffers (A -> P in columns 0..63, N in columns 64..127, then dA -> fp16 dA in 0..63)
 constexpr uint32_t bqColA = 0, bqColDQ = 256, bqColS = 384, bqColDS = 448;
-enum { qFull = 0, qEmpty = 2, qA = 4, qP = 6, qN = 8, qG = 10, qDA = 12, qDA16 = 14, qZ = 16, qDQ = 18, qDQFree = 19,
-       qS = 20, qSt = 21, qY = 22, qNum = 23 };
+enum { qFull = 0, qEmpty = 2, qA = 4, qP = 6, qN = 8, qG = 10, qDA = 12, qDA16 = 14, qZ = 16, qDQ = 18, qRS = 20, qDQFree = 22,
+       qS = 23, qSt = 24, qNum = 25 };
+// Barriers that a waiter may reach late are kept per score buffer / stage (index c & 1), so that their producer
+// cannot complete two phases before the waiter looks: qDQ has two waiters (the output group and issuer A, which
+// reuses the score buffer), qRS hands (row sum, q.z) from score group 1 to score group 2.
 
 __global__ void __launch_bounds__(kBqThreads, 1)
 causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -51,6 +56,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + qNum);
   float* z_buf = reinterpret_cast<float*>(sm + bqZ);
   float* gz_buf = reinterpret_cast<float*>(sm + bqGz);
+  float2* rs_buf = reinterpret_cast<float2*>(sm + bqRs);
   const uint32_t sbase = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, seg = blockIdx.y;
@@ -72,9 +78,10 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars[qDA + i], 1);
       mbar_init(&bars[qDA16 + i], 128);
       mbar_init(&bars[qZ + i], 128);
+      mbar_init(&bars[qDQ + i], 1);
+      mbar_init(&bars[qRS + i], 128);
     }
-    mbar_init(&bars[qDQ], 1); mbar_init(&bars[qDQFree], 128); mbar_init(&bars[qS], 1);
-    mbar_init(&bars[qSt], 128); mbar_init(&bars[qY], 128);
+    mbar_init(&bars[qDQFree], 128); mbar_init(&bars[qS], 1); mbar_init(&bars[qSt], 128);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
   }
@@ -105,9 +112,10 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tma_load_3d(base + bqG, &tm_g, fb, 0, bh, t0);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
+      constexpr uint32_t lead = 1u;
       RFA_TRACE_DECL(1)
       constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // Q K^T ; gs V^T ; gs S^T
       constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // P V ; Q S        (B MN-major)
@@ -120,129 +128,95 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const uint64_t dGk = umma_smem_desc(sbase + bqG, 0, 1024, kSwizzle128B), dGm = umma_smem_desc(sbase + bqG, kBox, 1024, kSwizzle128B);
       const uint64_t dSk = umma_smem_desc(sbase + bqS, 0, 1024, kSwizzle128B);      // S as [N = k rows][K = n]
       const uint64_t dSm = umma_smem_desc(sbase + bqS, kBox, 1024, kSwizzle128B);   // S as [K = k rows][N = n]
-      // A = Q K^T of chunk c into score buffer c & 1
-      auto issue_scores = [&](auto STC) {
-        constexpr int st = decltype(STC)::value;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma_ss(tmem + bqColA + st * 128, dQk + st * kSt + kstep_kmajor(j, kBox), dKk + st * kSt + kstep_kmajor(j, kBox), idKK, j > 0);
-        umma_commit(&bars[qA + st]);
-      };
-      // N = P V + Q S of chunk c into columns 64..127 of its score buffer
-      auto issue_n = [&](auto STC, int c) -> bool {
-        constexpr int st = decltype(STC)::value;
-        RFA_TRACE_EV(10, c);
-        if (!mbar_wait(&bars[qP + st], (c >> 1) & 1)) { tc_fail(2); return false; }
-        RFA_TRACE_EV(11, c);
-        if (!mbar_wait(&bars[qSt], c & 1)) { tc_fail(3); return false; }
-        tc_fence_after_sync();
-        RFA_TRACE_EV(12, c);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma_ts(tmem + bqColA + st * 128 + 64, tmem + bqColA + st * 128 + j * 8, dVm + st * kSt + kstep_mnmajor(j), idKM64, j > 0);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma_ss(tmem + bqColA + st * 128 + 64, dQk + st * kSt + kstep_kmajor(j, kBox), dSm + kstep_mnmajor(j), idKM64, 1);
-        umma_commit(&bars[qN + st]);
-        RFA_TRACE_EV(13, c);
-        return true;
-      };
-      auto chunk = [&](auto STC, int c) -> bool {
-        constexpr int st = decltype(STC)::value;
-        using Other = std::integral_constant<int, st ^ 1>;
-        RFA_TRACE_EV(14, c);
-        if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(4); return false; }
-        RFA_TRACE_EV(15, c);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 4; ++j)              // dA = gs V^T   (contraction over d = 64)
-          umma_ss(tmem + bqColA + st * 128, dGk + st * kSt + kstep_kmajor(j, kBox), dVk + st * kSt + kstep_kmajor(j, kBox), idKK, j > 0);
-        umma_commit(&bars[qDA + st]);
-        if (c > 0 && !mbar_wait(&bars[qDQFree], (c - 1) & 1)) { tc_fail(5); return false; }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 4; ++j)              // dQ = gs S_prev^T   (S tile as [N = k rows][K = n])
-          umma_ss(tmem + bqColDQ, dGk + st * kSt + kstep_kmajor(j, kBox), dSk + kstep_kmajor(j, kBox), idKK, j > 0);
-        const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // S += K^T V   (after the last read of the S tile for this chunk)
-          umma_ss(tmem + bqColS, dKm + st * kSt + kstep_mnmajor(j), dVm + st * kSt + kstep_mnmajor(j), idMM64, j == 0 ? acc0 : 1u);
-        umma_commit(&bars[qS]);
-        RFA_TRACE_EV(16, c);
-        if (want_dseg) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)            // dSseg += Q^T gs
-            umma_ss(tmem + bqColDS, dQm + st * kSt + kstep_mnmajor(j), dGm + st * kSt + kstep_mnmajor(j), idMM64, (c > 0 || j > 0) ? 1u : 0u);
-        }
-        // scores of chunk c + 1 as soon as its tiles are in (its buffer was freed by the dQ product of chunk
-        // c - 1) -- but without blocking: this chunk must not wait for the next chunk's load
-        bool scores_issued = (c + 1 >= nchunk) || c == 0;
-        if (!scores_issued && mbar_test(&bars[qFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
+      if (warp == 1) {
+        // ---- issuer A: scores A = Q K^T of chunk c into score buffer c & 1, then N = P V + Q S into its columns 64..127
+        auto issue_scores = [&](int c) -> bool {
+          const int st = c & 1;
+          const uint64_t so = (uint64_t)st * kSt;
+          if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(7); return false; }
+          // the buffer's previous user was chunk c - 2, whose last product (dQ += dA K, issuer B) read dA from it
+          if (c >= 2 && !mbar_wait(&bars[qDQ + st], ((c - 2) >> 1) & 1)) { tc_fail(8); return false; }
           tc_fence_after_sync();
-          issue_scores(Other{});
-          scores_issued = true;
+          umma_chain_ss<8, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColA + st * 128, dQk + so, dKk + so, idKK, 0);
+          umma_commit(&bars[qA + st]);
+          return true;
+        };
+        auto issue_n = [&](int c) -> bool {
+          const int st = c & 1;
+          const uint64_t so = (uint64_t)st * kSt;
+          RFA_TRACE_EV(10, c);
+          if (!mbar_wait(&bars[qP + st], (c >> 1) & 1)) { tc_fail(2); return false; }
+          RFA_TRACE_EV(11, c);
+          if (!mbar_wait(&bars[qSt], c & 1)) { tc_fail(3); return false; }
+          tc_fence_after_sync();
+          RFA_TRACE_EV(12, c);
+          umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, tmem + bqColA + st * 128, dVm + so, idKM64, 0);
+          umma_chain_ss<8, kStepK, kBlockK, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, dQk + so, dSm, idKM64, 1);
+          umma_commit(&bars[qN + st]);
+          RFA_TRACE_EV(13, c);
+          return true;
+        };
+        // in time order: N of chunk c needs P of chunk c (score group 1, about a microsecond after the scores); the
+        // tiles of chunk c + 1 arrive one chunk period after those of chunk c
+        bool ok = nchunk > 0;
+        if (ok) ok = issue_scores(0);
+#pragma unroll 1
+        for (int c = 0; ok && c < nchunk; ++c) {
+          ok = issue_n(c);
+          if (ok && c + 1 < nchunk) ok = issue_scores(c + 1);
         }
-        RFA_TRACE_EV(19, c);
-        if (!mbar_wait(&bars[qDA16 + st], (c >> 1) & 1)) { tc_fail(6); return false; }
-        RFA_TRACE_EV(20, c);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // dQ += dA K
-          umma_ts(tmem + bqColDQ, tmem + bqColA + st * 128 + j * 8, dKm + st * kSt + kstep_mnmajor(j), idKM128, 1);
-        umma_commit(&bars[qDQ]);
-        umma_commit(&bars[qEmpty + st]);         // every MMA that reads this stage has been issued
-        if (c + 1 < nchunk) {
-          if (!scores_issued) {
-            RFA_TRACE_EV(17, c);
-            if (!mbar_wait(&bars[qFull + (st ^ 1)], ((c + 1) >> 1) & 1)) { tc_fail(7); return false; }
-            RFA_TRACE_EV(18, c);
-            tc_fence_after_sync();
-            issue_scores(Other{});
-          }
-          if (!issue_n(Other{}, c + 1)) return false;
+      } else {
+        // ---- issuer B: dA, dQ and the state updates
+#pragma unroll 1
+        for (int c = 0; c < nchunk; ++c) {
+          const int st = c & 1;
+          const uint64_t so = (uint64_t)st * kSt;
+          RFA_TRACE_EV(14, c);
+          if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(4); break; }
+          RFA_TRACE_EV(15, c);
+          tc_fence_after_sync();
+          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColA + st * 128, dGk + so, dVk + so, idKK, 0);   // dA = gs V^T
+          umma_commit(&bars[qDA + st]);
+          if (!mbar_wait(&bars[qSt], c & 1)) { tc_fail(9); break; }                      // the S tile holds the state before chunk c
+          if (c > 0 && !mbar_wait(&bars[qDQFree], (c - 1) & 1)) { tc_fail(5); break; }
+          tc_fence_after_sync();
+          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColDQ, dGk + so, dSk, idKK, 0);                // dQ = gs S_prev^T
+          const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
+          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColS, dKm + so, dVm + so, idMM64, acc0);  // S += K^T V
+          umma_commit(&bars[qS]);
+          RFA_TRACE_EV(16, c);
+          if (want_dseg)                                                                   // dSseg += Q^T gs
+            umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColDS, dQm + so, dGm + so, idMM64, c > 0 ? 1u : 0u);
+          RFA_TRACE_EV(19, c);
+          if (!mbar_wait(&bars[qDA16 + st], (c >> 1) & 1)) { tc_fail(6); break; }
+          RFA_TRACE_EV(20, c);
+          tc_fence_after_sync();
+          umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bqColDQ, tmem + bqColA + st * 128, dKm + so, idKM128, 1);       // dQ += dA K
+          umma_commit(&bars[qDQ + st]);
+          umma_commit(&bars[qEmpty + st]);       // every MMA that reads this stage is complete when this arrives
+          RFA_TRACE_EV(21, c);
         }
-        RFA_TRACE_EV(21, c);
-        return true;
-      };
-      bool ok = nchunk > 0;
-      if (ok) {
-        ok = mbar_wait(&bars[qFull], 0);
-        if (ok) { tc_fence_after_sync(); issue_scores(std::integral_constant<int, 0>{}); } else tc_fail(8);
-      }
-      if (ok && nchunk > 1) {
-        ok = mbar_wait(&bars[qFull + 1], 0);
-        if (ok) { tc_fence_after_sync(); issue_scores(std::integral_constant<int, 1>{}); } else tc_fail(9);
-      }
-      if (ok) ok = issue_n(std::integral_constant<int, 0>{}, 0);
-      for (int c = 0; ok && c < nchunk; c += 2) {
-        ok = chunk(std::integral_constant<int, 0>{}, c);
-        if (ok && c + 1 < nchunk) ok = chunk(std::integral_constant<int, 1>{}, c + 1);
       }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------------ score group
+    // ------------------------------------------------------------------ score group 1: P, row sums, q . z
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // token row of the chunk
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    bool ok = true;
     RFA_TRACE_DECL(2)
     const bool tr = (warp == 5 && lane == 0);
-    // P = mask(A) fp16 + row sum; then q . z_prev in fp32 from this thread's own Q row
-    auto do_p = [&](int c, float& rowsum, float& qz) {
+    for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t colA = bqColA + st * 128;
       unsigned char* stage = sm + st * bqStage;
       const float* zs = z_buf + (c % 3) * 128;
-      if (tr) RFA_TRACE_EV(30, c);
-      if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(10); ok = false; return; }
-      if (tr) RFA_TRACE_EV(31, c);
-      if (!mbar_wait(&bars[qZ + (c & 1)], (c >> 1) & 1)) { tc_fail(11); ok = false; return; }
       if (tr) RFA_TRACE_EV(32, c);
-      if (!mbar_wait(&bars[qA + st], (c >> 1) & 1)) { tc_fail(12); ok = false; return; }
+      if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); break; }     // this group reads the Q tile itself
+      if (!mbar_wait(&bars[qA + st], (c >> 1) & 1)) { tc_fail(12); break; }
       if (tr) RFA_TRACE_EV(33, c);
       tc_fence_after_sync();
-      rowsum = 0.f;
-#pragma unroll
+      float rowsum = 0.f;
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
         if (piece <= quarter) {
@@ -269,8 +243,10 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tc_fence_before_sync();
       mbar_arrive(&bars[qP + st]);
       if (tr) RFA_TRACE_EV(34, c);
-      // q . z_prev while the tensor pipe computes N from the P just handed over
-      qz = 0.f;
+      // q . z_prev in fp32 from this thread's own Q row while the tensor pipe computes N from the P just handed over
+      // (the scores completed, so the stage's tiles are in; z of this version comes from the output group)
+      if (!mbar_wait(&bars[qZ + (c & 1)], (c >> 1) & 1)) { tc_fail(11); break; }
+      float qz = 0.f;
 #pragma unroll
       for (int ch = 0; ch < 16; ++ch) {
         const uint4 u = *reinterpret_cast<const uint4*>(stage + bqQ + row_chunk2(row, ch));
@@ -281,58 +257,69 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         f = unpack_half2(u.z); qz = fmaf(f.x, z1.x, qz); qz = fmaf(f.y, z1.y, qz);
         f = unpack_half2(u.w); qz = fmaf(f.x, z1.z, qz); qz = fmaf(f.y, z1.w, qz);
       }
-    };
-    // den, gz, gs
-    auto do_g = [&](int c, float rowsum, float qz, float& gz) {
+      rs_buf[(c & 1) * 128 + row] = make_float2(rowsum, qz);
+      mbar_arrive(&bars[qRS + st]);
+      if (tr) RFA_TRACE_EV(35, c);
+    }
+  } else if (warp >= 11) {
+    // ------------------------------------------------------------------ score group 2: den, gz, gs, then dA
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // token row of the chunk
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    RFA_TRACE_DECL(0)
+    const bool tr = (warp == 11 && lane == 0);
+    for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
+      const uint32_t colA = bqColA + st * 128;
       unsigned char* stage = sm + st * bqStage;
       const int64_t t0 = t_begin + (int64_t)c * kTC;
-      if (tr) RFA_TRACE_EV(35, c);
-      if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(13); ok = false; return; }
       if (tr) RFA_TRACE_EV(36, c);
+      if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); break; }     // this group rewrites the g tile itself
+      if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(13); break; }
+      if (!mbar_wait(&bars[qRS + st], (c >> 1) & 1)) { tc_fail(10); break; }
+      if (tr) RFA_TRACE_EV(37, c);
       tc_fence_after_sync();
-      uint32_t nn[64];
-      tmem_ld32(tmem + lane_addr + bqColA + st * 128 + 64, nn);
-      tmem_ld32(tmem + lane_addr + bqColA + st * 128 + 96, nn + 32);
-      tmem_ld_wait();
-      const float raw = rowsum + qz;
-      const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
-      float go = 0.f;
-      unsigned char* grow = stage + bqG;
+      float gz;
+      {
+        uint32_t nn[64];
+        tmem_ld32(tmem + lane_addr + colA + 64, nn);
+        tmem_ld32(tmem + lane_addr + colA + 96, nn + 32);
+        tmem_ld_wait();
+        const float2 rq = rs_buf[(c & 1) * 128 + row];
+        const float raw = rq.x + rq.y;
+        const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
+        float go = 0.f;
+        unsigned char* grow = stage + bqG;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
-        uint4 u = *p;
-        float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
-        go = fmaf(f0.x, __uint_as_float(nn[ch * 8 + 0]), go); go = fmaf(f0.y, __uint_as_float(nn[ch * 8 + 1]), go);
-        go = fmaf(f1.x, __uint_as_float(nn[ch * 8 + 2]), go); go = fmaf(f1.y, __uint_as_float(nn[ch * 8 + 3]), go);
-        go = fmaf(f2.x, __uint_as_float(nn[ch * 8 + 4]), go); go = fmaf(f2.y, __uint_as_float(nn[ch * 8 + 5]), go);
-        go = fmaf(f3.x, __uint_as_float(nn[ch * 8 + 6]), go); go = fmaf(f3.y, __uint_as_float(nn[ch * 8 + 7]), go);
-        u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
-        u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
-        *p = u;
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
+          uint4 u = *p;
+          float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
+          go = fmaf(f0.x, __uint_as_float(nn[ch * 8 + 0]), go); go = fmaf(f0.y, __uint_as_float(nn[ch * 8 + 1]), go);
+          go = fmaf(f1.x, __uint_as_float(nn[ch * 8 + 2]), go); go = fmaf(f1.y, __uint_as_float(nn[ch * 8 + 3]), go);
+          go = fmaf(f2.x, __uint_as_float(nn[ch * 8 + 4]), go); go = fmaf(f2.y, __uint_as_float(nn[ch * 8 + 5]), go);
+          go = fmaf(f3.x, __uint_as_float(nn[ch * 8 + 6]), go); go = fmaf(f3.y, __uint_as_float(nn[ch * 8 + 7]), go);
+          u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
+          u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
+          *p = u;
+        }
+        go *= inv;                                   // g . out
+        gz = raw > kEps ? -go * inv : 0.f;           // strict >, upstream rfa.py:91
+        if (t0 + row < t_end) {
+          ws_den[(size_t)bh * T + t0 + row] = dn;
+          ws_gz[(size_t)bh * T + t0 + row] = gz;
+        }
+        gz_buf[(c & 1) * 128 + row] = gz;
       }
-      go *= inv;                                   // g . out
-      gz = raw > kEps ? -go * inv : 0.f;           // strict >, upstream rfa.py:91
-      if (t0 + row < t_end) {
-        ws_den[(size_t)bh * T + t0 + row] = dn;
-        ws_gz[(size_t)bh * T + t0 + row] = gz;
-      }
-      gz_buf[(c & 1) * 128 + row] = gz;
       fence_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bars[qG + st]);
-      if (tr) RFA_TRACE_EV(37, c);
-    };
-    // dA = mask(gs V^T + gz) -> fp16 over the P columns
-    auto do_da = [&](int c, float gz) {
-      const int st = c & 1;
-      const uint32_t colA = bqColA + st * 128;
       if (tr) RFA_TRACE_EV(38, c);
-      if (!mbar_wait(&bars[qDA + st], (c >> 1) & 1)) { tc_fail(14); ok = false; return; }
+      // ---- dA = mask(gs V^T + gz) -> fp16 over the P columns
+      if (!mbar_wait(&bars[qDA + st], (c >> 1) & 1)) { tc_fail(14); break; }
       if (tr) RFA_TRACE_EV(39, c);
       tc_fence_after_sync();
-#pragma unroll
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
         if (piece <= quarter) {
@@ -358,18 +345,8 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tc_fence_before_sync();
       mbar_arrive(&bars[qDA16 + st]);
       if (tr) RFA_TRACE_EV(40, c);
-    };
-    float rs_cur = 0.f, qz_cur = 0.f;
-    if (nchunk > 0) do_p(0, rs_cur, qz_cur);
-    for (int c = 0; ok && c < nchunk; ++c) {
-      float gz = 0.f, rs_nxt = 0.f, qz_nxt = 0.f;
-      do_g(c, rs_cur, qz_cur, gz);
-      if (ok) do_da(c, gz);
-      if (ok && c + 1 < nchunk) do_p(c + 1, rs_nxt, qz_nxt);
-      rs_cur = rs_nxt;
-      qz_cur = qz_nxt;
     }
-  } else {
+  } else if (warp < 10) {
     // ------------------------------------------------------------------ output / state group
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // token row of the chunk / state row k
@@ -413,6 +390,8 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // ---- the state after this chunk -> fp16 operand tile (the serial chain of the scan)
       if (tr) RFA_TRACE_EV(52, c);
       if (!mbar_wait(&bars[qS], ph)) { tc_fail(16); ok = false; break; }
+      // ... and issuer A's N = P V + Q S of this chunk has finished reading the old S tile (issuer B's reader precedes qS)
+      if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(19); ok = false; break; }
       if (tr) RFA_TRACE_EV(53, c);
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
@@ -432,7 +411,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_arrive(&bars[qEmpty + st]);             // this group's last read of the stage's tiles
       // ---- grad_q = dQ + gz z_prev^T -> fp16, written straight from registers (one 256-byte row per thread)
       if (tr) RFA_TRACE_EV(54, c);
-      if (!mbar_wait(&bars[qDQ], ph)) { tc_fail(18); ok = false; break; }
+      if (!mbar_wait(&bars[qDQ + st], (c >> 1) & 1)) { tc_fail(18); ok = false; break; }
       if (tr) RFA_TRACE_EV(55, c);
       tc_fence_after_sync();
       const bool live = t0 + row < t_end;
