@@ -11,7 +11,9 @@
 // The fp32 state never leaves TMEM; its fp16 copy ([128 k][64 + 16] in two swizzled boxes)
 // is re-exported to shared memory once per chunk as the B operand of the next chunk.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = score
+// Warp roles (352 threads): warp 0 = TMA producer, warps 1 and 10 = MMA issuers (A: scores and P V,
+// B: Q [S|z] and the state update -- issuing one tcgen05.mma costs the issuing thread about as long as
+// the tensor pipe needs to execute it, so a single issuer cannot keep the pipe fed), warps 2..5 = score
 // group (A -> P), warps 6..9 = output/state group (N -> out, state export).  Within a group
 // thread <-> TMEM lane <-> token row / state row.  Two shared-memory stages of Q, K, V; two
 // TMEM buffers each for A/P and N, so the score group works one chunk ahead of the output
@@ -23,7 +25,7 @@
 
 namespace rfa {
 
-constexpr int kFwThreads = 320;
+constexpr int kFwThreads = 352;
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kFwQ = 0, kFwK = 2 * kBox, kFwV = 4 * kBox, kFwStage = 5 * kBox;   // 81920 per stage
@@ -39,7 +41,9 @@ constexpr uint32_t fColA = 0;        // two buffers of 128
 constexpr uint32_t fColN = 256;      // two buffers of 80
 constexpr uint32_t fColS = 416;      // 80: S (64) | z | zeros
 
-enum { fFull = 0, fEmpty = 2, fA = 4, fP = 6, fN = 8, fNFree = 10, fS = 12, fSt = 13, fY = 14, fFullV = 15, fEmptyV = 17, fNum = 19 };
+enum { fFull = 0, fEmpty = 2, fA = 4, fP = 6, fN = 8, fNFree = 10, fS = 12, fSt = 14, fY = 15, fFullV = 16, fEmptyV = 18, fNum = 20 };
+// fS (per N buffer): issuer B's products of a chunk (Q [S|z] into the N buffer, the state update) are complete; waited
+// on by issuer A (P V accumulates onto the N buffer) and by the output group (state export).
 // fFull/fEmpty guard the Q and K tiles of a stage (free once the state MMA has read K), fFullV/fEmptyV its V tile
 // (free once P V has run): the Q, K loads of chunk c+2 start while chunk c is still being finished.
 
@@ -66,15 +70,15 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[fFull + i], 1);
-      mbar_init(&bars[fEmpty + i], 1);
+      mbar_init(&bars[fEmpty + i], 2);        // one commit from each issuer
       mbar_init(&bars[fFullV + i], 1);
-      mbar_init(&bars[fEmptyV + i], 1);
+      mbar_init(&bars[fEmptyV + i], 2);
+      mbar_init(&bars[fS + i], 1);
       mbar_init(&bars[fA + i], 1);
       mbar_init(&bars[fP + i], 128);
       mbar_init(&bars[fN + i], 1);
       mbar_init(&bars[fNFree + i], 128);
     }
-    mbar_init(&bars[fS], 1);
     mbar_init(&bars[fSt], 128);
     mbar_init(&bars[fY], 128);
     mbar_fence_init();
@@ -118,87 +122,84 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tma_load_3d(base + kFwV, &tm_v, &bars[fFullV + st], 0, bh, t0);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
+      constexpr uint32_t lead = 1u;
       RFA_TRACE_DECL(1)
       constexpr uint32_t idA = umma_idesc_f16(128, 128, false, false);   // Q K^T
       constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);    // Q [S|z]   (B MN-major)
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V       (B MN-major)
       constexpr uint32_t idS = umma_idesc_f16(128, 80, true, true);      // K^T [V|1] (A, B MN-major)
-      // Operand descriptors (the shared-memory layout is static).  The chunk loop is unrolled by two so that
-      // the stage is a compile-time constant: every descriptor is a register, every k-step an immediate add.
-      const uint64_t dQ0 = umma_smem_desc(sbase + kFwQ, 0, 1024, kSwizzle128B), dQ1 = dQ0 + (kFwStage >> 4);      // Q, K-major
-      const uint64_t dK0 = umma_smem_desc(sbase + kFwK, 0, 1024, kSwizzle128B), dK1 = dK0 + (kFwStage >> 4);      // K, K-major
-      const uint64_t dKt0 = umma_smem_desc(sbase + kFwK, kBox, 1024, kSwizzle128B), dKt1 = dKt0 + (kFwStage >> 4);  // K^T, MN-major
-      const uint64_t dV0 = umma_smem_desc(sbase + kFwV, kBox, 1024, kSwizzle128B), dV1 = dV0 + (kFwStage >> 4);   // V, MN-major (N = 64)
-      const uint64_t dW0 = umma_smem_desc(sbase + kFwV, kFwOnes - kFwV, 1024, kSwizzle128B);                      // [V|1], MN-major (N = 80)
+      constexpr uint64_t kSt = kFwStage >> 4;
+      const uint64_t dQ = umma_smem_desc(sbase + kFwQ, 0, 1024, kSwizzle128B);        // Q, K-major
+      const uint64_t dK = umma_smem_desc(sbase + kFwK, 0, 1024, kSwizzle128B);        // K, K-major
+      const uint64_t dKt = umma_smem_desc(sbase + kFwK, kBox, 1024, kSwizzle128B);    // K^T, MN-major
+      const uint64_t dV = umma_smem_desc(sbase + kFwV, kBox, 1024, kSwizzle128B);     // V, MN-major (N = 64)
+      // [V|1], MN-major (N = 80): the second 64-block is the ones box, at a different distance from each stage's V tile
+      const uint64_t dW0 = umma_smem_desc(sbase + kFwV, kFwOnes - kFwV, 1024, kSwizzle128B);
       const uint64_t dW1 = umma_smem_desc(sbase + kFwStage + kFwV, kFwOnes - (kFwStage + kFwV), 1024, kSwizzle128B);
-      const uint64_t dS = umma_smem_desc(sbase + kFwS, kBox, 1024, kSwizzle128B);                                 // state tile, MN-major (N = 80)
-      auto issue_A = [&](auto STC) {
-        constexpr int s2 = decltype(STC)::value;
-        const uint64_t q = s2 ? dQ1 : dQ0, k = s2 ? dK1 : dK0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) umma_ss(tmem + fColA + s2 * 128, q + kstep_kmajor(j, kBox), k + kstep_kmajor(j, kBox), idA, j > 0);
-        umma_commit(&bars[fA + s2]);
-      };
-      // one chunk; returns false after a timed-out wait
-      auto chunk = [&](auto STC, int c) -> bool {
-        constexpr int st = decltype(STC)::value;
-        const uint64_t q = st ? dQ1 : dQ0, kt = st ? dKt1 : dKt0, v = st ? dV1 : dV0, w = st ? dW1 : dW0;
-        // the state before this chunk is in the operand tile, and the output group has let go of S
-        RFA_TRACE_EV(10, c);
-        if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); return false; }
-        if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); return false; }
-        tc_fence_after_sync();
-        RFA_TRACE_EV(11, c);
-        if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); return false; }
-        tc_fence_after_sync();
-        const uint32_t fresh_acc = (c == 0 && s_in == nullptr) ? 0u : 1u;
-        // N = Q [S|z]_prev  and  [S|z] += K^T [V|1]
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          umma_ss(tmem + fColN + st * 80, q + kstep_kmajor(j, kBox), dS + kstep_mnmajor(j), idQS, j > 0);
-          umma_ss(tmem + fColS, kt + kstep_mnmajor(j), w + kstep_mnmajor(j), idS, j == 0 ? fresh_acc : 1u);
+      const uint64_t dS = umma_smem_desc(sbase + kFwS, kBox, 1024, kSwizzle128B);     // state tile, MN-major (N = 80)
+      if (warp == 1) {
+        // ---- issuer A: scores of the next chunk as early as its Q, K are in; N += P V
+        auto issue_A = [&](int c) {
+          const int s2 = c & 1;
+          umma_chain_ss<8, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + fColA + s2 * 128, dQ + s2 * kSt, dK + s2 * kSt, idA, 0);
+          umma_commit(&bars[fA + s2]);
+          umma_commit(&bars[fEmpty + s2]);       // this issuer's last read of the stage's Q and K
+        };
+        bool ok = true;
+        if (nchunk > 0) {
+          ok = mbar_wait(&bars[fFull + 0], 0);
+          if (ok) { tc_fence_after_sync(); issue_A(0); } else tc_fail(2);
         }
-        umma_commit(&bars[fS]);
-        RFA_TRACE_EV(12, c);
-        umma_commit(&bars[fEmpty + st]);         // Q and K of this stage have been read for the last time
-        // next chunk's scores as early as its Q, K are there, so the score group never starves --
-        // but never hold back this chunk's P V (and with it the release of V) for a load in flight
-        bool next_issued = (c + 1 >= nchunk);
-        if (!next_issued && mbar_test(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
+#pragma unroll 1
+        for (int c = 0; ok && c < nchunk; ++c) {
+          const int st = c & 1;
+          bool next_issued = (c + 1 >= nchunk);
+          if (!next_issued && mbar_test(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) {
+            tc_fence_after_sync();
+            issue_A(c + 1);
+            next_issued = true;
+          }
+          RFA_TRACE_EV(13, c);
+          if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); break; }
+          if (!mbar_wait(&bars[fS + st], (c >> 1) & 1)) { tc_fail(16); break; }     // Q [S|z] has written the N buffer
+          RFA_TRACE_EV(14, c);
           tc_fence_after_sync();
-          issue_A(std::integral_constant<int, st ^ 1>{});
-          next_issued = true;
+          umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + fColN + st * 80, tmem + fColA + st * 128, dV + st * kSt, idPV, 1);   // N += P V
+          umma_commit(&bars[fN + st]);
+          umma_commit(&bars[fEmptyV + st]);
+          if (!next_issued) {
+            if (!mbar_wait(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) { tc_fail(5); break; }
+            tc_fence_after_sync();
+            issue_A(c + 1);
+          }
         }
-        RFA_TRACE_EV(13, c);
-        if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); return false; }
-        RFA_TRACE_EV(14, c);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 8; ++j)              // N += P V
-          umma_ts(tmem + fColN + st * 80, tmem + fColA + st * 128 + j * 8, v + kstep_mnmajor(j), idPV, 1);
-        umma_commit(&bars[fN + st]);
-        umma_commit(&bars[fEmptyV + st]);
-        if (!next_issued) {
-          if (!mbar_wait(&bars[fFull + (st ^ 1)], ((c + 1) >> 1) & 1)) { tc_fail(5); return false; }
+      } else {
+        // ---- issuer B: N = Q [S|z]_prev  and  [S|z] += K^T [V|1]
+#pragma unroll 1
+        for (int c = 0; c < nchunk; ++c) {
+          const int st = c & 1;
+          const uint64_t so = (uint64_t)st * kSt;
+          const uint64_t w = st ? dW1 : dW0;
+          // the state before this chunk is in the operand tile, and the output group has let go of S and of the N buffer
+          RFA_TRACE_EV(10, c);
+          if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); break; }
+          if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); break; }
+          if (!mbar_wait(&bars[fFull + st], (c >> 1) & 1)) { tc_fail(17); break; }
+          RFA_TRACE_EV(11, c);
+          if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }
           tc_fence_after_sync();
-          issue_A(std::integral_constant<int, st ^ 1>{});
+          const uint32_t fresh_acc = (c == 0 && s_in == nullptr) ? 0u : 1u;
+          umma_chain_ss<8, kStepK, kBlockK, kStepMN, kBlockMN>(lead, tmem + fColN + st * 80, dQ + so, dS, idQS, 0);
+          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + fColS, dKt + so, w, idS, fresh_acc);
+          umma_commit(&bars[fS + st]);
+          umma_commit(&bars[fEmpty + st]);       // this issuer's last read of the stage's Q and K ...
+          umma_commit(&bars[fEmptyV + st]);      // ... and of its V
+          RFA_TRACE_EV(12, c);
         }
-        return true;
-      };
-      bool ok = true;
-      RFA_TRACE_EV(91, 0); RFA_TRACE_CLOCK(90);
-      if (nchunk > 0) {
-        ok = mbar_wait(&bars[fFull + 0], 0);
-        if (ok) { tc_fence_after_sync(); issue_A(std::integral_constant<int, 0>{}); } else tc_fail(2);
       }
-      for (int c = 0; ok && c < nchunk; c += 2) {
-        ok = chunk(std::integral_constant<int, 0>{}, c);
-        if (ok && c + 1 < nchunk) ok = chunk(std::integral_constant<int, 1>{}, c + 1);
-      }
-      RFA_TRACE_EV(93, 0); RFA_TRACE_CLOCK(92);
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ score group: P = mask(A), row sums
@@ -216,7 +217,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(8); break; }
       tc_fence_after_sync();
       float rowsum = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
         if (piece <= quarter) {
@@ -245,7 +246,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_arrive(&bars[fP + st]);
       if (lane == 0 && warp == 5) RFA_TRACE_EV(22, c);
     }
-  } else {
+  } else if (warp < 10) {
     // ------------------------------------------------------------------ output / state group
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // token row in the chunk / state row k
@@ -280,7 +281,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int st = c & 1;
       // ---- the state after this chunk -> operand tile for the next chunk (the serial chain of the scan)
       if (ytid == 0) RFA_TRACE_EV(30, c);
-      if (!mbar_wait(&bars[fS], c & 1)) { tc_fail(9); ok = false; break; }
+      if (!mbar_wait(&bars[fS + st], (c >> 1) & 1)) { tc_fail(9); ok = false; break; }
       if (ytid == 0) RFA_TRACE_EV(31, c);
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
