@@ -416,7 +416,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tc_fence_after_sync();
       const bool live = t0 + row < t_end;
       __half* grow = reinterpret_cast<__half*>(gq_ptr) + ((size_t)(t0 + row) * BH + bh) * kK;
-#pragma unroll
+#pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t a[32];
         tmem_ld32(tmem + lane_addr + bqColDQ + piece * 32, a);

@@ -70,6 +70,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Bounded wait for the phase with the given parity to complete.
 constexpr uint32_t kSpinLimit = 1u << 20;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+  // kept rolled: unrolled copies of this loop at every wait site were most of the kernels' code, and a kernel whose
+  // roles together overflow the instruction cache stalls on instruction fetch
+#pragma unroll 1
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
