@@ -26,18 +26,20 @@ namespace rfa {
 constexpr int kBqThreads = 480;
 
 constexpr uint32_t bqQ = 0, bqK = 2 * kBox, bqV = 4 * kBox, bqG = 5 * kBox, bqStage = 6 * kBox;   // 98304 per stage
-constexpr uint32_t bqS = 2 * bqStage;            // S as an operand: [128 k][64 n] fp16, swizzled
-constexpr uint32_t bqZ = bqS + kBox;             // fp32 [3][128]: z before chunk c lives in buffer c % 3 (readers of version c,
+constexpr uint32_t bqS = 2 * bqStage;            // S as an operand: two tiles [128 k][64 n] fp16, swizzled; the state before
+                                                 // chunk c is in tile c & 1, so the export after chunk c never waits for a reader
+constexpr uint32_t bqZ = bqS + 2 * kBox;         // fp32 [3][128]: z before chunk c lives in buffer c % 3 (readers of version c,
                                                  // c + 1 and the writer of version c + 2 can be active at once)
-constexpr uint32_t bqGz = bqZ + 1536;            // fp32 [2][128]: gz of chunk c's rows in buffer c & 1
-constexpr uint32_t bqRs = bqGz + 1024;           // float2 [2][128]: (row sum of P, q.z) of chunk c's rows in buffer c & 1
-constexpr uint32_t bqBar = bqRs + 2048;
-constexpr uint32_t bqSmem = bqBar + 256 + 1024;
+constexpr uint32_t bqRg = bqZ + 1536;            // fp32 [2][128], buffer c & 1: row sum of P + q.z from score group 1, replaced
+                                                 // in place by gz once score group 2 has consumed it
+constexpr uint32_t bqBar = bqRg + 1024;
+constexpr uint32_t bqSmem = bqBar + 256;         // every byte of the 227 KB is used: no slack to align the base, which the
+                                                 // kernel therefore checks
 
 // TMEM: two score buffers (A -> P in columns 0..63, N in columns 64..127, then dA -> fp16 dA in 0..63)
 constexpr uint32_t bqColA = 0, bqColDQ = 256, bqColS = 384, bqColDS = 448;
-enum { qFull = 0, qEmpty = 2, qA = 4, qP = 6, qN = 8, qG = 10, qDA = 12, qDA16 = 14, qZ = 16, qDQ = 18, qRS = 20, qDQFree = 22,
-       qS = 23, qSt = 24, qNum = 25 };
+enum { qFull = 0, qEmpty = 2, qA = 4, qP = 6, qN = 8, qG = 10, qDA = 12, qDA16 = 14, qZ = 16, qDQ = 18, qRS = 20, qSt = 22,
+       qDQFree = 24, qS = 25, qNum = 26 };
 // Barriers that a waiter may reach late are kept per score buffer / stage (index c & 1), so that their producer
 // cannot complete two phases before the waiter looks: qDQ has two waiters (the output group and issuer A, which
 // reuses the score buffer), qRS hands (row sum, q.z) from score group 1 to score group 2.
@@ -50,13 +52,16 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        float* __restrict__ ws_den, float* __restrict__ ws_gz,
                        float* __restrict__ ds_seg, float* __restrict__ dz_seg,
                        int64_t T, int BH, int nseg, int64_t tseg) {
-  extern __shared__ unsigned char bq_raw[];
-  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(bq_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) unsigned char bq_raw[];
+  unsigned char* sm = bq_raw;
+  if (smem_u32(sm) & 1023u) {                    // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) tc_fail(99);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + bqBar);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + qNum);
   float* z_buf = reinterpret_cast<float*>(sm + bqZ);
-  float* gz_buf = reinterpret_cast<float*>(sm + bqGz);
-  float2* rs_buf = reinterpret_cast<float2*>(sm + bqRs);
+  float* rg_buf = reinterpret_cast<float*>(sm + bqRg);
   const uint32_t sbase = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, seg = blockIdx.y;
@@ -80,8 +85,9 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars[qZ + i], 128);
       mbar_init(&bars[qDQ + i], 1);
       mbar_init(&bars[qRS + i], 128);
+      mbar_init(&bars[qSt + i], 128);         // S tile i holds the state before a chunk c with c & 1 == i
     }
-    mbar_init(&bars[qDQFree], 128); mbar_init(&bars[qS], 1); mbar_init(&bars[qSt], 128);
+    mbar_init(&bars[qDQFree], 128); mbar_init(&bars[qS], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
   }
@@ -121,7 +127,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // P V ; Q S        (B MN-major)
       constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dA K             (B MN-major)
       constexpr uint32_t idMM64 = umma_idesc_f16(128, 64, true, true);    // K^T V ; Q^T gs   (A, B MN-major)
-      constexpr uint64_t kSt = bqStage >> 4;
+      constexpr uint64_t kSt = bqStage >> 4, kTile = kBox >> 4;
       const uint64_t dQk = umma_smem_desc(sbase + bqQ, 0, 1024, kSwizzle128B), dQm = umma_smem_desc(sbase + bqQ, kBox, 1024, kSwizzle128B);
       const uint64_t dKk = umma_smem_desc(sbase + bqK, 0, 1024, kSwizzle128B), dKm = umma_smem_desc(sbase + bqK, kBox, 1024, kSwizzle128B);
       const uint64_t dVk = umma_smem_desc(sbase + bqV, 0, 1024, kSwizzle128B), dVm = umma_smem_desc(sbase + bqV, kBox, 1024, kSwizzle128B);
@@ -147,11 +153,11 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           RFA_TRACE_EV(10, c);
           if (!mbar_wait(&bars[qP + st], (c >> 1) & 1)) { tc_fail(2); return false; }
           RFA_TRACE_EV(11, c);
-          if (!mbar_wait(&bars[qSt], c & 1)) { tc_fail(3); return false; }
+          if (!mbar_wait(&bars[qSt + (c & 1)], (c >> 1) & 1)) { tc_fail(3); return false; }
           tc_fence_after_sync();
           RFA_TRACE_EV(12, c);
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, tmem + bqColA + st * 128, dVm + so, idKM64, 0);
-          umma_chain_ss<8, kStepK, kBlockK, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, dQk + so, dSm, idKM64, 1);
+          umma_chain_ss<8, kStepK, kBlockK, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, dQk + so, dSm + st * kTile, idKM64, 1);
           umma_commit(&bars[qN + st]);
           RFA_TRACE_EV(13, c);
           return true;
@@ -171,19 +177,23 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int c = 0; c < nchunk; ++c) {
           const int st = c & 1;
           const uint64_t so = (uint64_t)st * kSt;
+          // the state update needs only the chunk's K and V (and the output group's read of the previous state): it runs
+          // ahead of everything else, so the export of the next S tile is never on the chunk's critical path
+          if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(20); break; }
+          if (!mbar_wait(&bars[qSt + (c & 1)], (c >> 1) & 1)) { tc_fail(9); break; }
+          tc_fence_after_sync();
+          const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
+          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColS, dKm + so, dVm + so, idMM64, acc0);  // S += K^T V
+          umma_commit(&bars[qS]);
           RFA_TRACE_EV(14, c);
           if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(4); break; }
           RFA_TRACE_EV(15, c);
           tc_fence_after_sync();
           umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColA + st * 128, dGk + so, dVk + so, idKK, 0);   // dA = gs V^T
           umma_commit(&bars[qDA + st]);
-          if (!mbar_wait(&bars[qSt], c & 1)) { tc_fail(9); break; }                      // the S tile holds the state before chunk c
           if (c > 0 && !mbar_wait(&bars[qDQFree], (c - 1) & 1)) { tc_fail(5); break; }
           tc_fence_after_sync();
-          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColDQ, dGk + so, dSk, idKK, 0);                // dQ = gs S_prev^T
-          const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
-          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColS, dKm + so, dVm + so, idMM64, acc0);  // S += K^T V
-          umma_commit(&bars[qS]);
+          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColDQ, dGk + so, dSk + st * kTile, idKK, 0);  // dQ = gs S_prev^T
           RFA_TRACE_EV(16, c);
           if (want_dseg)                                                                   // dSseg += Q^T gs
             umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColDS, dQm + so, dGm + so, idMM64, c > 0 ? 1u : 0u);
@@ -257,7 +267,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         f = unpack_half2(u.z); qz = fmaf(f.x, z1.x, qz); qz = fmaf(f.y, z1.y, qz);
         f = unpack_half2(u.w); qz = fmaf(f.x, z1.z, qz); qz = fmaf(f.y, z1.w, qz);
       }
-      rs_buf[(c & 1) * 128 + row] = make_float2(rowsum, qz);
+      rg_buf[(c & 1) * 128 + row] = rowsum + qz;
       mbar_arrive(&bars[qRS + st]);
       if (tr) RFA_TRACE_EV(35, c);
     }
@@ -285,8 +295,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_ld32(tmem + lane_addr + colA + 64, nn);
         tmem_ld32(tmem + lane_addr + colA + 96, nn + 32);
         tmem_ld_wait();
-        const float2 rq = rs_buf[(c & 1) * 128 + row];
-        const float raw = rq.x + rq.y;
+        const float raw = rg_buf[(c & 1) * 128 + row];
         const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
         float go = 0.f;
         unsigned char* grow = stage + bqG;
@@ -309,7 +318,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           ws_den[(size_t)bh * T + t0 + row] = dn;
           ws_gz[(size_t)bh * T + t0 + row] = gz;
         }
-        gz_buf[(c & 1) * 128 + row] = gz;
+        rg_buf[(c & 1) * 128 + row] = gz;            // over the value just consumed
       }
       fence_async_smem();
       tc_fence_before_sync();
@@ -367,7 +376,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       z_buf[row] = z_in ? z_in[row] : 0.f;
       fence_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&bars[qSt]);
+      mbar_arrive(&bars[qSt + 0]);
       mbar_arrive(&bars[qZ + 0]);
     }
     bool ok = true;
@@ -380,18 +389,18 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       unsigned char* stage = sm + st * bqStage;
       const int64_t t0 = t_begin + (int64_t)c * kTC;
       const float* zs = z_buf + (c % 3) * 128;
-      const float* gzs = gz_buf + (c & 1) * 128;
+      const float* gzs = rg_buf + (c & 1) * 128;
       // ---- z before the next chunk = z + colsum(K): needs only the staged K tile
       if (tr) RFA_TRACE_EV(50, c);
       if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); ok = false; break; }
       if (tr) RFA_TRACE_EV(51, c);
       z_buf[((c + 1) % 3) * 128 + row] = zs[row] + column_sum2(stage + bqK, quarter, lane, nullptr);
       mbar_arrive(&bars[qZ + ((c + 1) & 1)]);
-      // ---- the state after this chunk -> fp16 operand tile (the serial chain of the scan)
+      // ---- the state after this chunk -> the other fp16 operand tile.  Its previous readers (the products of chunk
+      //      c - 1 that read the state before chunk c - 1) were issued before this chunk's state update by the same
+      //      issuer, or consumed before them, so qS alone orders the overwrite.
       if (tr) RFA_TRACE_EV(52, c);
       if (!mbar_wait(&bars[qS], ph)) { tc_fail(16); ok = false; break; }
-      // ... and issuer A's N = P V + Q S of this chunk has finished reading the old S tile (issuer B's reader precedes qS)
-      if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(19); ok = false; break; }
       if (tr) RFA_TRACE_EV(53, c);
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
@@ -399,10 +408,10 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_ld32(tmem + lane_addr + bqColS, r);
         tmem_ld32(tmem + lane_addr + bqColS + 32, r + 32);
         tmem_ld_wait();
-        store_state_row(s_tile, row, r);
+        store_state_row(s_tile + ((c + 1) & 1) * kBox, row, r);
         fence_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(&bars[qSt]);
+        mbar_arrive(&bars[qSt + ((c + 1) & 1)]);
       }
       // gz of every row of this chunk is in shared memory once qG completed (it did: the state MMA waited on it)
       if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(17); ok = false; break; }
