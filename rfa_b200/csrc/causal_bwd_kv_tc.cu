@@ -229,15 +229,20 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (warp == 5 && lane == 0) RFA_TRACE_EV(21, i);
       if (!KV_DBG(0) && !KV_DBG(5)) {
         unsigned char* grow = stage + kvG;
+        // all eight loads of the row first (independent), then the scaling, then the stores: a load behind an in-place
+        // store would wait for it, and shared-memory round trips of this warp queue behind the tensor pipe's reads
+        uint4 gu[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) gu[ch] = *reinterpret_cast<const uint4*>(grow + row_chunk1(row, ch));
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
-          uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
-          uint4 u = *p;
+          const uint4 u = gu[ch];
           float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
-          u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
-          u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
-          *p = u;
+          gu[ch].x = pack_half2(f0.x * inv, f0.y * inv); gu[ch].y = pack_half2(f1.x * inv, f1.y * inv);
+          gu[ch].z = pack_half2(f2.x * inv, f2.y * inv); gu[ch].w = pack_half2(f3.x * inv, f3.y * inv);
         }
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(grow + row_chunk1(row, ch)) = gu[ch];
         gzs[row] = gz;
       }
       fence_async_smem();

@@ -295,23 +295,31 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_ld32(tmem + lane_addr + colA + 64, nn);
         tmem_ld32(tmem + lane_addr + colA + 96, nn + 32);
         tmem_ld_wait();
+        if (tr) RFA_TRACE_EV(41, c);
         const float raw = rg_buf[(c & 1) * 128 + row];
         const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
         float go = 0.f;
         unsigned char* grow = stage + bqG;
+        // all eight loads of the row first: they are independent, whereas a load behind an in-place store of the
+        // same tile would have to wait for it (shared-memory accesses of this warp queue behind the tensor pipe's
+        // operand reads, so every dependent round trip is expensive)
+        uint4 gu[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) gu[ch] = *reinterpret_cast<const uint4*>(grow + row_chunk1(row, ch));
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
-          uint4* p = reinterpret_cast<uint4*>(grow + row_chunk1(row, ch));
-          uint4 u = *p;
+          const uint4 u = gu[ch];
           float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
           go = fmaf(f0.x, __uint_as_float(nn[ch * 8 + 0]), go); go = fmaf(f0.y, __uint_as_float(nn[ch * 8 + 1]), go);
           go = fmaf(f1.x, __uint_as_float(nn[ch * 8 + 2]), go); go = fmaf(f1.y, __uint_as_float(nn[ch * 8 + 3]), go);
           go = fmaf(f2.x, __uint_as_float(nn[ch * 8 + 4]), go); go = fmaf(f2.y, __uint_as_float(nn[ch * 8 + 5]), go);
           go = fmaf(f3.x, __uint_as_float(nn[ch * 8 + 6]), go); go = fmaf(f3.y, __uint_as_float(nn[ch * 8 + 7]), go);
-          u.x = pack_half2(f0.x * inv, f0.y * inv); u.y = pack_half2(f1.x * inv, f1.y * inv);
-          u.z = pack_half2(f2.x * inv, f2.y * inv); u.w = pack_half2(f3.x * inv, f3.y * inv);
-          *p = u;
+          gu[ch].x = pack_half2(f0.x * inv, f0.y * inv); gu[ch].y = pack_half2(f1.x * inv, f1.y * inv);
+          gu[ch].z = pack_half2(f2.x * inv, f2.y * inv); gu[ch].w = pack_half2(f3.x * inv, f3.y * inv);
         }
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(grow + row_chunk1(row, ch)) = gu[ch];
+        if (tr) RFA_TRACE_EV(42, c);
         go *= inv;                                   // g . out
         gz = raw > kEps ? -go * inv : 0.f;           // strict >, upstream rfa.py:91
         if (t0 + row < t_end) {
@@ -320,6 +328,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         rg_buf[(c & 1) * 128 + row] = gz;            // over the value just consumed
       }
+      if (tr) RFA_TRACE_EV(43, c);
       fence_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bars[qG + st]);
