@@ -192,6 +192,8 @@ feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w,
 
 // tensor-core forward for fp16 rows with head_dim = proj_dim = 64 (feature_map_tc.cu)
 int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int64_t rows, int H, float scale, int sms, cudaStream_t st);
+int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_phi, __half* g_x, float* g_w, int64_t rows, int H,
+                              float scale, int sms, cudaStream_t st);
 
 static int fm_check(const void* x, const float* w, int64_t rows, int H, int d, int D) {
   RFA_REQUIRE(x && w, RFA_EINVAL, "feature_map: null pointer");
@@ -265,6 +267,12 @@ extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, c
   RFA_REQUIRE(x_dtype == g_dtype && x_dtype == gx_dtype, RFA_EUNSUPPORTED,
               "feature_map_bwd: x, g_phi and g_x must share one dtype");
   if (rows == 0) return 0;
+  if (x_dtype == RFA_F16 && d == 64 && D == 64) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return launch_feature_map_bwd_tc((const __half*)x, w, (const __half*)g_phi, (__half*)g_x, g_w, rows, H, scale, sms, as_stream(stream));
+  }
   size_t smem = 0;
   const int R = fm_pick_rows(D, d, true, g_w != nullptr, &smem);
   RFA_REQUIRE(R > 0, RFA_EUNSUPPORTED, "feature_map_bwd: shared memory budget exceeded");

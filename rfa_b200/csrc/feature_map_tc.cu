@@ -152,6 +152,277 @@ int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int6
   return check_launch("rfa_feature_map_fwd");
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Feature map backward on tcgen05 for the same case (fp16, head_dim = proj_dim = 64).
+// With inv = 1 / (|x| + 1e-3), u = (W x) inv and g_u = scale (g_sin cos u - g_cos sin u)   (upstream utils.py:100-120):
+//     gh   = g_u inv                         fp16 tile [128 rows][64 j], written by epilogue group 1
+//     gx'  = gh W                            (= (W^T g_u) inv)
+//     g_x  = gx' - x (x . gx') inv / |x|
+//     g_W += gh^T x                          accumulated over all row tiles of the CTA in tensor memory
+// Three small MMA chains per tile of 128 rows: U = X W^T, gx' = gh W, g_W += gh^T X.  The last one has M = 64
+// (rows j): it is issued with M = 128, the second 64-row block of its MN-major A operand being whatever tile
+// follows gh in shared memory -- accumulator rows 64..127 are never read.
+// HBM-bound: 384 bytes in, 128 bytes out per (row, head).
+namespace fmb {
+constexpr int kThreads_ = 320;                 // warp 0 TMA, warp 1 MMA issuer, warps 2..5 group 1 (g_u), warps 6..9 group 2 (g_x)
+constexpr uint32_t kX = 0, kGP = kBox, kStage = 3 * kBox;          // per stage: x tile, g_phi tile (two boxes)
+constexpr uint32_t kGH = 2 * kStage;           // two gh tiles; the output staging tile follows them
+constexpr uint32_t kOut = kGH + 2 * kBox;
+constexpr uint32_t kW = kOut + kBox;           // W  as [j][i] (K-major, contraction over i)
+constexpr uint32_t kWt = kW + 8192;            // W^T as [i][j] (K-major, contraction over j)
+constexpr uint32_t kRn = kWt + 8192;           // float2 [2][128]: (inv, inv / |x|) of the tile's rows
+constexpr uint32_t kBarOff = kRn + 2048;
+constexpr uint32_t kSmem = kBarOff + 256 + 1024;
+constexpr uint32_t cU = 0, cGX = 128, cGW = 256;
+enum { bFull = 0, bEmpty = 2, bU = 4, bUFree = 6, bGH = 8, bGHFree = 10, bGX = 12, bGXFree = 14, bEpi = 16, bDone = 17, bNum = 18 };
+}
+
+__global__ void __launch_bounds__(fmb::kThreads_, 1)
+feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gp,
+                          const __grid_constant__ CUtensorMap tm_gx, const float* __restrict__ w, float* __restrict__ g_w,
+                          int64_t rows, int H, float scale) {
+  using namespace fmb;
+  extern __shared__ unsigned char fmb_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fmb_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBarOff);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + bNum);
+  float2* rn = reinterpret_cast<float2*>(sm + kRn);
+  const uint32_t sbase = smem_u32(sm);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y;
+  const bool want_gw = g_w != nullptr;
+  const int ntile_all = (int)((rows + kTC - 1) / kTC);
+  const int ntile = blockIdx.x < ntile_all ? (ntile_all - 1 - blockIdx.x) / gridDim.x + 1 : 0;   // tiles blockIdx.x, +gridDim.x, ...
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[bFull + i], 1);
+      mbar_init(&bars[bEmpty + i], 257);       // the issuer's commit + both epilogue groups
+      mbar_init(&bars[bU + i], 1); mbar_init(&bars[bUFree + i], 128);
+      mbar_init(&bars[bGH + i], 128); mbar_init(&bars[bGHFree + i], 1);
+      mbar_init(&bars[bGX + i], 1); mbar_init(&bars[bGXFree + i], 128);
+    }
+    mbar_init(&bars[bEpi], 128); mbar_init(&bars[bDone], 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_gp); tma_prefetch_desc(&tm_gx);
+  }
+  // W_h as two fp16 K-major operand tiles: [j][i] and its transpose [i][j]
+  for (int idx = tid; idx < 64 * 8; idx += kThreads_) {
+    const int j = idx >> 3, ch = idx & 7;
+    const float4 a = *reinterpret_cast<const float4*>(w + ((size_t)h * 64 + j) * 64 + ch * 8);
+    const float4 b = *reinterpret_cast<const float4*>(w + ((size_t)h * 64 + j) * 64 + ch * 8 + 4);
+    uint4 u;
+    u.x = pack_half2(a.x, a.y); u.y = pack_half2(a.z, a.w); u.z = pack_half2(b.x, b.y); u.w = pack_half2(b.z, b.w);
+    *reinterpret_cast<uint4*>(sm + kW + row_chunk1(j, ch)) = u;
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e)                // element (i = ch * 8 + e, j) of the transposed tile
+      *reinterpret_cast<__half*>(sm + kWt + sw128_offset(ch * 8 + e, j)) = __float2half_rn(v[e]);
+  }
+  fence_async_smem();
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0)
+      for (int i = 0; i < ntile; ++i) {
+        const int st = i & 1;
+        if (i >= 2 && !mbar_wait(&bars[bEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(11); break; }
+        const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+        unsigned char* base = sm + st * kStage;
+        mbar_arrive_expect_tx(&bars[bFull + st], kStage);
+        tma_load_3d(base + kX, &tm_x, &bars[bFull + st], 0, h, row0);
+        tma_load_3d(base + kGP, &tm_gp, &bars[bFull + st], 0, h, row0);
+        tma_load_3d(base + kGP + kBox, &tm_gp, &bars[bFull + st], 64, h, row0);
+      }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t lead = 1u;
+      constexpr uint32_t idKK = umma_idesc_f16(128, 64, false, false);     // X W^T ; gh W
+      constexpr uint32_t idMM = umma_idesc_f16(128, 64, true, true);       // gh^T X
+      const uint64_t dX = umma_smem_desc(sbase + kX, 0, 1024, kSwizzle128B);            // x, K-major [r][i]
+      const uint64_t dXm = umma_smem_desc(sbase + kX, kBox, 1024, kSwizzle128B);        // x, MN-major (rows = contraction r)
+      const uint64_t dW = umma_smem_desc(sbase + kW, 0, 1024, kSwizzle128B);
+      const uint64_t dWt = umma_smem_desc(sbase + kWt, 0, 1024, kSwizzle128B);
+      const uint64_t dGH = umma_smem_desc(sbase + kGH, 0, 1024, kSwizzle128B);          // gh, K-major [r][j]
+      const uint64_t dGHm = umma_smem_desc(sbase + kGH, kBox, 1024, kSwizzle128B);      // gh, MN-major; second M block = next tile
+      constexpr uint64_t kSt = kStage >> 4, kTile = kBox >> 4;
+      auto issue_u = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(12); return false; }
+        if (i >= 2 && !mbar_wait(&bars[bUFree + st], ((i >> 1) + 1) & 1)) { tc_fail(13); return false; }
+        tc_fence_after_sync();
+        umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + cU + st * 64, dX + st * kSt, dW, idKK, 0);
+        umma_commit(&bars[bU + st]);
+        return true;
+      };
+      bool ok = ntile > 0 ? issue_u(0) : true;
+#pragma unroll 1
+      for (int i = 0; ok && i < ntile; ++i) {
+        const int st = i & 1;
+        if (i + 1 < ntile && !issue_u(i + 1)) break;
+        if (!mbar_wait(&bars[bGH + st], (i >> 1) & 1)) { tc_fail(14); break; }
+        if (i >= 2 && !mbar_wait(&bars[bGXFree + st], ((i >> 1) + 1) & 1)) { tc_fail(15); break; }
+        tc_fence_after_sync();
+        umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + cGX + st * 64, dGH + st * kTile, dWt, idKK, 0);   // gx' = gh W
+        umma_commit(&bars[bGX + st]);
+        if (want_gw)                                                                                                  // g_W += gh^T X
+          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + cGW, dGHm + st * kTile, dXm + st * kSt, idMM, i > 0 ? 1u : 0u);
+        umma_commit(&bars[bGHFree + st]);
+        umma_commit(&bars[bEmpty + st]);
+      }
+      umma_commit(&bars[bDone]);
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ group 1: inv, u, g_u -> gh
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    for (int i = 0; i < ntile; ++i) {
+      const int st = i & 1;
+      unsigned char* base = sm + st * kStage;
+      if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(16); break; }
+      float ss = 0.f;                                  // |x|^2 of this thread's row
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint4 u = *reinterpret_cast<const uint4*>(base + kX + row_chunk1(row, ch));
+        float2 f;
+        f = unpack_half2(u.x); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+        f = unpack_half2(u.y); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+        f = unpack_half2(u.z); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+        f = unpack_half2(u.w); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+      }
+      const float n = sqrtf(ss), inv = 1.f / (n + kNormEps);
+      if (!mbar_wait(&bars[bU + st], (i >> 1) & 1)) { tc_fail(17); break; }
+      tc_fence_after_sync();
+      uint32_t u[64];
+      tmem_ld32(tmem + lane_addr + cU + st * 64, u);
+      tmem_ld32(tmem + lane_addr + cU + st * 64 + 32, u + 32);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[bUFree + st]);
+      // the gh tile of this parity was last read by the products of tile i - 2
+      if (i >= 2 && !mbar_wait(&bars[bGHFree + st], ((i >> 1) + 1) & 1)) { tc_fail(18); break; }
+      rn[st * 128 + row] = make_float2(inv, n > 0.f ? inv / n : 0.f);
+      const float sc = scale * inv;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint4 gs = *reinterpret_cast<const uint4*>(base + kGP + row_chunk1(row, ch));          // g_sin, columns 8 ch ..
+        const uint4 gc = *reinterpret_cast<const uint4*>(base + kGP + kBox + row_chunk1(row, ch));   // g_cos
+        const uint32_t gsw[4] = {gs.x, gs.y, gs.z, gs.w}, gcw[4] = {gc.x, gc.y, gc.z, gc.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = unpack_half2(gsw[e]), b = unpack_half2(gcw[e]);
+          float s0, c0, s1, c1;
+          __sincosf(__uint_as_float(u[ch * 8 + 2 * e]) * inv, &s0, &c0);
+          __sincosf(__uint_as_float(u[ch * 8 + 2 * e + 1]) * inv, &s1, &c1);
+          o[e] = pack_half2(sc * (a.x * c0 - b.x * s0), sc * (a.y * c1 - b.y * s1));
+        }
+        *reinterpret_cast<uint4*>(sm + kGH + st * kBox + row_chunk1(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      fence_async_smem();
+      mbar_arrive(&bars[bGH + st]);
+      mbar_arrive(&bars[bEmpty + st]);                 // this group's reads of the stage are done
+    }
+  } else {
+    // ------------------------------------------------------------------ group 2: g_x
+    const int quarter = warp & 3, row = quarter * 32 + lane, etid = tid - 192;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    uint32_t epi_phase = 0;
+    bool ok = true;
+    for (int i = 0; ok && i < ntile; ++i) {
+      const int st = i & 1;
+      unsigned char* base = sm + st * kStage;
+      const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+      if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(19); ok = false; break; }
+      if (!mbar_wait(&bars[bGH + st], (i >> 1) & 1)) { tc_fail(20); ok = false; break; }      // orders the read of rn
+      if (!mbar_wait(&bars[bGX + st], (i >> 1) & 1)) { tc_fail(21); ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t gx[64];
+      tmem_ld32(tmem + lane_addr + cGX + st * 64, gx);
+      tmem_ld32(tmem + lane_addr + cGX + st * 64 + 32, gx + 32);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[bGXFree + st]);
+      const float2 r2 = rn[st * 128 + row];
+      uint4 xu[8];
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) xu[ch] = *reinterpret_cast<const uint4*>(base + kX + row_chunk1(row, ch));
+      mbar_arrive(&bars[bEmpty + st]);                 // this group's reads of the stage are done
+      float dot = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint32_t xw[4] = {xu[ch].x, xu[ch].y, xu[ch].z, xu[ch].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_half2(xw[e]);
+          dot = fmaf(f.x, __uint_as_float(gx[ch * 8 + 2 * e]), dot);
+          dot = fmaf(f.y, __uint_as_float(gx[ch * 8 + 2 * e + 1]), dot);
+        }
+      }
+      const float c2 = dot * r2.y;                     // (x . gx') inv / |x|
+      if (i > 0) {                                     // the previous tile's store must have drained the staging tile
+        if (etid == 0) tma_store_wait_read<0>();
+        if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(22); ok = false; break; }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint32_t xw[4] = {xu[ch].x, xu[ch].y, xu[ch].z, xu[ch].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_half2(xw[e]);
+          o[e] = pack_half2(__uint_as_float(gx[ch * 8 + 2 * e]) - f.x * c2, __uint_as_float(gx[ch * 8 + 2 * e + 1]) - f.y * c2);
+        }
+        *reinterpret_cast<uint4*>(sm + kOut + row_chunk1(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      fence_async_smem();
+      if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(23); ok = false; break; }
+      if (etid == 0) {
+        tma_store_3d(&tm_gx, sm + kOut, 0, h, row0);
+        tma_store_commit();
+      }
+    }
+    // ---- g_W of this CTA's tiles: rows j = 0..63 of the accumulator
+    if (ok && want_gw && ntile > 0) {
+      if (!mbar_wait(&bars[bDone], 0)) tc_fail(24);
+      else if (row < 64) {
+        tc_fence_after_sync();
+        uint32_t gw[64];
+        tmem_ld32(tmem + lane_addr + cGW, gw);
+        tmem_ld32(tmem + lane_addr + cGW + 32, gw + 32);
+        tmem_ld_wait();
+        float* dst = g_w + ((size_t)h * 64 + row) * 64;
+#pragma unroll
+        for (int e = 0; e < 64; ++e) atomicAdd(dst + e, __uint_as_float(gw[e]));
+      }
+    }
+    if (etid == 0) tma_store_wait<0>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// x, g_x [rows][H][64] fp16, g_phi [rows][H][128] fp16, w [H][64][64] fp32, g_w [H][64][64] fp32 accumulated into (may be null)
+int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_phi, __half* g_x, float* g_w, int64_t rows, int H,
+                              float scale, int sms, cudaStream_t st) {
+  CUtensorMap tx, tg, to;
+  if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tg, g_phi, rows, H, 128, kTC) || make_tmap_rows(&to, g_x, rows, H, 64, kTC))
+    return fail(RFA_EDEVICE, "feature_map_bwd: cuTensorMapEncodeTiled failed or is unavailable");
+  cudaError_t e = cudaFuncSetAttribute(feature_map_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fmb::kSmem);
+  if (e != cudaSuccess) return fail((int)e, "feature_map_bwd: cannot reserve %u bytes of shared memory: %s", fmb::kSmem, cudaGetErrorString(e));
+  const int64_t ntile = (rows + kTC - 1) / kTC;
+  int64_t gx = (sms + H - 1) / H;
+  if (gx > ntile) gx = ntile;
+  if (gx < 1) gx = 1;
+  feature_map_bwd_tc_kernel<<<dim3((unsigned)gx, H), fmb::kThreads_, fmb::kSmem, st>>>(tx, tg, to, w, g_w, rows, H, scale);
+  return check_launch("rfa_feature_map_bwd");
+}
+
 int tc_status_feature_map() { return tc_status_read_clear(); }
 
 }  // namespace rfa

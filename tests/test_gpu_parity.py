@@ -160,6 +160,26 @@ def test_feature_map_shapes_fp32(dev, rows, H, d, D):
     assert_close(gx, rx, "g_x", rel=1e-4, mabs=1e-4); assert_close(gw, rw, "g_w", rel=1e-4, mabs=1e-3)
 
 
+@pytest.mark.parametrize("rows,H", [(1, 1), (130, 3), (1000, 2), (4096, 16)])
+def test_feature_map_fp16_tensor_core_path(dev, rows, H):
+    """fp16 rows with head_dim = proj_dim = 64 take the tcgen05 kernels (forward and backward); several row tiles per
+    CTA, a ragged last tile, a zero vector, and g_W accumulated over all tiles and CTAs of a head."""
+    from rfa_b200 import ops
+    gen = torch.Generator().manual_seed(rows + H)
+    x = h16(torch.randn(rows, H, 64, generator=gen) * 2)
+    x[0, 0] = 0
+    w = torch.randn(H, 64, 64, generator=gen)
+    gp = h16(torch.randn(rows, H, 128, generator=gen))
+    phi = ops.feature_map_fwd(x.to(dev).half(), w.to(dev), 0.1)
+    gx, gw = ops.feature_map_bwd(x.to(dev).half(), w.to(dev), gp.to(dev).half(), 0.1, True)
+    assert phi.dtype == torch.half and gx.dtype == torch.half
+    assert_close(phi, O.random_project(x, w), "phi", rel=2e-3, mabs=2e-4)
+    rx, rw = O.random_project_backward(x, w, gp)
+    assert_close(gx, rx, "g_x"); assert_close(gw, rw, "g_w", rel=2e-3, mabs=5e-2)
+    gx2, none = ops.feature_map_bwd(x.to(dev).half(), w.to(dev), gp.to(dev).half(), 0.1, False)
+    assert none is None and torch.equal(gx2, gx)
+
+
 # ----------------------------------------------------------------------------- decode
 def test_decode_against_upstream_fixture(dev):
     from rfa_b200.causal_attention import incremental_rfa
