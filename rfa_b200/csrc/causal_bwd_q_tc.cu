@@ -225,7 +225,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (!mbar_wait(&bars[qA + st], (c >> 1) & 1)) { tc_fail(12); break; }
       if (tr) RFA_TRACE_EV(33, c);
       tc_fence_after_sync();
-      float rowsum = 0.f;
+      float rowsum = 0.f, rowsum_b = 0.f;
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
@@ -240,7 +240,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               if (i > lane) x0 = 0.f;
               if (i + 1 > lane) x1 = 0.f;
             }
-            rowsum += x0 + x1;
+            if (i & 2) rowsum_b += x0 + x1; else rowsum += x0 + x1;
             p[i >> 1] = pack_half2(x0, x1);
           }
         } else {
@@ -256,18 +256,19 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // q . z_prev in fp32 from this thread's own Q row while the tensor pipe computes N from the P just handed over
       // (the scores completed, so the stage's tiles are in; z of this version comes from the output group)
       if (!mbar_wait(&bars[qZ + (c & 1)], (c >> 1) & 1)) { tc_fail(11); break; }
-      float qz = 0.f;
+      float qz0 = 0.f, qz1 = 0.f, qz2 = 0.f, qz3 = 0.f;      // four partial sums: a single one is a 128-long dependent chain
 #pragma unroll
       for (int ch = 0; ch < 16; ++ch) {
         const uint4 u = *reinterpret_cast<const uint4*>(stage + bqQ + row_chunk2(row, ch));
         const float4 z0 = *reinterpret_cast<const float4*>(zs + ch * 8), z1 = *reinterpret_cast<const float4*>(zs + ch * 8 + 4);
         float2 f;
-        f = unpack_half2(u.x); qz = fmaf(f.x, z0.x, qz); qz = fmaf(f.y, z0.y, qz);
-        f = unpack_half2(u.y); qz = fmaf(f.x, z0.z, qz); qz = fmaf(f.y, z0.w, qz);
-        f = unpack_half2(u.z); qz = fmaf(f.x, z1.x, qz); qz = fmaf(f.y, z1.y, qz);
-        f = unpack_half2(u.w); qz = fmaf(f.x, z1.z, qz); qz = fmaf(f.y, z1.w, qz);
+        f = unpack_half2(u.x); qz0 = fmaf(f.x, z0.x, qz0); qz1 = fmaf(f.y, z0.y, qz1);
+        f = unpack_half2(u.y); qz2 = fmaf(f.x, z0.z, qz2); qz3 = fmaf(f.y, z0.w, qz3);
+        f = unpack_half2(u.z); qz0 = fmaf(f.x, z1.x, qz0); qz1 = fmaf(f.y, z1.y, qz1);
+        f = unpack_half2(u.w); qz2 = fmaf(f.x, z1.z, qz2); qz3 = fmaf(f.y, z1.w, qz3);
       }
-      rg_buf[(c & 1) * 128 + row] = rowsum + qz;
+      const float qz = (qz0 + qz1) + (qz2 + qz3);
+      rg_buf[(c & 1) * 128 + row] = (rowsum + rowsum_b) + qz;
       mbar_arrive(&bars[qRS + st]);
       if (tr) RFA_TRACE_EV(35, c);
     }
@@ -298,7 +299,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (tr) RFA_TRACE_EV(41, c);
         const float raw = rg_buf[(c & 1) * 128 + row];
         const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
-        float go = 0.f;
+        float go = 0.f, go1 = 0.f, go2 = 0.f, go3 = 0.f;
         unsigned char* grow = stage + bqG;
         // all eight loads of the row first: they are independent, whereas a load behind an in-place store of the
         // same tile would have to wait for it (shared-memory accesses of this warp queue behind the tensor pipe's
@@ -310,17 +311,17 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int ch = 0; ch < 8; ++ch) {
           const uint4 u = gu[ch];
           float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
-          go = fmaf(f0.x, __uint_as_float(nn[ch * 8 + 0]), go); go = fmaf(f0.y, __uint_as_float(nn[ch * 8 + 1]), go);
-          go = fmaf(f1.x, __uint_as_float(nn[ch * 8 + 2]), go); go = fmaf(f1.y, __uint_as_float(nn[ch * 8 + 3]), go);
-          go = fmaf(f2.x, __uint_as_float(nn[ch * 8 + 4]), go); go = fmaf(f2.y, __uint_as_float(nn[ch * 8 + 5]), go);
-          go = fmaf(f3.x, __uint_as_float(nn[ch * 8 + 6]), go); go = fmaf(f3.y, __uint_as_float(nn[ch * 8 + 7]), go);
+          go = fmaf(f0.x, __uint_as_float(nn[ch * 8 + 0]), go); go1 = fmaf(f0.y, __uint_as_float(nn[ch * 8 + 1]), go1);
+          go2 = fmaf(f1.x, __uint_as_float(nn[ch * 8 + 2]), go2); go3 = fmaf(f1.y, __uint_as_float(nn[ch * 8 + 3]), go3);
+          go = fmaf(f2.x, __uint_as_float(nn[ch * 8 + 4]), go); go1 = fmaf(f2.y, __uint_as_float(nn[ch * 8 + 5]), go1);
+          go2 = fmaf(f3.x, __uint_as_float(nn[ch * 8 + 6]), go2); go3 = fmaf(f3.y, __uint_as_float(nn[ch * 8 + 7]), go3);
           gu[ch].x = pack_half2(f0.x * inv, f0.y * inv); gu[ch].y = pack_half2(f1.x * inv, f1.y * inv);
           gu[ch].z = pack_half2(f2.x * inv, f2.y * inv); gu[ch].w = pack_half2(f3.x * inv, f3.y * inv);
         }
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(grow + row_chunk1(row, ch)) = gu[ch];
         if (tr) RFA_TRACE_EV(42, c);
-        go *= inv;                                   // g . out
+        go = ((go + go1) + (go2 + go3)) * inv;       // g . out
         gz = raw > kEps ? -go * inv : 0.f;           // strict >, upstream rfa.py:91
         if (t0 + row < t_end) {
           ws_den[(size_t)bh * T + t0 + row] = dn;

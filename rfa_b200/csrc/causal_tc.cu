@@ -216,7 +216,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // rs[st] of chunk c-2 must have been read by the output group
       if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(8); break; }
       tc_fence_after_sync();
-      float rowsum = 0.f;
+      float rowsum = 0.f, rowsum_b = 0.f;
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
@@ -231,7 +231,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
               if (i > lane) x0 = 0.f;
               if (i + 1 > lane) x1 = 0.f;
             }
-            rowsum += x0 + x1;
+            if (i & 2) rowsum_b += x0 + x1; else rowsum += x0 + x1;
             p[i >> 1] = pack_half2(x0, x1);
           }
         } else {
@@ -240,7 +240,7 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         tmem_st16(tmem + lane_addr + colA + piece * 16, p);
       }
-      rs[st * 128 + row] = rowsum;
+      rs[st * 128 + row] = rowsum + rowsum_b;
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[fP + st]);
