@@ -39,7 +39,9 @@ constexpr uint32_t bqSmem = bqBar + 256;         // every byte of the 227 KB is 
 // TMEM: two score buffers (A -> P in columns 0..63, N in columns 64..127, then dA -> fp16 dA in 0..63)
 constexpr uint32_t bqColA = 0, bqColDQ = 256, bqColS = 384, bqColDS = 448;
 enum { qFull = 0, qEmpty = 2, qA = 4, qP = 6, qN = 8, qG = 10, qDA = 12, qDA16 = 14, qZ = 16, qDQ = 18, qRS = 20, qSt = 22,
-       qDQFree = 24, qS = 25, qNum = 26 };
+       qDQFree = 24, qS = 25, qFullV = 26, qNum = 28 };
+// qFull guards the Q and K tiles of a stage, qFullV its V and g tiles, requested in that order: the scores start as soon
+// as Q and K are in.
 // Barriers that a waiter may reach late are kept per score buffer / stage (index c & 1), so that their producer
 // cannot complete two phases before the waiter looks: qDQ has two waiters (the output group and issuer A, which
 // reuses the score buffer), qRS hands (row sum, q.z) from score group 1 to score group 2.
@@ -75,6 +77,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[qFull + i], 1);
+      mbar_init(&bars[qFullV + i], 1);
       mbar_init(&bars[qEmpty + i], 129);      // the MMA issuer's commit + the output group's last reads
       mbar_init(&bars[qA + i], 1);
       mbar_init(&bars[qP + i], 128);
@@ -109,13 +112,15 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int t0 = (int)(t_begin + (int64_t)c * kTC);
         uint64_t* fb = &bars[qFull + st];
         RFA_TRACE_EV(2, c);
-        mbar_arrive_expect_tx(fb, bqStage);
+        uint64_t* fv = &bars[qFullV + st];
+        mbar_arrive_expect_tx(fb, 4 * kBox);
         tma_load_3d(base + bqQ, &tm_q, fb, 0, bh, t0);
         tma_load_3d(base + bqQ + kBox, &tm_q, fb, 64, bh, t0);
         tma_load_3d(base + bqK, &tm_k, fb, 0, bh, t0);
         tma_load_3d(base + bqK + kBox, &tm_k, fb, 64, bh, t0);
-        tma_load_3d(base + bqV, &tm_v, fb, 0, bh, t0);
-        tma_load_3d(base + bqG, &tm_g, fb, 0, bh, t0);
+        mbar_arrive_expect_tx(fv, 2 * kBox);
+        tma_load_3d(base + bqV, &tm_v, fv, 0, bh, t0);
+        tma_load_3d(base + bqG, &tm_g, fv, 0, bh, t0);
       }
     }
   } else if (warp == 1 || warp == 10) {
@@ -154,6 +159,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           if (!mbar_wait(&bars[qP + st], (c >> 1) & 1)) { tc_fail(2); return false; }
           RFA_TRACE_EV(11, c);
           if (!mbar_wait(&bars[qSt + (c & 1)], (c >> 1) & 1)) { tc_fail(3); return false; }
+          if (!mbar_wait(&bars[qFullV + st], (c >> 1) & 1)) { tc_fail(23); return false; }
           tc_fence_after_sync();
           RFA_TRACE_EV(12, c);
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, tmem + bqColA + st * 128, dVm + so, idKM64, 0);
@@ -180,6 +186,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           // the state update needs only the chunk's K and V (and the output group's read of the previous state): it runs
           // ahead of everything else, so the export of the next S tile is never on the chunk's critical path
           if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(20); break; }
+          if (!mbar_wait(&bars[qFullV + st], (c >> 1) & 1)) { tc_fail(24); break; }
           if (!mbar_wait(&bars[qSt + (c & 1)], (c >> 1) & 1)) { tc_fail(9); break; }
           tc_fence_after_sync();
           const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
@@ -285,7 +292,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       unsigned char* stage = sm + st * bqStage;
       const int64_t t0 = t_begin + (int64_t)c * kTC;
       if (tr) RFA_TRACE_EV(36, c);
-      if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); break; }     // this group rewrites the g tile itself
+      if (!mbar_wait(&bars[qFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }    // this group rewrites the g tile itself
       if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(13); break; }
       if (!mbar_wait(&bars[qRS + st], (c >> 1) & 1)) { tc_fail(10); break; }
       if (tr) RFA_TRACE_EV(37, c);
