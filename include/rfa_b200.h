@@ -154,6 +154,17 @@ int rfa_cross_state_fwd(const void* phi_k, const void* v, const uint8_t* pad_mas
                         float* s, float* z,
                         int64_t T, int B, int H, int K, int d, rfa_stream_t stream);
 
+/* The same reduction over nseg contiguous runs of tokens at once (nseg CTAs per
+ * (batch, head) instead of one, for few long sequences): s_part [BH,nseg,K,d],
+ * z_part [BH,nseg,K] fp32, run i covering tokens [i*L, min(T,(i+1)*L)) with
+ * L = rfa_state_partials_run_length(T, nseg) (a multiple of 128); the caller
+ * sums over nseg.  No padding mask.  No counterpart upstream (its kernels walk a
+ * whole sequence in one CTA, cuda/forward.cu:112-125); used for the per-shard
+ * totals of the sequence-sharded causal path. */
+int64_t rfa_state_partials_run_length(int64_t T, int nseg);
+int rfa_state_partials(const void* phi_k, const void* v, float* s_part, float* z_part,
+                       int64_t T, int BH, int K, int d, int nseg, rfa_stream_t stream);
+
 /* Gradient of the reduction: g_phi_k [T,BH,K] (zero at padded rows),
  * g_v [T,BH,d] from d_s [BH,K,d], d_z [BH,K] fp32. */
 int rfa_cross_state_bwd(const void* phi_k, const void* v, const uint8_t* pad_mask,

@@ -35,6 +35,8 @@ SIGNATURES = {
     "rfa_causal_bwd_noalloc_max_token_heads": (_i64, []),
     "rfa_causal_bwd_noalloc": (_int, [_vp] * 4 + [_vp] * 3 + [_i64, _int, _int, _int, _vp]),
     "rfa_cross_state_fwd": (_int, [_vp] * 5 + [_i64, _int, _int, _int, _int, _vp]),
+    "rfa_state_partials_run_length": (_i64, [_i64, _int]),
+    "rfa_state_partials": (_int, [_vp] * 4 + [_i64, _int, _int, _int, _int, _vp]),
     "rfa_cross_state_bwd": (_int, [_vp] * 7 + [_i64, _int, _int, _int, _int, _vp]),
     "rfa_cross_query_fwd": (_int, [_vp] * 4 + [_i64, _int, _int, _int, _vp]),
     "rfa_cross_query_bwd": (_int, [_vp] * 7 + [_i64, _int, _int, _int, _vp]),

@@ -274,6 +274,28 @@ extern "C" int rfa_cross_state_fwd(const void* phi_k, const void* v, const uint8
   return launch_cross_state_fwd_tc((const __half*)phi_k, (const __half*)v, pad_mask, s, z, T, BH, H, 1, tseg, as_stream(stream));
 }
 
+extern "C" int64_t rfa_state_partials_run_length(int64_t T, int nseg) {
+  if (T <= 0 || nseg <= 0) return 0;
+  const int64_t per = (T + nseg - 1) / nseg;
+  return ((per + kSegAlign - 1) / kSegAlign) * kSegAlign;
+}
+
+extern "C" int rfa_state_partials(const void* phi_k, const void* v, float* s_part, float* z_part,
+                                  int64_t T, int BH, int K, int d, int nseg, rfa_stream_t stream) {
+  if (int e = check_geometry("state_partials", T, BH, K, d)) return e;
+  RFA_REQUIRE(nseg > 0 && nseg <= 65535, RFA_EINVAL, "state_partials: nseg=%d", nseg);
+  RFA_REQUIRE(phi_k && v && s_part && z_part, RFA_EINVAL, "state_partials: null pointer");
+  RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(s_part) && aligned16(z_part), RFA_EALIGN,
+              "state_partials: 16-byte alignment required");
+  if (T == 0) {
+    cudaMemsetAsync(s_part, 0, (size_t)BH * nseg * kK * kD * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(z_part, 0, (size_t)BH * nseg * kK * sizeof(float), as_stream(stream));
+    return check_launch("rfa_state_partials(T=0)");
+  }
+  return launch_cross_state_fwd_tc((const __half*)phi_k, (const __half*)v, nullptr, s_part, z_part, T, BH, 1, nseg,
+                                   rfa_state_partials_run_length(T, nseg), as_stream(stream));
+}
+
 extern "C" int rfa_cross_state_bwd(const void* phi_k, const void* v, const uint8_t* pad_mask, const float* d_s,
                                    const float* d_z, void* g_phi_k, void* g_v,
                                    int64_t T, int B, int H, int K, int d, rfa_stream_t stream) {

@@ -62,21 +62,30 @@ __device__ __forceinline__ void zero_row2(unsigned char* tile, int row) {     //
 // state reduction.  grid (BH, nseg)
 // ===========================================================================
 namespace xs {
-constexpr uint32_t kK_ = 0, kV_ = 2 * kBox, kStage = 3 * kBox, kBarOff = 2 * kStage, kSmem = kBarOff + 128 + 1024;
-enum { bFull = 0, bReady = 2, bEmpty = 4, bDone = 6, bEpi = 7, bNum = 8 };
+constexpr uint32_t kK_ = 0, kV_ = 2 * kBox, kStage = 3 * kBox;
+// NS stages of 48 KB: two let two CTAs share an SM (many short sequences: cross attention), four give one CTA per SM
+// enough loads in flight to run a long sequence at the memory's rate (segment / shard boundary states)
+template <int NS> struct L {
+  static constexpr uint32_t kBarOff = NS * kStage, kSmem = kBarOff + 128 + 1024;
+  enum { bFull = 0, bReady = NS, bEmpty = 2 * NS, bDone = 3 * NS, bEpi = 3 * NS + 1, bNum = 3 * NS + 2 };
+};
 }
 
-__global__ void __launch_bounds__(kXThreads, 2)
+template <int NS>
+__global__ void __launch_bounds__(kXThreads, 1)
 cross_state_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           const uint8_t* __restrict__ pad_mask, float* __restrict__ s_out, float* __restrict__ z_out,
                           int64_t T, int BH, int H, int nseg, int64_t tseg) {
   using namespace xs;
+  constexpr uint32_t kBarOff = L<NS>::kBarOff;
+  constexpr int bFull = L<NS>::bFull, bReady = L<NS>::bReady, bEmpty = L<NS>::bEmpty, bDone = L<NS>::bDone, bEpi = L<NS>::bEpi, bNum = L<NS>::bNum;
   RFA_X_PROLOGUE(bNum, 64)
   const int bh = blockIdx.x, seg = blockIdx.y;
   const int64_t t_begin = seg * tseg, t_end = min(T, t_begin + tseg);
   const int nchunk = (int)((t_end - t_begin + kTC - 1) / kTC);
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars[bFull + i], 1); mbar_init(&bars[bReady + i], 128); mbar_init(&bars[bEmpty + i], 1); }
+    // a stage is free again once the product has read it (commit) and the epilogue warps have summed its K columns
+    for (int i = 0; i < NS; ++i) { mbar_init(&bars[bFull + i], 1); mbar_init(&bars[bReady + i], 128); mbar_init(&bars[bEmpty + i], 129); }
     mbar_init(&bars[bDone], 1); mbar_init(&bars[bEpi], 128);
     mbar_fence_init();
     tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
@@ -85,8 +94,8 @@ cross_state_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
   if (warp == 0) {
     if (lane == 0)
       for (int c = 0; c < nchunk; ++c) {
-        const int st = c & 1;
-        if (c >= 2 && !mbar_wait(&bars[bEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
+        const int st = c % NS;
+        if (c >= NS && !mbar_wait(&bars[bEmpty + st], ((c / NS) + 1) & 1)) { tc_fail(1); break; }
         unsigned char* base = sm + st * kStage;
         const int t0 = (int)(t_begin + (int64_t)c * kTC);
         mbar_arrive_expect_tx(&bars[bFull + st], kStage);
@@ -99,13 +108,14 @@ cross_state_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
       constexpr uint32_t idMM = umma_idesc_f16(128, 64, true, true);
       const uint64_t dK = umma_smem_desc(sbase + kK_, kBox, 1024, kSwizzle128B), dV = umma_smem_desc(sbase + kV_, kBox, 1024, kSwizzle128B);
       bool ok = true;
+#pragma unroll 1
       for (int c = 0; c < nchunk; ++c) {
-        const int st = c & 1;
-        if (!mbar_wait(&bars[bReady + st], (c >> 1) & 1)) { tc_fail(2); ok = false; break; }
+        const int st = c % NS;
+        // with a padding mask the epilogue warps first zero the padded rows of the staged K tile
+        if (!mbar_wait(&bars[(pad_mask ? bReady : bFull) + st], (c / NS) & 1)) { tc_fail(2); ok = false; break; }
         tc_fence_after_sync();
         const uint64_t so = (uint64_t)st * (kStage >> 4);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) umma_ss(tmem, dK + so + kstep_mnmajor(j), dV + so + kstep_mnmajor(j), idMM, (c > 0 || j > 0) ? 1u : 0u);
+        umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(1u, tmem, dK + so, dV + so, idMM, c > 0 ? 1u : 0u);
         umma_commit(&bars[bEmpty + st]);
       }
       if (ok) umma_commit(&bars[bDone]);
@@ -118,17 +128,18 @@ cross_state_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid
     uint32_t epi_phase = 0;
     bool ok = true;
     for (int c = 0; ok && c < nchunk; ++c) {
-      const int st = c & 1;
+      const int st = c % NS;
       unsigned char* stage = sm + st * kStage;
       const int64_t t0 = t_begin + (int64_t)c * kTC;
-      if (!mbar_wait(&bars[bFull + st], (c >> 1) & 1)) { tc_fail(3); ok = false; break; }
+      if (!mbar_wait(&bars[bFull + st], (c / NS) & 1)) { tc_fail(3); ok = false; break; }
       if (mrow) {                                   // padded keys contribute nothing: zero their feature rows
         if (t0 + row < t_end && mrow[t0 + row]) zero_row2(stage + kK_, row);
         fence_async_smem();
         if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(4); ok = false; break; }
+        mbar_arrive(&bars[bReady + st]);
       }
       z_acc += column_sum2(stage + kK_, quarter, lane, nullptr);
-      mbar_arrive(&bars[bReady + st]);
+      mbar_arrive(&bars[bEmpty + st]);
     }
     if (ok) {
       uint32_t r[64];
@@ -556,8 +567,16 @@ int launch_cross_state_fwd_tc(const __half* k, const __half* v, const uint8_t* p
   if (r1 || r2)
     return fail(RFA_EDEVICE, "cross_state_fwd: cuTensorMapEncodeTiled failed or is unavailable (%d, %d; k=%p v=%p T=%lld BH=%d)", r1, r2,
                 (const void*)k, (const void*)v, (long long)T, BH);
-  if (int e = x_opt_in(cross_state_fwd_tc_kernel, xs::kSmem, "cross_state_fwd")) return e;
-  cross_state_fwd_tc_kernel<<<dim3(BH, nseg), kXThreads, xs::kSmem, st>>>(tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if ((int64_t)BH * nseg > sms) {            // more CTAs than SMs: two per SM, two stages each
+    if (int e = x_opt_in(cross_state_fwd_tc_kernel<2>, xs::L<2>::kSmem, "cross_state_fwd")) return e;
+    cross_state_fwd_tc_kernel<2><<<dim3(BH, nseg), kXThreads, xs::L<2>::kSmem, st>>>(tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
+  } else {
+    if (int e = x_opt_in(cross_state_fwd_tc_kernel<4>, xs::L<4>::kSmem, "cross_state_fwd")) return e;
+    cross_state_fwd_tc_kernel<4><<<dim3(BH, nseg), kXThreads, xs::L<4>::kSmem, st>>>(tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
+  }
   return check_launch("rfa_cross_state_fwd");
 }
 

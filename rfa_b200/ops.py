@@ -151,6 +151,23 @@ def cross_state_fwd(phi_k: Tensor, v: Tensor, pad_mask: Optional[Tensor]) -> Tup
     return s, z
 
 
+def state_total(phi_k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor]:
+    """phi_k [T,BH,K], v [T,BH,d] fp16 -> (sum_t k_t v_t^T [BH,K,d], sum_t k_t [BH,K]) fp32, with enough CTAs per
+    sequence to fill the GPU when BH is small (partials over runs of tokens, summed here)."""
+    require_half(phi_k, v)
+    T, BH, K = phi_k.shape
+    d = v.shape[-1]
+    phi_k, v = phi_k.contiguous(), v.contiguous()
+    sms = torch.cuda.get_device_properties(phi_k.device).multi_processor_count
+    nseg = max(1, min(sms // max(BH, 1), T // 512))
+    s = torch.empty(BH, nseg, K, d, dtype=torch.float32, device=phi_k.device)
+    z = torch.empty(BH, nseg, K, dtype=torch.float32, device=phi_k.device)
+    with _guard(phi_k):
+        check(_lib.load().rfa_state_partials(ptr(phi_k), ptr(v), ptr(s), ptr(z), T, BH, K, d, nseg, stream_of(phi_k)),
+              "rfa_state_partials")
+    return (s[:, 0], z[:, 0]) if nseg == 1 else (s.sum(dim=1), z.sum(dim=1))
+
+
 def cross_state_bwd(phi_k: Tensor, v: Tensor, pad_mask: Optional[Tensor], d_s: Tensor, d_z: Tensor):
     T, B, H, K = phi_k.shape
     d = v.shape[-1]

@@ -47,15 +47,19 @@ def exclusive_scan_over_ranks(local: Tensor, group=None, reverse: bool = False) 
     return sel.sum(dim=0)
 
 
+def _group_size(group) -> int:
+    if not (dist.is_available() and dist.is_initialized()):
+        return 1
+    return dist.get_world_size(group)
+
+
 class _CudaKernels:
     """The four local steps on the sm_100a kernels."""
 
     @staticmethod
     def segment_state(k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor]:
         from . import ops
-        T, BH, K = k.shape
-        s, z = ops.cross_state_fwd(k.view(T, 1, BH, K), v.view(T, 1, BH, -1), None)
-        return s.view(BH, K, -1), z.view(BH, K)
+        return ops.state_total(k, v)
 
     @staticmethod
     def forward(q, k, v, s_in, z_in):
@@ -73,6 +77,11 @@ class _CudaKernels:
         from . import ops
         return ops.causal_bwd_kv(q, k, v, g, ds_in, dz_in, ctx)
 
+    @staticmethod
+    def backward_full(q, k, v, g):
+        from . import ops
+        return ops.causal_bwd(q, k, v, g, None, None, None, None)
+
 
 class SequenceShardedRFA(torch.autograd.Function):
     """``SequenceShardedRFA.apply(q, k, v, group)`` -- attention output for this rank's tokens."""
@@ -82,6 +91,11 @@ class SequenceShardedRFA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, group=None):
         kern = SequenceShardedRFA.kernels
+        ctx.group = group
+        ctx.alone = _group_size(group) == 1
+        if ctx.alone:                              # the whole sequence is here: no carry in either direction
+            ctx.save_for_backward(q, k, v)
+            return kern.forward(q, k, v, None, None)
         s_loc, z_loc = kern.segment_state(k, v)
         packed = torch.cat([s_loc.reshape(s_loc.shape[0], -1), z_loc], dim=1)          # [BH, K*d + K]
         carry = exclusive_scan_over_ranks(packed, group)
@@ -95,8 +109,15 @@ class SequenceShardedRFA(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         kern = SequenceShardedRFA.kernels
-        q, k, v, s_in, z_in = ctx.saved_tensors
         g = g.contiguous()
+        if ctx.alone:
+            q, k, v = ctx.saved_tensors
+            if hasattr(kern, "backward_full"):
+                return tuple(kern.backward_full(q, k, v, g)) + (None,)
+            gq, _, _, sweep_ctx = kern.backward_q(q, k, v, g, None, None)
+            gk, gv = kern.backward_kv(q, k, v, g, None, None, sweep_ctx)
+            return gq, gk, gv, None
+        q, k, v, s_in, z_in = ctx.saved_tensors
         gq, ds_loc, dz_loc, sweep_ctx = kern.backward_q(q, k, v, g, s_in, z_in)
         packed = torch.cat([ds_loc.reshape(ds_loc.shape[0], -1), dz_loc], dim=1)
         carry = exclusive_scan_over_ranks(packed, ctx.group, reverse=True)

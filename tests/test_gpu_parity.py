@@ -180,6 +180,20 @@ def test_feature_map_fp16_tensor_core_path(dev, rows, H):
     assert none is None and torch.equal(gx2, gx)
 
 
+def test_state_total_matches_single_cta_reduction(dev):
+    """Partials over runs of tokens (many CTAs per sequence) summed == the one-CTA-per-sequence reduction == oracle."""
+    from rfa_b200 import ops
+    for T, BH in [(5000, 2), (300, 3), (1, 1)]:
+        q, k, v, g = feats(T, BH, seed=T + BH)
+        kd, vd = k.to(dev).half(), v.to(dev).half()
+        s1, z1 = ops.state_total(kd, vd)
+        s0, z0 = ops.cross_state_fwd(kd.view(T, 1, BH, -1), vd.view(T, 1, BH, -1), None)
+        rs, rz = O.segment_state(k, v)
+        assert_close(s1, rs, "S", rel=1e-4, mabs=1e-3); assert_close(z1, rz, "z", rel=1e-4, mabs=1e-3)
+        assert_close(s1, s0.view(BH, 128, 64).cpu(), "S vs single", rel=1e-5, mabs=1e-3)
+        assert_close(z1, z0.view(BH, 128).cpu(), "z vs single", rel=1e-5, mabs=1e-3)
+
+
 # ----------------------------------------------------------------------------- decode
 def test_decode_against_upstream_fixture(dev):
     from rfa_b200.causal_attention import incremental_rfa
