@@ -448,15 +448,18 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_ld32(tmem + lane_addr + bqColDQ + piece * 32, a);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int k0 = piece * 32 + j * 8;
-          const float4 z0 = *reinterpret_cast<const float4*>(zs + k0), z1 = *reinterpret_cast<const float4*>(zs + k0 + 4);
-          uint4 u;
-          u.x = pack_half2(fmaf(gz, z0.x, __uint_as_float(a[j * 8 + 0])), fmaf(gz, z0.y, __uint_as_float(a[j * 8 + 1])));
-          u.y = pack_half2(fmaf(gz, z0.z, __uint_as_float(a[j * 8 + 2])), fmaf(gz, z0.w, __uint_as_float(a[j * 8 + 3])));
-          u.z = pack_half2(fmaf(gz, z1.x, __uint_as_float(a[j * 8 + 4])), fmaf(gz, z1.y, __uint_as_float(a[j * 8 + 5])));
-          u.w = pack_half2(fmaf(gz, z1.z, __uint_as_float(a[j * 8 + 6])), fmaf(gz, z1.w, __uint_as_float(a[j * 8 + 7])));
-          if (live) *reinterpret_cast<uint4*>(grow + k0) = u;
+        for (int j = 0; j < 2; ++j) {              // 32 bytes (one sector) per store: half as many passes of the load/store unit
+          uint32_t o[8];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int k0 = piece * 32 + j * 16 + e * 8, a0 = j * 16 + e * 8;
+            const float4 z0 = *reinterpret_cast<const float4*>(zs + k0), z1 = *reinterpret_cast<const float4*>(zs + k0 + 4);
+            o[e * 4 + 0] = pack_half2(fmaf(gz, z0.x, __uint_as_float(a[a0 + 0])), fmaf(gz, z0.y, __uint_as_float(a[a0 + 1])));
+            o[e * 4 + 1] = pack_half2(fmaf(gz, z0.z, __uint_as_float(a[a0 + 2])), fmaf(gz, z0.w, __uint_as_float(a[a0 + 3])));
+            o[e * 4 + 2] = pack_half2(fmaf(gz, z1.x, __uint_as_float(a[a0 + 4])), fmaf(gz, z1.y, __uint_as_float(a[a0 + 5])));
+            o[e * 4 + 3] = pack_half2(fmaf(gz, z1.z, __uint_as_float(a[a0 + 6])), fmaf(gz, z1.w, __uint_as_float(a[a0 + 7])));
+          }
+          if (live) st_global_v8(grow + piece * 32 + j * 16, o);
         }
       }
       tc_fence_before_sync();
