@@ -10,9 +10,9 @@
 // The score matrices are computed TRANSPOSED (keys on the TMEM lanes) so that their fp16
 // versions can stay in tensor memory as the A operands of the dK / dV products.
 //
-// Warp roles (352 threads): warp 0 TMA producer, warps 1 and 10 MMA issuers, warps 2..5 score
-// group (scales g in place, packs Pt and dAt), warps 6..9 output/state group (grad_k, grad_v,
-// state export, dz).  Issuing one tcgen05.mma costs the issuing thread about as long as the
+// Warp roles (480 threads): warp 0 TMA producer, warps 1 and 10 MMA issuers, warps 2..5 score
+// group 1 (packs Pt), warps 11..14 score group 2 (scales g in place, packs dAt), warps 6..9
+// output/state group (grad_k, grad_v, state export, dz).  Issuing one tcgen05.mma costs the issuing thread about as long as the
 // tensor pipe needs to execute it (N <= 128), so the 48 MMAs of a chunk are split over two
 // issuers: A (At, dAt, dK) and B (dV, dS).  The products that read the exported state tile are
 // issued first in a chunk and the state update right after g is scaled, which keeps the serial
@@ -23,7 +23,7 @@
 
 namespace rfa {
 
-constexpr int kKvThreads = 352;
+constexpr int kKvThreads = 480;
 
 #ifdef RFA_TRACE
 // tuning builds only: switch parts of the kernel off (results are then wrong) to see what the chain is sensitive to
@@ -36,15 +36,18 @@ extern "C" int rfa_trace_set_dbg_kv(int v) { return (int)cudaMemcpyToSymbol(g_kv
 
 constexpr uint32_t kvQ = 0, kvK = 2 * kBox, kvV = 4 * kBox, kvG = 5 * kBox, kvStage = 6 * kBox;   // 98304 per stage
 constexpr uint32_t kvS = 2 * kvStage;            // dS as an operand: [128 k][64 n] fp16, swizzled
-constexpr uint32_t kvDz = kvS + kBox;            // fp32 [128]
-constexpr uint32_t kvGz = kvDz + 512;            // fp32 [2][128]: gz of the chunk's query rows
+constexpr uint32_t kvDz = kvS + kBox;            // fp32 [2][128]: dz entering chunk i lives in buffer i & 1
+constexpr uint32_t kvGz = kvDz + 1024;           // fp32 [2][128]: gz of the chunk's query rows
 constexpr uint32_t kvBar = kvGz + 1024;
 constexpr uint32_t kvSmem = kvBar + 256 + 1024;
 
 constexpr uint32_t kvColAt = 0, kvColDAt = 128, kvColDK = 256, kvColDV = 384, kvColDS = 448;
 enum { vFull = 0, vEmpty = 2, vAt = 4, vG = 5, vDAt = 7, vP = 8, vDA16 = 9, vDK = 10, vDV = 11, vDKFree = 12, vDVFree = 13,
-       vS = 14, vSt = 15, vY = 16, vSR = 17, vNum = 18 };
+       vS = 14, vSt = 15, vY = 16, vSR = 17, vStaged = 18, vNum = 20 };
 // vSR: both issuers have finished reading the exported state tile (one commit each per chunk).
+// vEmpty: the Q and g tiles of a stage may be refilled (every product of the chunk is complete, dz has been summed);
+// vStaged: grad_k / grad_v are staged in its K and V tiles -- the producer thread stores them and refills those two
+// once the store has read them, so the output group never waits for a store.
 // vG is one barrier per stage: the output group waits on it late in a chunk, when the score group may already
 // have completed the next chunk's phase; with one barrier per stage a waiter is never two phases behind.
 
@@ -71,7 +74,8 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const float* dz_in = dz_seg ? dz_seg + slot * kK : nullptr;
 
   if (tid == 0) {
-    mbar_init(&bars[vFull], 1); mbar_init(&bars[vFull + 1], 1);
+    mbar_init(&bars[vFull], 2); mbar_init(&bars[vFull + 1], 2);      // two requests per use: (g, Q) and (K, V)
+    mbar_init(&bars[vStaged], 128); mbar_init(&bars[vStaged + 1], 128);
     mbar_init(&bars[vEmpty], 128); mbar_init(&bars[vEmpty + 1], 128);
     mbar_init(&bars[vAt], 1); mbar_init(&bars[vG], 128); mbar_init(&bars[vG + 1], 128); mbar_init(&bars[vDAt], 1); mbar_init(&bars[vP], 128);
     mbar_init(&bars[vDA16], 128); mbar_init(&bars[vDK], 1); mbar_init(&bars[vDV], 1);
@@ -92,25 +96,47 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
+    // It also issues the stores of the staged gradients, and refills a stage in two halves: g and Q as soon as the
+    // chunk two earlier has no further use for them, K and V once its staged gradients have been read out.
     if (lane == 0) {
       RFA_TRACE_DECL(0)
+      auto chunk_t0 = [&](int j) { return (int)(t_begin + (int64_t)(nchunk - 1 - j) * kTC); };
+      auto store_chunk = [&](int j) {
+        unsigned char* base = sm + (j & 1) * kvStage;
+        tma_store_3d(&tm_gk, base + kvK, 0, bh, chunk_t0(j));
+        tma_store_3d(&tm_gk, base + kvK + kBox, 64, bh, chunk_t0(j));
+        tma_store_3d(&tm_gv, base + kvV, 0, bh, chunk_t0(j));
+        tma_store_commit();
+      };
+      bool ok = true;
       for (int i = 0; i < nchunk; ++i) {
         const int st = i & 1;
-        RFA_TRACE_EV(1, i);
-        if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
         unsigned char* base = sm + st * kvStage;
-        const int t0 = (int)(t_begin + (int64_t)(nchunk - 1 - i) * kTC);
+        const int t0 = chunk_t0(i);
         uint64_t* fb = &bars[vFull + st];
+        RFA_TRACE_EV(1, i);
+        if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); ok = false; break; }
         RFA_TRACE_EV(2, i);
-        if (KV_DBG(2)) { mbar_arrive(fb); continue; }
-        mbar_arrive_expect_tx(fb, kvStage);
+        mbar_arrive_expect_tx(fb, 3 * kBox);
         tma_load_3d(base + kvG, &tm_g, fb, 0, bh, t0);
-        tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
-        tma_load_3d(base + kvK + kBox, &tm_k, fb, 64, bh, t0);
         tma_load_3d(base + kvQ, &tm_q, fb, 0, bh, t0);
         tma_load_3d(base + kvQ + kBox, &tm_q, fb, 64, bh, t0);
+        if (i >= 2) {
+          if (!mbar_wait(&bars[vStaged + st], ((i >> 1) + 1) & 1)) { tc_fail(25); ok = false; break; }
+          store_chunk(i - 2);
+          tma_store_wait_read<0>();                  // the K and V tiles have been read out
+        }
+        RFA_TRACE_EV(3, i);
+        mbar_arrive_expect_tx(fb, 3 * kBox);
+        tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
+        tma_load_3d(base + kvK + kBox, &tm_k, fb, 64, bh, t0);
         tma_load_3d(base + kvV, &tm_v, fb, 0, bh, t0);
       }
+      for (int j = (nchunk >= 2 ? nchunk - 2 : 0); ok && j < nchunk; ++j) {
+        if (!mbar_wait(&bars[vStaged + (j & 1)], (j >> 1) & 1)) { tc_fail(26); break; }
+        store_chunk(j);
+      }
+      tma_store_wait<0>();
     }
   } else if (warp == 1 || warp == 10) {
     // ------------------------------------------------------------------ MMA issuers
@@ -207,47 +233,12 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------------ score group
+    // ------------------------------------------------------------------ score group 1: Pt[s][t] = At[s][t] for t >= s
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;           // query row t (scaling g) / key row s (packing)
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;   // key row s = quarter * 32 + lane
     RFA_TRACE_DECL(2)
     for (int i = 0; i < nchunk; ++i) {
-      const int st = i & 1;
       const uint32_t ph = i & 1;
-      unsigned char* stage = sm + st * kvStage;
-      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
-      float* gzs = gz_buf + (i & 1) * 128;
-      // ---- gs = g / den over the staged g tile; gz of this thread's query row
-      float inv = 1.f, gz = 0.f;
-      if (t0 + row < t_end) {
-        inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
-        gz = ws_gz[(size_t)bh * T + t0 + row];
-      }
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(20, i);
-      if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(21, i);
-      if (!KV_DBG(0) && !KV_DBG(5)) {
-        unsigned char* grow = stage + kvG;
-        // all eight loads of the row first (independent), then the scaling, then the stores: a load behind an in-place
-        // store would wait for it, and shared-memory round trips of this warp queue behind the tensor pipe's reads
-        uint4 gu[8];
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) gu[ch] = *reinterpret_cast<const uint4*>(grow + row_chunk1(row, ch));
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint4 u = gu[ch];
-          float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
-          gu[ch].x = pack_half2(f0.x * inv, f0.y * inv); gu[ch].y = pack_half2(f1.x * inv, f1.y * inv);
-          gu[ch].z = pack_half2(f2.x * inv, f2.y * inv); gu[ch].w = pack_half2(f3.x * inv, f3.y * inv);
-        }
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(grow + row_chunk1(row, ch)) = gu[ch];
-        gzs[row] = gz;
-      }
-      fence_async_smem();
-      mbar_arrive(&bars[vG + st]);
-      // ---- Pt[s][t] = At[s][t] for t >= s  (fp16 over the first 64 columns)
       if (warp == 5 && lane == 0) RFA_TRACE_EV(22, i);
       if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
       if (warp == 5 && lane == 0) RFA_TRACE_EV(23, i);
@@ -255,7 +246,6 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
-        if (KV_DBG(0)) continue;
         if (piece >= quarter) {
           uint32_t a[32];
           tmem_ld32(tmem + lane_addr + kvColAt + piece * 32, a);
@@ -278,16 +268,57 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vP]);
+      if (warp == 5 && lane == 0) RFA_TRACE_EV(24, i);
+    }
+  } else if (warp >= 11) {
+    // ------------------------------------------------------------------ score group 2: gs = g / den, then dAt
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // query row t (scaling g) / key row s (packing)
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    RFA_TRACE_DECL(5)
+    for (int i = 0; i < nchunk; ++i) {
+      const int st = i & 1;
+      const uint32_t ph = i & 1;
+      unsigned char* stage = sm + st * kvStage;
+      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
+      float* gzs = gz_buf + (i & 1) * 128;
+      // ---- gs = g / den over the staged g tile; gz of this thread's query row
+      float inv = 1.f, gz = 0.f;
+      if (t0 + row < t_end) {
+        inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
+        gz = ws_gz[(size_t)bh * T + t0 + row];
+      }
+      if (warp == 11 && lane == 0) RFA_TRACE_EV(20, i);
+      if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
+      if (warp == 11 && lane == 0) RFA_TRACE_EV(21, i);
+      {
+        unsigned char* grow = stage + kvG;
+        // all eight loads of the row first (independent), then the scaling, then the stores
+        uint4 gu[8];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) gu[ch] = *reinterpret_cast<const uint4*>(grow + row_chunk1(row, ch));
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 u = gu[ch];
+          float2 f0 = unpack_half2(u.x), f1 = unpack_half2(u.y), f2 = unpack_half2(u.z), f3 = unpack_half2(u.w);
+          gu[ch].x = pack_half2(f0.x * inv, f0.y * inv); gu[ch].y = pack_half2(f1.x * inv, f1.y * inv);
+          gu[ch].z = pack_half2(f2.x * inv, f2.y * inv); gu[ch].w = pack_half2(f3.x * inv, f3.y * inv);
+        }
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(grow + row_chunk1(row, ch)) = gu[ch];
+        gzs[row] = gz;
+      }
+      fence_async_smem();
+      mbar_arrive(&bars[vG + st]);
+      if (warp == 11 && lane == 0) RFA_TRACE_EV(27, i);
       // ---- dAt[s][t] = (v_s . gs_t + gz_t) for t >= s; gz of all rows is there once vG completed
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(12); break; }
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(24, i);
       if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(25, i);
+      if (warp == 11 && lane == 0) RFA_TRACE_EV(25, i);
       tc_fence_after_sync();
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t p[16];
-        if (KV_DBG(0)) continue;
         if (piece >= quarter) {
           uint32_t a[32];
           tmem_ld32(tmem + lane_addr + kvColDAt + piece * 32, a);
@@ -315,9 +346,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vDA16]);
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(26, i);
+      if (warp == 11 && lane == 0) RFA_TRACE_EV(26, i);
     }
-  } else {
+  } else if (warp < 10) {
     // ------------------------------------------------------------------ output / state group
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // key row s of the chunk / state row k
@@ -346,9 +377,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       const int st = i & 1;
       const uint32_t ph = i & 1;
       unsigned char* stage = sm + st * kvStage;
-      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
       const float* gzs = gz_buf + (i & 1) * 128;
-      // dzs of the previous chunk is final for every thread
+      const float* dz_cur = dzs + (i & 1) * 128;
+      // every thread has written its dz entering this chunk and finished the previous chunk's reads of the other buffer
       if (!epi_sync(&bars[vY], y_phase)) { tc_fail(14); ok = false; break; }
       // ---- the state update is complete and both issuers have finished reading the old state tile
       if (ytid == 0) RFA_TRACE_EV(30, i);
@@ -357,8 +388,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (ytid == 0) RFA_TRACE_EV(31, i);
       tc_fence_after_sync();
       // ---- reverse state after this chunk -> fp16 operand tile (the serial chain of the scan)
-      if (i + 1 < nchunk && KV_DBG(1)) { tc_fence_before_sync(); mbar_arrive(&bars[vSt]); }
-      if (i + 1 < nchunk && !KV_DBG(1)) {
+      if (i + 1 < nchunk) {
         uint32_t r[64];
         tmem_ld32(tmem + lane_addr + kvColDS, r);
         tmem_ld32(tmem + lane_addr + kvColDS + 32, r + 32);
@@ -369,27 +399,29 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         mbar_arrive(&bars[vSt]);
       }
       if (ytid == 0) RFA_TRACE_EV(32, i);
-      // ---- grad_v -> V tile
-      if (KV_DBG(1)) { mbar_arrive(&bars[vDVFree]); mbar_arrive(&bars[vDKFree]); }
-      if (!KV_DBG(1)) {
-        uint32_t r[64];
-        if (!mbar_wait(&bars[vDV], ph)) { tc_fail(13); ok = false; break; }
-        tc_fence_after_sync();
-        tmem_ld32(tmem + lane_addr + kvColDV, r);
-        tmem_ld32(tmem + lane_addr + kvColDV + 32, r + 32);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        mbar_arrive(&bars[vDVFree]);
-        // issuer A's last product of the chunk is complete: nothing reads the V, K and Q tiles any more (issuer B
-        // finished with vDV), so the V and K tiles become staging
-        if (!mbar_wait(&bars[vDK], ph)) { tc_fail(19); ok = false; break; }
-        tc_fence_after_sync();
-        store_state_row(stage + kvV, row, r);
-      }
+      // ---- dz += Q^T gz while the chunk's other products are in flight (the state MMA waited on vG, so gz is there);
+      //      the new dz goes to the other buffer
+      if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
+      dzs[((i + 1) & 1) * 128 + row] = dz_cur[row] + column_sum2(stage + kvQ, quarter, lane, gzs);
+      if (ytid == 0) RFA_TRACE_EV(34, i);
+      // ---- grad_v: issuer B's last product of the chunk
+      uint32_t r[64];
+      if (!mbar_wait(&bars[vDV], ph)) { tc_fail(13); ok = false; break; }
+      tc_fence_after_sync();
+      tmem_ld32(tmem + lane_addr + kvColDV, r);
+      tmem_ld32(tmem + lane_addr + kvColDV + 32, r + 32);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[vDVFree]);
+      // issuer A's last product is complete as well: no product reads the stage any more.  Its Q and g tiles can be
+      // refilled; V and K become staging.
+      if (!mbar_wait(&bars[vDK], ph)) { tc_fail(19); ok = false; break; }
+      tc_fence_after_sync();
+      mbar_arrive(&bars[vEmpty + st]);
+      store_state_row(stage + kvV, row, r);
       // ---- grad_k = dK + dz_next -> K tile
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
-        if (KV_DBG(1)) continue;
         uint32_t a[32];
         tmem_ld32(tmem + lane_addr + kvColDK + piece * 32, a);
         tmem_ld_wait();
@@ -397,7 +429,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int k0 = piece * 32 + j * 8;
-          const float4 z0 = *reinterpret_cast<const float4*>(dzs + k0), z1 = *reinterpret_cast<const float4*>(dzs + k0 + 4);
+          const float4 z0 = *reinterpret_cast<const float4*>(dz_cur + k0), z1 = *reinterpret_cast<const float4*>(dz_cur + k0 + 4);
           uint4 u;
           u.x = pack_half2(__uint_as_float(a[j * 8 + 0]) + z0.x, __uint_as_float(a[j * 8 + 1]) + z0.y);
           u.y = pack_half2(__uint_as_float(a[j * 8 + 2]) + z0.z, __uint_as_float(a[j * 8 + 3]) + z0.w);
@@ -407,23 +439,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
       }
       fence_async_smem();
+      mbar_arrive(&bars[vStaged + st]);            // the producer thread stores the two tiles and refills them
       if (ytid == 0) RFA_TRACE_EV(33, i);
-      if (!epi_sync(&bars[vY], y_phase)) { tc_fail(16); ok = false; break; }   // staging complete; dzs reads done
-      if (ytid == 0 && !KV_DBG(1) && !KV_DBG(4)) {
-        tma_store_3d(&tm_gk, stage + kvK, 0, bh, (int)t0);
-        tma_store_3d(&tm_gk, stage + kvK + kBox, 64, bh, (int)t0);
-        tma_store_3d(&tm_gv, stage + kvV, 0, bh, (int)t0);
-        tma_store_commit();
-      }
-      // ---- dz += Q^T gz   (vG completed long ago; waiting on it here orders this thread after the writes of gz)
-      if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
-      if (!KV_DBG(1)) dzs[row] += column_sum2(stage + kvQ, quarter, lane, gzs);
-      if (ytid == 0) RFA_TRACE_EV(34, i);
-      if (ytid == 0) tma_store_wait_read<0>();
-      if (ytid == 0) RFA_TRACE_EV(35, i);
-      mbar_arrive(&bars[vEmpty + st]);
     }
-    if (ytid == 0) tma_store_wait<0>();
   }
   tc_fence_before_sync();
   __syncthreads();
