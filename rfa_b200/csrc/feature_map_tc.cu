@@ -145,7 +145,7 @@ int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int6
   cudaError_t e = cudaFuncSetAttribute(feature_map_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fm::kSmem);
   if (e != cudaSuccess) return fail((int)e, "feature_map_fwd: cannot reserve %u bytes of shared memory: %s", fm::kSmem, cudaGetErrorString(e));
   const int64_t ntile = (rows + kTC - 1) / kTC;
-  int64_t gx = (2LL * sms + H - 1) / H;
+  int64_t gx = 2LL * sms / H;                    // two CTAs per SM, and never more CTAs than fit at once
   if (gx > ntile) gx = ntile;
   if (gx < 1) gx = 1;
   feature_map_fwd_tc_kernel<<<dim3((unsigned)gx, H), fm::kThreads_, fm::kSmem, st>>>(tx, tp, w, rows, H, scale);
@@ -416,7 +416,7 @@ int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_p
   cudaError_t e = cudaFuncSetAttribute(feature_map_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fmb::kSmem);
   if (e != cudaSuccess) return fail((int)e, "feature_map_bwd: cannot reserve %u bytes of shared memory: %s", fmb::kSmem, cudaGetErrorString(e));
   const int64_t ntile = (rows + kTC - 1) / kTC;
-  int64_t gx = (sms + H - 1) / H;
+  int64_t gx = sms / H;                          // one CTA per SM (shared memory): never more CTAs than SMs, or a second wave runs
   if (gx > ntile) gx = ntile;
   if (gx < 1) gx = 1;
   feature_map_bwd_tc_kernel<<<dim3((unsigned)gx, H), fmb::kThreads_, fmb::kSmem, st>>>(tx, tg, to, w, g_w, rows, H, scale);
