@@ -308,8 +308,29 @@ def run_long(args, rank, local_rank, world):
     for _ in range(args.warmup):
         step()
     barrier()
+    # The step is ~40 short launches plus two all-gathers: issued eagerly it is bound by the host.  Capture it in a CUDA
+    # graph (kernels, NCCL all-gathers and the autograd backward alike); fall back to eager issue if capture fails.
+    run, mode = step, "eager"
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                step()
+            stream.wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            graph.replay()
+            torch.cuda.synchronize()
+            run, mode = graph.replay, "cuda graph"
+        except Exception as e:                      # noqa: BLE001 -- report and measure eagerly
+            mode = f"eager (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+    barrier()
     with ClockSampler(local_rank) as clk:
-        ms = timed(step, args.steps, stream)
+        ms = timed(run, args.steps, stream)
         barrier()
     t = torch.tensor([ms], device=device)
     if world > 1:
@@ -323,12 +344,18 @@ def run_long(args, rank, local_rank, world):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"causal RFA fwd+bwd, B1 H{Hh} T{Tt} d64 D64 fp16", "heads_x_sequence_shards": [g_h, g_s],
-                       "l2": "9.1 GB per step, far larger than L2"},
+                       "l2": "9.1 GB per step, far larger than L2", "issue": mode},
             "clocks": clk.summary, "gpu_launches": None,
             "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9 / world, "peak": hbm, "unit": "GB/s per GPU",
                          "frac": nbytes / (ms * 1e-3) / 1e9 / world / hbm, "peak_source": peak_src, "traffic": None}}), flush=True)
     if world > 1:
         dist.barrier()
+        torch.cuda.synchronize()
+        if mode == "cuda graph":
+            # tearing the process group down under a captured graph that holds NCCL kernels did not return here; every
+            # rank has finished its work and rank 0 has printed, so leave without running the destructors
+            sys.stdout.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
@@ -339,6 +366,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="long workload: issue the step eagerly instead of as a CUDA graph")
     ap.add_argument("--workload", default="headline", choices=["headline", "long"],
                     help="headline = B8 H16 T2048 (the metric's config); long = B1 H32 T131072, sequence-sharded")
     args = ap.parse_args()
