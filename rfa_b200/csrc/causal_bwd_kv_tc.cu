@@ -243,28 +243,33 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
       if (warp == 5 && lane == 0) RFA_TRACE_EV(23, i);
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int piece = 0; piece < 4; ++piece) {
-        uint32_t p[16];
-        if (piece >= quarter) {
-          uint32_t a[32];
-          tmem_ld32(tmem + lane_addr + kvColAt + piece * 32, a);
-          tmem_ld_wait();
+      // 32-column pieces right of the diagonal one need no mask, the diagonal one keeps columns >= lane, the rest are zero
+      auto pack_piece = [&](int piece, auto DIAG) {
+        constexpr bool diag = decltype(DIAG)::value;
+        uint32_t a[32], p[16];
+        tmem_ld32(tmem + lane_addr + kvColAt + piece * 32, a);
+        tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float x0 = __uint_as_float(a[e]), x1 = __uint_as_float(a[e + 1]);
-            if (piece == quarter) {
-              if (e < lane) x0 = 0.f;
-              if (e + 1 < lane) x1 = 0.f;
-            }
-            p[e >> 1] = pack_half2(x0, x1);
+        for (int e = 0; e < 32; e += 2) {
+          float x0 = __uint_as_float(a[e]), x1 = __uint_as_float(a[e + 1]);
+          if (diag) {
+            if (e < lane) x0 = 0.f;
+            if (e + 1 < lane) x1 = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) p[e] = 0u;
+          p[e >> 1] = pack_half2(x0, x1);
         }
         tmem_st16(tmem + lane_addr + kvColAt + piece * 16, p);
+      };
+      {
+        uint32_t zero[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) zero[e] = 0u;
+#pragma unroll 1
+        for (int piece = 0; piece < quarter; ++piece) tmem_st16(tmem + lane_addr + kvColAt + piece * 16, zero);
       }
+      pack_piece(quarter, std::true_type{});
+#pragma unroll 1
+      for (int piece = quarter + 1; piece < 4; ++piece) pack_piece(piece, std::false_type{});
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vP]);
@@ -316,33 +321,37 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
       if (warp == 11 && lane == 0) RFA_TRACE_EV(25, i);
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int piece = 0; piece < 4; ++piece) {
-        uint32_t p[16];
-        if (piece >= quarter) {
-          uint32_t a[32];
-          tmem_ld32(tmem + lane_addr + kvColDAt + piece * 32, a);
-          tmem_ld_wait();
+      auto pack_da = [&](int piece, auto DIAG) {
+        constexpr bool diag = decltype(DIAG)::value;
+        uint32_t a[32], p[16];
+        tmem_ld32(tmem + lane_addr + kvColDAt + piece * 32, a);
+        tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            const float4 gz4 = *reinterpret_cast<const float4*>(gzs + piece * 32 + e);
-            float x0 = __uint_as_float(a[e]) + gz4.x, x1 = __uint_as_float(a[e + 1]) + gz4.y;
-            float x2 = __uint_as_float(a[e + 2]) + gz4.z, x3 = __uint_as_float(a[e + 3]) + gz4.w;
-            if (piece == quarter) {
-              if (e < lane) x0 = 0.f;
-              if (e + 1 < lane) x1 = 0.f;
-              if (e + 2 < lane) x2 = 0.f;
-              if (e + 3 < lane) x3 = 0.f;
-            }
-            p[e >> 1] = pack_half2(x0, x1);
-            p[(e >> 1) + 1] = pack_half2(x2, x3);
+        for (int e = 0; e < 32; e += 4) {
+          const float4 gz4 = *reinterpret_cast<const float4*>(gzs + piece * 32 + e);
+          float x0 = __uint_as_float(a[e]) + gz4.x, x1 = __uint_as_float(a[e + 1]) + gz4.y;
+          float x2 = __uint_as_float(a[e + 2]) + gz4.z, x3 = __uint_as_float(a[e + 3]) + gz4.w;
+          if (diag) {
+            if (e < lane) x0 = 0.f;
+            if (e + 1 < lane) x1 = 0.f;
+            if (e + 2 < lane) x2 = 0.f;
+            if (e + 3 < lane) x3 = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) p[e] = 0u;
+          p[e >> 1] = pack_half2(x0, x1);
+          p[(e >> 1) + 1] = pack_half2(x2, x3);
         }
         tmem_st16(tmem + lane_addr + kvColDAt + piece * 16, p);
+      };
+      {
+        uint32_t zero[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) zero[e] = 0u;
+#pragma unroll 1
+        for (int piece = 0; piece < quarter; ++piece) tmem_st16(tmem + lane_addr + kvColDAt + piece * 16, zero);
       }
+      pack_da(quarter, std::true_type{});
+#pragma unroll 1
+      for (int piece = quarter + 1; piece < 4; ++piece) pack_da(piece, std::false_type{});
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vDA16]);

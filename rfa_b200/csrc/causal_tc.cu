@@ -217,28 +217,33 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(8); break; }
       tc_fence_after_sync();
       float rowsum = 0.f, rowsum_b = 0.f;
-#pragma unroll 1
-      for (int piece = 0; piece < 4; ++piece) {
-        uint32_t p[16];
-        if (piece <= quarter) {
-          uint32_t a[32];
-          tmem_ld32(tmem + lane_addr + colA + piece * 32, a);
-          tmem_ld_wait();
+      // 32-column pieces left of the diagonal one need no mask, the diagonal one keeps columns <= lane, the rest are zero
+      auto pack_piece = [&](int piece, auto DIAG) {
+        constexpr bool diag = decltype(DIAG)::value;
+        uint32_t a[32], p[16];
+        tmem_ld32(tmem + lane_addr + colA + piece * 32, a);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = __uint_as_float(a[i]), x1 = __uint_as_float(a[i + 1]);
-            if (piece == quarter) {
-              if (i > lane) x0 = 0.f;
-              if (i + 1 > lane) x1 = 0.f;
-            }
-            if (i & 2) rowsum_b += x0 + x1; else rowsum += x0 + x1;
-            p[i >> 1] = pack_half2(x0, x1);
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = __uint_as_float(a[i]), x1 = __uint_as_float(a[i + 1]);
+          if (diag) {
+            if (i > lane) x0 = 0.f;
+            if (i + 1 > lane) x1 = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) p[i] = 0u;
+          if (i & 2) rowsum_b += x0 + x1; else rowsum += x0 + x1;
+          p[i >> 1] = pack_half2(x0, x1);
         }
         tmem_st16(tmem + lane_addr + colA + piece * 16, p);
+      };
+#pragma unroll 1
+      for (int piece = 0; piece < quarter; ++piece) pack_piece(piece, std::false_type{});
+      pack_piece(quarter, std::true_type{});
+      {
+        uint32_t zero[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) zero[i] = 0u;
+#pragma unroll 1
+        for (int piece = quarter + 1; piece < 4; ++piece) tmem_st16(tmem + lane_addr + colA + piece * 16, zero);
       }
       rs[st * 128 + row] = rowsum + rowsum_b;
       tmem_st_wait();
