@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the upstream Python sources.
 
-Run once, in a container that has the upstream checkout (default
-``/root/reference/random_feature_attention``; override with ``RFA_REFERENCE``):
+Run once, in a container that has the upstream checkout (set ``RFA_REFERENCE`` to its
+``random_feature_attention`` directory if it is not at the default location):
 
     python tests/golden/make_golden.py
 
