@@ -105,3 +105,37 @@ def test_shard_bounds_cover_the_sequence():
         assert spans[0][0] == 0 and spans[-1][1] == T
         assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
         assert all((lo % 128 == 0) or lo == T for lo, _ in spans)
+
+
+def test_a_lone_shard_skips_the_exchange():
+    """Without a process group (or in a group of one) the whole sequence is local: no shard total is computed, no
+    carry is exchanged, and the result equals the plain oracle.  Kernels without a one-call backward fall back to
+    the two sweeps with empty carries."""
+    from rfa_b200 import sharded
+
+    calls = []
+
+    class Counting(OracleKernels):
+        @staticmethod
+        def segment_state(k, v):
+            calls.append("segment_state")
+            return OracleKernels.segment_state(k, v)
+
+    saved = sharded.SequenceShardedRFA.kernels
+    sharded.SequenceShardedRFA.kernels = Counting
+    try:
+        gen = torch.Generator().manual_seed(3)
+        T, BH = 70, 2
+        q = (torch.rand(T, BH, 128, generator=gen, dtype=torch.float64) * 0.2).requires_grad_(True)
+        k = (torch.rand(T, BH, 128, generator=gen, dtype=torch.float64) * 0.2).requires_grad_(True)
+        v = torch.randn(T, BH, 64, generator=gen, dtype=torch.float64).requires_grad_(True)
+        g = torch.randn(T, BH, 64, generator=gen, dtype=torch.float64)
+        out = sharded.sequence_sharded_causal_rfa(q, k, v, None)
+        out.backward(g)
+        assert calls == []
+        ro = O.causal_forward(q.detach(), k.detach(), v.detach())
+        rq, rk, rv = O.causal_backward(q.detach(), k.detach(), v.detach(), g)
+        for a, b in ((out.detach(), ro), (q.grad, rq), (k.grad, rk), (v.grad, rv)):
+            assert torch.allclose(a, b, rtol=1e-10, atol=1e-12)
+    finally:
+        sharded.SequenceShardedRFA.kernels = saved
