@@ -51,11 +51,20 @@ int rfa_version(void);
 const char* rfa_last_error(void);
 
 /* Device-side health of the tensor-core kernels on the current device.  Every wait
- * inside them is bounded; a wait that runs out records its site here and the kernel
- * leaves early (outputs are then invalid).  Returns 0 when no wait ever ran out, else
- * the site code; synchronises the device and clears the flag.  No upstream
- * counterpart (upstream never reads launch or device errors, cuda/forward.cu:155). */
+ * inside them is bounded (about four seconds of wall-clock time); a wait that runs out
+ * records its site and the kernel leaves early (its outputs are then invalid).
+ * rfa_debug_status(): 0 when no wait ever ran out, else 100 * kernel family + site code;
+ * synchronises the device and clears the flag.
+ * rfa_status_mirror_enable(): makes the kernels on the current device also write that
+ * code to one word of mapped host memory (allocated once per process with cudaHostAlloc
+ * by the first call; call it once per device, outside stream capture).
+ * rfa_status_peek(): that word -- no synchronisation, no clearing -- so a host can look
+ * after every call and learn of a failure in an EARLIER kernel without stalling.
+ * No upstream counterpart (upstream never reads launch or device errors,
+ * cuda/forward.cu:155). */
 int rfa_debug_status(void);
+int rfa_status_mirror_enable(void);
+int rfa_status_peek(void);
 
 /* ------------------------------------------------------------------------
  * Feature map  phi(x) = scale * [sin(W xhat) | cos(W xhat)], xhat = x/(|x|+1e-3)
@@ -117,12 +126,16 @@ int rfa_causal_bwd(const void* q, const void* k, const void* v, const void* g,
  *   - T * BH must not exceed rfa_causal_bwd_noalloc_max_token_heads() (524288);
  *     larger problems are refused with RFA_EWORKSPACE.
  *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress); make that call before starting any stream capture.
+ *     (cudaGetSymbolAddress), and a host thread's first launch of any kernel of
+ *     this library binds the device's primary context to that thread
+ *     (cudaSetDevice on the current device); make the first call on each device
+ *     and from each calling thread before starting any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels can
  *     overlap on the GPU (different streams, no dependency) race on it.  Calls
  *     on one stream are safe.  Nothing in it needs clearing between calls: each
  *     call's first sweep rewrites every element its second sweep reads.
- *   - Calls neither cudaMalloc/cudaFree nor any allocating library routine. */
+ *   - Allocates nothing: no cudaMalloc, cudaFree, cudaHostAlloc or allocating
+ *     library routine is called, on the first call or later. */
 int64_t rfa_causal_bwd_noalloc_max_token_heads(void);
 int rfa_causal_bwd_noalloc(const void* q, const void* k, const void* v, const void* g,
                            void* gq, void* gk, void* gv,

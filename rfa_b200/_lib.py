@@ -25,6 +25,8 @@ SIGNATURES = {
     "rfa_version": (_int, []),
     "rfa_last_error": (C.c_char_p, []),
     "rfa_debug_status": (_int, []),
+    "rfa_status_mirror_enable": (_int, []),
+    "rfa_status_peek": (_int, []),
     "rfa_feature_map_fwd": (_int, [_vp, _int, _vp, _vp, _int, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_feature_map_bwd": (_int, [_vp, _int, _vp, _vp, _int, _vp, _int, _vp, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_causal_workspace_bytes": (_sz, [_i64, _int, _int, _int]),
@@ -68,8 +70,28 @@ def last_error() -> str:
     return load().rfa_last_error().decode("utf-8", "replace")
 
 
+_mirrored = set()
+
+
+def watch_device(index: int) -> None:
+    """Once per device (with that device current): have the kernels mirror a bounded wait that ran out into a word of
+    mapped host memory, which ``check`` looks at after every call."""
+    if index in _mirrored:
+        return
+    status = load().rfa_status_mirror_enable()
+    if status != 0:
+        raise RuntimeError(f"rfa_status_mirror_enable failed with status {status}: {last_error()}")
+    _mirrored.add(index)
+
+
 def check(status: int, what: str) -> None:
     if status == 0:
+        code = load().rfa_status_peek()         # a plain host read: no synchronisation
+        if code:
+            load().rfa_debug_status()           # synchronise and clear, so that the error is reported once
+            raise RuntimeError(
+                f"rfa_b200: a bounded wait inside a kernel launched before or by {what} ran out (site code {code}); "
+                "results computed since are invalid")
         return
     msg = f"{what} failed with status {status}: {last_error()}"
     if status < 0 and status != -5:

@@ -2,6 +2,8 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace rfa {
@@ -23,11 +25,16 @@ int check_launch(const char* what) {
   return (int)e;
 }
 
-int tc_status_causal_fwd();
-int tc_status_causal_bwd();
-int tc_status_causal_bwd_kv();
-int tc_status_cross();
-int tc_status_feature_map();
+// per kernel family (one translation unit each): read-and-clear of the device status word, and the setter of the
+// mapped host word its kernels mirror a failure into
+#define RFA_TC_FAMILIES(X) X(causal_fwd, 1) X(causal_bwd, 2) X(causal_bwd_kv, 3) X(cross, 4) X(feature_map, 5)
+#define RFA_DECLARE(name, id) int tc_status_##name(); int tc_mirror_##name(int*);
+RFA_TC_FAMILIES(RFA_DECLARE)
+#undef RFA_DECLARE
+
+static std::mutex g_mirror_mu;
+static int* g_mirror_word = nullptr;            // one word of mapped, portable host memory per process
+static bool g_mirror_on[64] = {};               // per device ordinal: kernels there know the word
 
 }  // namespace rfa
 
@@ -36,13 +43,45 @@ int tc_status_feature_map();
 // the device and clears the flags.
 extern "C" int rfa_debug_status(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1000;
-  const int f = rfa::tc_status_causal_fwd(), b = rfa::tc_status_causal_bwd();
-  if (f) return f < 0 ? f : 100 + f;
-  if (b) return b < 0 ? b : 200 + b;
-  if (const int kv = rfa::tc_status_causal_bwd_kv()) return kv < 0 ? kv : 300 + kv;
-  if (const int x = rfa::tc_status_cross()) return x < 0 ? x : 400 + x;
-  if (const int f2 = rfa::tc_status_feature_map()) return f2 < 0 ? f2 : 500 + f2;
+  int first = 0;
+#define RFA_READ(name, id)                                   \
+  {                                                          \
+    const int v = rfa::tc_status_##name();                   \
+    if (v && !first) first = v < 0 ? v : 100 * id + v;       \
+  }
+  RFA_TC_FAMILIES(RFA_READ)
+#undef RFA_READ
+  if (rfa::g_mirror_word) *reinterpret_cast<volatile int*>(rfa::g_mirror_word) = 0;
+  return first;
+}
+
+extern "C" int rfa_status_mirror_enable(void) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return rfa::fail((int)e, "status_mirror_enable: cudaGetDevice: %s", cudaGetErrorString(e));
+  RFA_REQUIRE(dev >= 0 && dev < 64, RFA_EUNSUPPORTED, "status_mirror_enable: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(rfa::g_mirror_mu);
+  if (rfa::g_mirror_on[dev]) return 0;
+  if (!rfa::g_mirror_word) {
+    void* p = nullptr;
+    e = cudaHostAlloc(&p, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e != cudaSuccess) return rfa::fail((int)e, "status_mirror_enable: cudaHostAlloc: %s", cudaGetErrorString(e));
+    *static_cast<int*>(p) = 0;
+    rfa::g_mirror_word = static_cast<int*>(p);
+  }
+  int* devp = nullptr;
+  e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&devp), rfa::g_mirror_word, 0);
+  if (e != cudaSuccess) return rfa::fail((int)e, "status_mirror_enable: cudaHostGetDevicePointer: %s", cudaGetErrorString(e));
+#define RFA_SET(name, id) \
+  if (int r = rfa::tc_mirror_##name(devp)) return rfa::fail(r, "status_mirror_enable: cannot set the mirror of " #name);
+  RFA_TC_FAMILIES(RFA_SET)
+#undef RFA_SET
+  rfa::g_mirror_on[dev] = true;
   return 0;
+}
+
+extern "C" int rfa_status_peek(void) {
+  return rfa::g_mirror_word ? *reinterpret_cast<volatile int*>(rfa::g_mirror_word) : 0;
 }
 
 extern "C" int rfa_version(void) { return RFA_B200_VERSION; }

@@ -7,7 +7,7 @@
 // With few (batch, head) pairs a sequence is cut into segments that run as separate CTAs;
 // the states at their boundaries come from a reduction pre-pass plus an exclusive scan, the
 // same primitive a multi-device split of the sequence uses.
-#include "tiles.cuh"
+#include "common.cuh"
 
 namespace rfa {
 
@@ -58,8 +58,8 @@ static CausalPlan plan_causal(int64_t T, int BH) {
 }
 
 struct CausalWs {
-  float* den;      // [T][BH]   clamped denominators
-  float* gz;       // [T][BH]   gradient w.r.t. the raw denominator
+  float* den;      // [BH][T]   clamped denominators
+  float* gz;       // [BH][T]   gradient w.r.t. the raw denominator
   float* s_seg;    // [BH][nseg][K*d]  forward state entering each segment
   float* z_seg;    // [BH][nseg][K]
   float* ds_seg;   // [BH][nseg][K*d]  reverse state entering each segment
@@ -153,9 +153,9 @@ extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void*
                               void* workspace, size_t workspace_bytes,
                               int64_t T, int BH, int K, int d, rfa_stream_t stream) {
   if (int e = check_geometry("causal_fwd", T, BH, K, d)) return e;
-  RFA_REQUIRE(q && k && v && out, RFA_EINVAL, "causal_fwd: null pointer");
   RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (s_out == nullptr) == (z_out == nullptr), RFA_EINVAL,
               "causal_fwd: s/z pointers must be given in pairs");
+  RFA_REQUIRE(T == 0 || (q && k && v && out), RFA_EINVAL, "causal_fwd: null pointer");   // empty arrays have no address
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(s_in) && aligned16(z_in) &&
                   aligned16(s_out) && aligned16(z_out), RFA_EALIGN, "causal_fwd: 16-byte alignment required");
   const CausalPlan p = plan_causal(T, BH);
@@ -189,7 +189,7 @@ extern "C" int rfa_causal_bwd_q(const void* q, const void* k, const void* v, con
                                 void* workspace, size_t workspace_bytes,
                                 int64_t T, int BH, int K, int d, rfa_stream_t stream) {
   if (int e = check_geometry("causal_bwd_q", T, BH, K, d)) return e;
-  RFA_REQUIRE(q && k && v && g && gq, RFA_EINVAL, "causal_bwd_q: null pointer");
+  RFA_REQUIRE(T == 0 || (q && k && v && g && gq), RFA_EINVAL, "causal_bwd_q: null pointer");   // empty arrays have no address
   RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (ds_seg == nullptr) == (dz_seg == nullptr), RFA_EINVAL,
               "causal_bwd_q: s/z pointers must be given in pairs");
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) && aligned16(gq) && aligned16(s_in) &&
@@ -228,7 +228,7 @@ extern "C" int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, co
                                  const float* ds_in, const float* dz_in, void* workspace, size_t workspace_bytes,
                                  int64_t T, int BH, int K, int d, rfa_stream_t stream) {
   if (int e = check_geometry("causal_bwd_kv", T, BH, K, d)) return e;
-  RFA_REQUIRE(q && k && v && g && gk && gv, RFA_EINVAL, "causal_bwd_kv: null pointer");
+  RFA_REQUIRE(T == 0 || (q && k && v && g && gk && gv), RFA_EINVAL, "causal_bwd_kv: null pointer");
   RFA_REQUIRE((ds_in == nullptr) == (dz_in == nullptr), RFA_EINVAL, "causal_bwd_kv: ds/dz must be given in pairs");
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) && aligned16(gk) && aligned16(gv) &&
                   aligned16(ds_in) && aligned16(dz_in), RFA_EALIGN, "causal_bwd_kv: 16-byte alignment required");
@@ -262,7 +262,7 @@ extern "C" int rfa_cross_state_fwd(const void* phi_k, const void* v, const uint8
   RFA_REQUIRE(B > 0 && H > 0, RFA_EINVAL, "cross_state_fwd: B=%d H=%d", B, H);
   const int BH = B * H;
   if (int e = check_geometry("cross_state_fwd", T, BH, K, d)) return e;
-  RFA_REQUIRE(phi_k && v && s && z, RFA_EINVAL, "cross_state_fwd: null pointer");
+  RFA_REQUIRE(s && z && (T == 0 || (phi_k && v)), RFA_EINVAL, "cross_state_fwd: null pointer");
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(s) && aligned16(z), RFA_EALIGN,
               "cross_state_fwd: 16-byte alignment required");
   if (T == 0) {
@@ -284,7 +284,7 @@ extern "C" int rfa_state_partials(const void* phi_k, const void* v, float* s_par
                                   int64_t T, int BH, int K, int d, int nseg, rfa_stream_t stream) {
   if (int e = check_geometry("state_partials", T, BH, K, d)) return e;
   RFA_REQUIRE(nseg > 0 && nseg <= 65535, RFA_EINVAL, "state_partials: nseg=%d", nseg);
-  RFA_REQUIRE(phi_k && v && s_part && z_part, RFA_EINVAL, "state_partials: null pointer");
+  RFA_REQUIRE(s_part && z_part && (T == 0 || (phi_k && v)), RFA_EINVAL, "state_partials: null pointer");
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(s_part) && aligned16(z_part), RFA_EALIGN,
               "state_partials: 16-byte alignment required");
   if (T == 0) {
@@ -324,7 +324,7 @@ extern "C" int rfa_cross_query_bwd(const void* phi_q, const float* s, const floa
                                    void* g_phi_q, float* d_s, float* d_z,
                                    int64_t T, int BH, int K, int d, rfa_stream_t stream) {
   if (int e = check_geometry("cross_query_bwd", T, BH, K, d)) return e;
-  RFA_REQUIRE(phi_q && s && z && g && g_phi_q && d_s && d_z, RFA_EINVAL, "cross_query_bwd: null pointer");
+  RFA_REQUIRE(s && z && d_s && d_z && (T == 0 || (phi_q && g && g_phi_q)), RFA_EINVAL, "cross_query_bwd: null pointer");
   RFA_REQUIRE(aligned16(phi_q) && aligned16(s) && aligned16(z) && aligned16(g) && aligned16(g_phi_q) && aligned16(d_s) &&
                   aligned16(d_z), RFA_EALIGN, "cross_query_bwd: 16-byte alignment required");
   if (T == 0) {

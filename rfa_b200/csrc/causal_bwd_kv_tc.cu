@@ -19,20 +19,12 @@
 // chain of the scan (state MMA -> export -> next chunk's readers) short.  All waits are bounded.
 #include <type_traits>
 
+#define RFA_TC_FAMILY 3
 #include "tc_common.cuh"
 
 namespace rfa {
 
 constexpr int kKvThreads = 480;
-
-#ifdef RFA_TRACE
-// tuning builds only: switch parts of the kernel off (results are then wrong) to see what the chain is sensitive to
-static __device__ int g_kv_dbg;
-extern "C" int rfa_trace_set_dbg_kv(int v) { return (int)cudaMemcpyToSymbol(g_kv_dbg, &v, sizeof(int)); }
-#define KV_DBG(bit) ((kv_dbg >> (bit)) & 1)
-#else
-#define KV_DBG(bit) 0
-#endif
 
 constexpr uint32_t kvQ = 0, kvK = 2 * kBox, kvV = 4 * kBox, kvG = 5 * kBox, kvStage = 6 * kBox;   // 98304 per stage
 constexpr uint32_t kvS = 2 * kvStage;            // dS as an operand: [128 k][64 n] fp16, swizzled
@@ -90,16 +82,12 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-#ifdef RFA_TRACE
-  const int kv_dbg = g_kv_dbg;
-#endif
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
     // It also issues the stores of the staged gradients, and refills a stage in two halves: g and Q as soon as the
     // chunk two earlier has no further use for them, K and V once its staged gradients have been read out.
     if (lane == 0) {
-      RFA_TRACE_DECL(0)
       auto chunk_t0 = [&](int j) { return (int)(t_begin + (int64_t)(nchunk - 1 - j) * kTC); };
       auto store_chunk = [&](int j) {
         unsigned char* base = sm + (j & 1) * kvStage;
@@ -114,9 +102,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         unsigned char* base = sm + st * kvStage;
         const int t0 = chunk_t0(i);
         uint64_t* fb = &bars[vFull + st];
-        RFA_TRACE_EV(1, i);
         if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); ok = false; break; }
-        RFA_TRACE_EV(2, i);
         mbar_arrive_expect_tx(fb, 3 * kBox);
         tma_load_3d(base + kvG, &tm_g, fb, 0, bh, t0);
         tma_load_3d(base + kvQ, &tm_q, fb, 0, bh, t0);
@@ -126,7 +112,6 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           store_chunk(i - 2);
           tma_store_wait_read<0>();                  // the K and V tiles have been read out
         }
-        RFA_TRACE_EV(3, i);
         mbar_arrive_expect_tx(fb, 3 * kBox);
         tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
         tma_load_3d(base + kvK + kBox, &tm_k, fb, 64, bh, t0);
@@ -142,7 +127,6 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t lead = 1u;
-      RFA_TRACE_DECL(1)
       constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // K Q^T ; V gs^T ; V dS^T
       constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dAt Q            (B MN-major)
       constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // Pt gs ; K dS     (B MN-major)
@@ -174,18 +158,15 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           const uint64_t so = (uint64_t)st * dStage;
           const uint32_t ph = i & 1;
           // dK = V dS_next^T first: it reads the state tile, which the output group wants to overwrite
-          RFA_TRACE_EV(10, i);
           if (!mbar_wait(&bars[vSt], ph)) { tc_fail(3); break; }
           if (i > 0 && !mbar_wait(&bars[vDKFree], (i - 1) & 1)) { tc_fail(4); break; }
           tc_fence_after_sync();
           umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDK, dVk + so, dSk, idKK, 0);
           umma_commit(&bars[vSR]);
-          RFA_TRACE_EV(11, i);
           if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(5); break; }
           tc_fence_after_sync();
           umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDAt, dVk + so, dGk + so, idKK, 0);          // dAt = V gs^T
           umma_commit(&bars[vDAt]);
-          RFA_TRACE_EV(12, i);
           // the next chunk's scores as soon as its tiles are in and Pt of this chunk has been consumed (dV complete)
           bool next_issued = (i + 1 >= nchunk);
           if (!next_issued && mbar_test(&bars[vFull + (st ^ 1)], ((i + 1) >> 1) & 1) && mbar_test(&bars[vDV], ph)) {
@@ -194,18 +175,15 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
             next_issued = true;
           }
           if (!mbar_wait(&bars[vDA16], ph)) { tc_fail(6); break; }
-          RFA_TRACE_EV(13, i);
           tc_fence_after_sync();
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + kvColDK, tmem + kvColDAt, dQm + so, idKM128, 1);                // dK += dAt Q
           umma_commit(&bars[vDK]);
-          RFA_TRACE_EV(14, i);
           if (!next_issued) {
             if (!mbar_wait(&bars[vFull + (st ^ 1)], ((i + 1) >> 1) & 1)) { tc_fail(7); break; }
             if (!mbar_wait(&bars[vDV], ph)) { tc_fail(8); break; }
             tc_fence_after_sync();
             issue_At(st ^ 1);
           }
-          RFA_TRACE_EV(15, i);
         }
       } else {
         // ---- issuer B: dV and the state update
@@ -236,12 +214,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     // ------------------------------------------------------------------ score group 1: Pt[s][t] = At[s][t] for t >= s
     const int quarter = warp & 3;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;   // key row s = quarter * 32 + lane
-    RFA_TRACE_DECL(2)
     for (int i = 0; i < nchunk; ++i) {
       const uint32_t ph = i & 1;
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(22, i);
       if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(23, i);
       tc_fence_after_sync();
       // 32-column pieces right of the diagonal one need no mask, the diagonal one keeps columns >= lane, the rest are zero
       auto pack_piece = [&](int piece, auto DIAG) {
@@ -273,14 +248,12 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vP]);
-      if (warp == 5 && lane == 0) RFA_TRACE_EV(24, i);
     }
   } else if (warp >= 11) {
     // ------------------------------------------------------------------ score group 2: gs = g / den, then dAt
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // query row t (scaling g) / key row s (packing)
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    RFA_TRACE_DECL(5)
     for (int i = 0; i < nchunk; ++i) {
       const int st = i & 1;
       const uint32_t ph = i & 1;
@@ -293,9 +266,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
         gz = ws_gz[(size_t)bh * T + t0 + row];
       }
-      if (warp == 11 && lane == 0) RFA_TRACE_EV(20, i);
       if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
-      if (warp == 11 && lane == 0) RFA_TRACE_EV(21, i);
       {
         unsigned char* grow = stage + kvG;
         // all eight loads of the row first (independent), then the scaling, then the stores
@@ -315,11 +286,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       fence_async_smem();
       mbar_arrive(&bars[vG + st]);
-      if (warp == 11 && lane == 0) RFA_TRACE_EV(27, i);
       // ---- dAt[s][t] = (v_s . gs_t + gz_t) for t >= s; gz of all rows is there once vG completed
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(12); break; }
       if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
-      if (warp == 11 && lane == 0) RFA_TRACE_EV(25, i);
       tc_fence_after_sync();
       auto pack_da = [&](int piece, auto DIAG) {
         constexpr bool diag = decltype(DIAG)::value;
@@ -355,7 +324,6 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vDA16]);
-      if (warp == 11 && lane == 0) RFA_TRACE_EV(26, i);
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------------ output / state group
@@ -381,7 +349,6 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     }
     bool ok = true;
     uint32_t y_phase = 0;
-    RFA_TRACE_DECL(3)
     for (int i = 0; ok && i < nchunk; ++i) {
       const int st = i & 1;
       const uint32_t ph = i & 1;
@@ -391,10 +358,8 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       // every thread has written its dz entering this chunk and finished the previous chunk's reads of the other buffer
       if (!epi_sync(&bars[vY], y_phase)) { tc_fail(14); ok = false; break; }
       // ---- the state update is complete and both issuers have finished reading the old state tile
-      if (ytid == 0) RFA_TRACE_EV(30, i);
       if (!mbar_wait(&bars[vS], ph)) { tc_fail(15); ok = false; break; }
       if (!mbar_wait(&bars[vSR], ph)) { tc_fail(18); ok = false; break; }
-      if (ytid == 0) RFA_TRACE_EV(31, i);
       tc_fence_after_sync();
       // ---- reverse state after this chunk -> fp16 operand tile (the serial chain of the scan)
       if (i + 1 < nchunk) {
@@ -407,12 +372,10 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         tc_fence_before_sync();
         mbar_arrive(&bars[vSt]);
       }
-      if (ytid == 0) RFA_TRACE_EV(32, i);
       // ---- dz += Q^T gz while the chunk's other products are in flight (the state MMA waited on vG, so gz is there);
       //      the new dz goes to the other buffer
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
       dzs[((i + 1) & 1) * 128 + row] = dz_cur[row] + column_sum2(stage + kvQ, quarter, lane, gzs);
-      if (ytid == 0) RFA_TRACE_EV(34, i);
       // ---- grad_v: issuer B's last product of the chunk
       uint32_t r[64];
       if (!mbar_wait(&bars[vDV], ph)) { tc_fail(13); ok = false; break; }
@@ -449,7 +412,6 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       fence_async_smem();
       mbar_arrive(&bars[vStaged + st]);            // the producer thread stores the two tiles and refills them
-      if (ytid == 0) RFA_TRACE_EV(33, i);
     }
   }
   tc_fence_before_sync();
@@ -472,8 +434,6 @@ int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, c
   return check_launch("rfa_causal_bwd_kv");
 }
 
-int tc_status_causal_bwd_kv() { return tc_status_read_clear(); }
-
-RFA_TRACE_DUMP_FN(rfa_trace_dump_kv)
+RFA_TC_UNIT(causal_bwd_kv)
 
 }  // namespace rfa

@@ -19,6 +19,7 @@
 // output group finish chunk c.  All waits are bounded.
 #include <type_traits>
 
+#define RFA_TC_FAMILY 2
 #include "tc_common.cuh"
 
 namespace rfa {
@@ -103,15 +104,12 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      RFA_TRACE_DECL(0)
       for (int c = 0; c < nchunk; ++c) {
         const int st = c & 1;
-        RFA_TRACE_EV(1, c);
         if (c >= 2 && !mbar_wait(&bars[qEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
         unsigned char* base = sm + st * bqStage;
         const int t0 = (int)(t_begin + (int64_t)c * kTC);
         uint64_t* fb = &bars[qFull + st];
-        RFA_TRACE_EV(2, c);
         uint64_t* fv = &bars[qFullV + st];
         mbar_arrive_expect_tx(fb, 4 * kBox);
         tma_load_3d(base + bqQ, &tm_q, fb, 0, bh, t0);
@@ -127,7 +125,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t lead = 1u;
-      RFA_TRACE_DECL(1)
       constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // Q K^T ; gs V^T ; gs S^T
       constexpr uint32_t idKM64 = umma_idesc_f16(128, 64, false, true);   // P V ; Q S        (B MN-major)
       constexpr uint32_t idKM128 = umma_idesc_f16(128, 128, false, true); // dA K             (B MN-major)
@@ -155,17 +152,13 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         auto issue_n = [&](int c) -> bool {
           const int st = c & 1;
           const uint64_t so = (uint64_t)st * kSt;
-          RFA_TRACE_EV(10, c);
           if (!mbar_wait(&bars[qP + st], (c >> 1) & 1)) { tc_fail(2); return false; }
-          RFA_TRACE_EV(11, c);
           if (!mbar_wait(&bars[qSt + (c & 1)], (c >> 1) & 1)) { tc_fail(3); return false; }
           if (!mbar_wait(&bars[qFullV + st], (c >> 1) & 1)) { tc_fail(23); return false; }
           tc_fence_after_sync();
-          RFA_TRACE_EV(12, c);
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, tmem + bqColA + st * 128, dVm + so, idKM64, 0);
           umma_chain_ss<8, kStepK, kBlockK, kStepMN, kBlockMN>(lead, tmem + bqColA + st * 128 + 64, dQk + so, dSm + st * kTile, idKM64, 1);
           umma_commit(&bars[qN + st]);
-          RFA_TRACE_EV(13, c);
           return true;
         };
         // in time order: N of chunk c needs P of chunk c (score group 1, about a microsecond after the scores); the
@@ -192,26 +185,20 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           const uint32_t acc0 = (c == 0 && s_in == nullptr) ? 0u : 1u;
           umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColS, dKm + so, dVm + so, idMM64, acc0);  // S += K^T V
           umma_commit(&bars[qS]);
-          RFA_TRACE_EV(14, c);
           if (!mbar_wait(&bars[qG + st], (c >> 1) & 1)) { tc_fail(4); break; }
-          RFA_TRACE_EV(15, c);
           tc_fence_after_sync();
           umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColA + st * 128, dGk + so, dVk + so, idKK, 0);   // dA = gs V^T
           umma_commit(&bars[qDA + st]);
           if (c > 0 && !mbar_wait(&bars[qDQFree], (c - 1) & 1)) { tc_fail(5); break; }
           tc_fence_after_sync();
           umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bqColDQ, dGk + so, dSk + st * kTile, idKK, 0);  // dQ = gs S_prev^T
-          RFA_TRACE_EV(16, c);
           if (want_dseg)                                                                   // dSseg += Q^T gs
             umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bqColDS, dQm + so, dGm + so, idMM64, c > 0 ? 1u : 0u);
-          RFA_TRACE_EV(19, c);
           if (!mbar_wait(&bars[qDA16 + st], (c >> 1) & 1)) { tc_fail(6); break; }
-          RFA_TRACE_EV(20, c);
           tc_fence_after_sync();
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bqColDQ, tmem + bqColA + st * 128, dKm + so, idKM128, 1);       // dQ += dA K
           umma_commit(&bars[qDQ + st]);
           umma_commit(&bars[qEmpty + st]);       // every MMA that reads this stage is complete when this arrives
-          RFA_TRACE_EV(21, c);
         }
       }
     }
@@ -220,17 +207,13 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // token row of the chunk
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    RFA_TRACE_DECL(2)
-    const bool tr = (warp == 5 && lane == 0);
     for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t colA = bqColA + st * 128;
       unsigned char* stage = sm + st * bqStage;
       const float* zs = z_buf + (c % 3) * 128;
-      if (tr) RFA_TRACE_EV(32, c);
       if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); break; }     // this group reads the Q tile itself
       if (!mbar_wait(&bars[qA + st], (c >> 1) & 1)) { tc_fail(12); break; }
-      if (tr) RFA_TRACE_EV(33, c);
       tc_fence_after_sync();
       float rowsum = 0.f, rowsum_b = 0.f;
       // 32-column pieces left of the diagonal one need no mask, the diagonal one keeps columns <= lane, the rest are zero
@@ -264,7 +247,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[qP + st]);
-      if (tr) RFA_TRACE_EV(34, c);
       // q . z_prev in fp32 from this thread's own Q row while the tensor pipe computes N from the P just handed over
       // (the scores completed, so the stage's tiles are in; z of this version comes from the output group)
       if (!mbar_wait(&bars[qZ + (c & 1)], (c >> 1) & 1)) { tc_fail(11); break; }
@@ -282,25 +264,20 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float qz = (qz0 + qz1) + (qz2 + qz3);
       rg_buf[(c & 1) * 128 + row] = (rowsum + rowsum_b) + qz;
       mbar_arrive(&bars[qRS + st]);
-      if (tr) RFA_TRACE_EV(35, c);
     }
   } else if (warp >= 11) {
     // ------------------------------------------------------------------ score group 2: den, gz, gs, then dA
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // token row of the chunk
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    RFA_TRACE_DECL(0)
-    const bool tr = (warp == 11 && lane == 0);
     for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t colA = bqColA + st * 128;
       unsigned char* stage = sm + st * bqStage;
       const int64_t t0 = t_begin + (int64_t)c * kTC;
-      if (tr) RFA_TRACE_EV(36, c);
       if (!mbar_wait(&bars[qFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }    // this group rewrites the g tile itself
       if (!mbar_wait(&bars[qN + st], (c >> 1) & 1)) { tc_fail(13); break; }
       if (!mbar_wait(&bars[qRS + st], (c >> 1) & 1)) { tc_fail(10); break; }
-      if (tr) RFA_TRACE_EV(37, c);
       tc_fence_after_sync();
       float gz;
       {
@@ -308,7 +285,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_ld32(tmem + lane_addr + colA + 64, nn);
         tmem_ld32(tmem + lane_addr + colA + 96, nn + 32);
         tmem_ld_wait();
-        if (tr) RFA_TRACE_EV(41, c);
         const float raw = rg_buf[(c & 1) * 128 + row];
         const float dn = fmaxf(raw, kEps), inv = 1.f / dn;
         float go = 0.f, go1 = 0.f, go2 = 0.f, go3 = 0.f;
@@ -332,7 +308,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) *reinterpret_cast<uint4*>(grow + row_chunk1(row, ch)) = gu[ch];
-        if (tr) RFA_TRACE_EV(42, c);
         go = ((go + go1) + (go2 + go3)) * inv;       // g . out
         gz = raw > kEps ? -go * inv : 0.f;           // strict >, upstream rfa.py:91
         if (t0 + row < t_end) {
@@ -341,14 +316,11 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         rg_buf[(c & 1) * 128 + row] = gz;            // over the value just consumed
       }
-      if (tr) RFA_TRACE_EV(43, c);
       fence_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bars[qG + st]);
-      if (tr) RFA_TRACE_EV(38, c);
       // ---- dA = mask(gs V^T + gz) -> fp16 over the P columns
       if (!mbar_wait(&bars[qDA + st], (c >> 1) & 1)) { tc_fail(14); break; }
-      if (tr) RFA_TRACE_EV(39, c);
       tc_fence_after_sync();
       auto pack_da = [&](int piece, auto DIAG) {
         constexpr bool diag = decltype(DIAG)::value;
@@ -379,7 +351,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[qDA16 + st]);
-      if (tr) RFA_TRACE_EV(40, c);
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------------ output / state group
@@ -388,7 +359,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int ytid = tid - 192;
     unsigned char* s_tile = sm + bqS;
-    (void)ytid;
     {
       uint32_t r[64];
 #pragma unroll
@@ -407,8 +377,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     bool ok = true;
     float dz_acc = 0.f;
-    RFA_TRACE_DECL(3)
-    const bool tr = (ytid == 0);
     for (int c = 0; ok && c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t ph = c & 1;
@@ -417,17 +385,13 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float* zs = z_buf + (c % 3) * 128;
       const float* gzs = rg_buf + (c & 1) * 128;
       // ---- z before the next chunk = z + colsum(K): needs only the staged K tile
-      if (tr) RFA_TRACE_EV(50, c);
       if (!mbar_wait(&bars[qFull + st], (c >> 1) & 1)) { tc_fail(15); ok = false; break; }
-      if (tr) RFA_TRACE_EV(51, c);
       z_buf[((c + 1) % 3) * 128 + row] = zs[row] + column_sum2(stage + bqK, quarter, lane, nullptr);
       mbar_arrive(&bars[qZ + ((c + 1) & 1)]);
       // ---- the state after this chunk -> the other fp16 operand tile.  Its previous readers (the products of chunk
       //      c - 1 that read the state before chunk c - 1) were issued before this chunk's state update by the same
       //      issuer, or consumed before them, so qS alone orders the overwrite.
-      if (tr) RFA_TRACE_EV(52, c);
       if (!mbar_wait(&bars[qS], ph)) { tc_fail(16); ok = false; break; }
-      if (tr) RFA_TRACE_EV(53, c);
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
         uint32_t r[64];
@@ -445,9 +409,7 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float gz = gzs[row];
       mbar_arrive(&bars[qEmpty + st]);             // this group's last read of the stage's tiles
       // ---- grad_q = dQ + gz z_prev^T -> fp16, written straight from registers (one 256-byte row per thread)
-      if (tr) RFA_TRACE_EV(54, c);
       if (!mbar_wait(&bars[qDQ + st], (c >> 1) & 1)) { tc_fail(18); ok = false; break; }
-      if (tr) RFA_TRACE_EV(55, c);
       tc_fence_after_sync();
       const bool live = t0 + row < t_end;
       __half* grow = reinterpret_cast<__half*>(gq_ptr) + ((size_t)(t0 + row) * BH + bh) * kK;
@@ -473,7 +435,6 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       }
       tc_fence_before_sync();
       mbar_arrive(&bars[qDQFree]);                 // after the last read of dQ and of this chunk's z, gz
-      if (tr) RFA_TRACE_EV(57, c);
     }
     if (ok && want_dseg) {
       uint32_t r[64];
@@ -513,8 +474,6 @@ int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, co
   return check_launch("rfa_causal_bwd_q");
 }
 
-int tc_status_causal_bwd() { return tc_status_read_clear(); }
-
-RFA_TRACE_DUMP_FN(rfa_trace_dump_q)
+RFA_TC_UNIT(causal_bwd)
 
 }  // namespace rfa

@@ -21,6 +21,7 @@
 // All waits are bounded.
 #include <type_traits>
 
+#define RFA_TC_FAMILY 1
 #include "tc_common.cuh"
 
 namespace rfa {
@@ -104,14 +105,12 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      RFA_TRACE_DECL(0)
       for (int c = 0; c < nchunk; ++c) {
         const int st = c & 1;
         if (c >= 2 && !mbar_wait(&bars[fEmpty + st], ((c >> 1) + 1) & 1)) { tc_fail(1); break; }
         unsigned char* base = sm + st * kFwStage;
         const int t0 = (int)(t_begin + (int64_t)c * kTC);
         uint64_t* fb = &bars[fFull + st];
-        RFA_TRACE_EV(1, c);
         mbar_arrive_expect_tx(fb, 4 * kBox);
         tma_load_3d(base + kFwQ, &tm_q, fb, 0, bh, t0);
         tma_load_3d(base + kFwQ + kBox, &tm_q, fb, 64, bh, t0);
@@ -126,7 +125,6 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t lead = 1u;
-      RFA_TRACE_DECL(1)
       constexpr uint32_t idA = umma_idesc_f16(128, 128, false, false);   // Q K^T
       constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);    // Q [S|z]   (B MN-major)
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V       (B MN-major)
@@ -162,10 +160,8 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             issue_A(c + 1);
             next_issued = true;
           }
-          RFA_TRACE_EV(13, c);
           if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(6); break; }
           if (!mbar_wait(&bars[fS + st], (c >> 1) & 1)) { tc_fail(16); break; }     // Q [S|z] has written the N buffer
-          RFA_TRACE_EV(14, c);
           tc_fence_after_sync();
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + fColN + st * 80, tmem + fColA + st * 128, dV + st * kSt, idPV, 1);   // N += P V
           umma_commit(&bars[fN + st]);
@@ -184,11 +180,9 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const uint64_t so = (uint64_t)st * kSt;
           const uint64_t w = st ? dW1 : dW0;
           // the state before this chunk is in the operand tile, and the output group has let go of S and of the N buffer
-          RFA_TRACE_EV(10, c);
           if (!mbar_wait(&bars[fSt], c & 1)) { tc_fail(3); break; }
           if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(4); break; }
           if (!mbar_wait(&bars[fFull + st], (c >> 1) & 1)) { tc_fail(17); break; }
-          RFA_TRACE_EV(11, c);
           if (!mbar_wait(&bars[fFullV + st], (c >> 1) & 1)) { tc_fail(15); break; }
           tc_fence_after_sync();
           const uint32_t fresh_acc = (c == 0 && s_in == nullptr) ? 0u : 1u;
@@ -197,7 +191,6 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           umma_commit(&bars[fS + st]);
           umma_commit(&bars[fEmpty + st]);       // this issuer's last read of the stage's Q and K ...
           umma_commit(&bars[fEmptyV + st]);      // ... and of its V
-          RFA_TRACE_EV(12, c);
         }
       }
     }
@@ -206,13 +199,10 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    RFA_TRACE_DECL(2)
     for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t colA = fColA + st * 128;
-      if (lane == 0 && warp == 5) RFA_TRACE_EV(20, c);
       if (!mbar_wait(&bars[fA + st], (c >> 1) & 1)) { tc_fail(7); break; }
-      if (lane == 0 && warp == 5) RFA_TRACE_EV(21, c);
       // rs[st] of chunk c-2 must have been read by the output group
       if (c >= 2 && !mbar_wait(&bars[fNFree + st], ((c >> 1) + 1) & 1)) { tc_fail(8); break; }
       tc_fence_after_sync();
@@ -249,7 +239,6 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[fP + st]);
-      if (lane == 0 && warp == 5) RFA_TRACE_EV(22, c);
     }
   } else if (warp < 10) {
     // ------------------------------------------------------------------ output / state group
@@ -281,13 +270,10 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     bool ok = true;
     uint32_t y_phase = 0;
-    RFA_TRACE_DECL(3)
     for (int c = 0; ok && c < nchunk; ++c) {
       const int st = c & 1;
       // ---- the state after this chunk -> operand tile for the next chunk (the serial chain of the scan)
-      if (ytid == 0) RFA_TRACE_EV(30, c);
       if (!mbar_wait(&bars[fS + st], (c >> 1) & 1)) { tc_fail(9); ok = false; break; }
-      if (ytid == 0) RFA_TRACE_EV(31, c);
       tc_fence_after_sync();
       if (c + 1 < nchunk) {
         uint32_t r[80];
@@ -302,11 +288,9 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive(&bars[fSt]);
       }
       // ---- N: numerator (64 columns) and q.z_prev (column 64); row sum from the score group
-      if (ytid == 0) RFA_TRACE_EV(32, c);
       if (!mbar_wait(&bars[fP + st], (c >> 1) & 1)) { tc_fail(10); ok = false; break; }
       if (!mbar_wait(&bars[fN + st], (c >> 1) & 1)) { tc_fail(11); ok = false; break; }
       tc_fence_after_sync();
-      if (ytid == 0) RFA_TRACE_EV(33, c);
       uint32_t nn[64], nz[16];
       tmem_ld32(tmem + lane_addr + fColN + st * 80, nn);
       tmem_ld32(tmem + lane_addr + fColN + st * 80 + 32, nn + 32);
@@ -336,7 +320,6 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (ytid == 0) {
         tma_store_3d(&tm_o, sm + kFwOut, 0, bh, (int)(t_begin + (int64_t)c * kTC));
         tma_store_commit();
-        RFA_TRACE_EV(34, c);
       }
     }
     // ---- final state out (prefill -> decode hand-off, segment carry); the last wait on fS ordered it
@@ -380,8 +363,6 @@ int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __ha
   return check_launch("rfa_causal_fwd");
 }
 
-int tc_status_causal_fwd() { return tc_status_read_clear(); }
-
-RFA_TRACE_DUMP_FN(rfa_trace_dump)
+RFA_TC_UNIT(causal_fwd)
 
 }  // namespace rfa

@@ -21,6 +21,10 @@ inline cudaStream_t as_stream(rfa_stream_t s) { return reinterpret_cast<cudaStre
     if (!(cond)) return ::rfa::fail((code), __VA_ARGS__); \
   } while (0)
 
+// Geometry of the attention kernels: feature width K = 2 * proj_dim = 128, head dim d = 64.
+constexpr int kK = 128;        // width of phi
+constexpr int kD = 64;         // head dim
+
 constexpr float kEps = 1.0f;       // denominator clamp (upstream rfa.py:17, cuda/utils.cu:20)
 constexpr float kNormEps = 1e-3f;  // x / (|x| + 1e-3)   (upstream utils.py:102)
 

@@ -11,6 +11,7 @@
 //     state bwd   dK  = V dS^T,  dV = K dS
 // Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 epilogue
 // (thread <-> TMEM lane <-> row).  All waits are bounded.
+#define RFA_TC_FAMILY 4
 #include "tc_common.cuh"
 
 namespace rfa {
@@ -610,6 +611,6 @@ int launch_cross_state_bwd_tc(const __half* k, const __half* v, const uint8_t* p
   return check_launch("rfa_cross_state_bwd");
 }
 
-int tc_status_cross() { return tc_status_read_clear(); }
+RFA_TC_UNIT(cross)
 
 }  // namespace rfa

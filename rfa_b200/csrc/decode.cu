@@ -201,12 +201,21 @@ decode_step_fused_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
   decode_body<TIn, TState>(pq, pk, vs, S + bh * (size_t)K * d, z + bh * K, out + bh * d, red, den_s, K, d, buf);
 }
 
+static int check_decode_dtypes(const char* what, int in_dtype, int state_dtype) {
+  const bool ok = (in_dtype == RFA_F16 && (state_dtype == RFA_F32 || state_dtype == RFA_F16)) ||
+                  (in_dtype == RFA_F32 && state_dtype == RFA_F32);
+  RFA_REQUIRE(ok, RFA_EUNSUPPORTED, "%s: unsupported dtype pair in=%d state=%d", what, in_dtype, state_dtype);
+  return 0;
+}
+
 static int check_decode_geometry(int BH, int K, int d) {
   RFA_REQUIRE(BH > 0 && K > 0 && d > 0, RFA_EINVAL, "decode: BH=%d K=%d d=%d must be positive", BH, K, d);
   const int d4 = d / 4;
   RFA_REQUIRE(d % 4 == 0 && d4 <= kDecodeThreads && kDecodeThreads % d4 == 0, RFA_EUNSUPPORTED,
               "decode: head_dim %d must be 4*2^m and <= %d", d, 4 * kDecodeThreads);
   RFA_REQUIRE(K <= 4096, RFA_EUNSUPPORTED, "decode: K=%d too large (max 4096)", K);
+  // the kernel keeps v behind the two K-long feature vectors in shared memory and reads it 16 bytes at a time
+  RFA_REQUIRE(K % 4 == 0, RFA_EUNSUPPORTED, "decode: K=%d must be a multiple of 4", K);
   return 0;
 }
 
@@ -219,6 +228,7 @@ extern "C" int rfa_decode_step(const void* phi_q, const void* phi_k, const void*
                                int BH, int K, int d, rfa_stream_t stream) {
   RFA_REQUIRE(phi_q && phi_k && v && s && z && out, RFA_EINVAL, "decode: null pointer");
   if (int e = check_decode_geometry(BH, K, d)) return e;
+  if (int e = check_decode_dtypes("decode", in_dtype, state_dtype)) return e;
   RFA_REQUIRE(aligned16(phi_q) && aligned16(phi_k) && aligned16(v) && aligned16(s) && aligned16(z) && aligned16(out),
               RFA_EALIGN, "decode: pointers must be 16-byte aligned");
   const size_t smem = kDecodeThreads * sizeof(float4) + (2 * K + d + 4) * sizeof(float);
@@ -241,6 +251,7 @@ extern "C" int rfa_decode_step_fused(const void* q, const void* k, const void* v
   RFA_REQUIRE(H > 0 && D > 0, RFA_EINVAL, "decode_fused: H=%d D=%d must be positive", H, D);
   RFA_REQUIRE(D % 8 == 0, RFA_EUNSUPPORTED, "decode_fused: proj_dim %d must be a multiple of 8", D);
   if (int e = check_decode_geometry(BH, 2 * D, d)) return e;
+  if (int e = check_decode_dtypes("decode_fused", in_dtype, state_dtype)) return e;
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(s) && aligned16(z) && aligned16(out) && aligned16(w),
               RFA_EALIGN, "decode_fused: pointers must be 16-byte aligned");
   const int K = 2 * D;

@@ -5,6 +5,7 @@
 // staged x tile is never rewritten.  One CTA owns one head (W_h resident as an fp16 operand tile)
 // and walks row tiles with a two-stage TMA ring; phi leaves through a staging tile and a TMA store.
 // HBM-bound: 128 bytes in, 256 bytes out per (row, head).
+#define RFA_TC_FAMILY 5
 #include "tc_common.cuh"
 
 namespace rfa {
@@ -423,6 +424,6 @@ int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_p
   return check_launch("rfa_feature_map_bwd");
 }
 
-int tc_status_feature_map() { return tc_status_read_clear(); }
+RFA_TC_UNIT(feature_map)
 
 }  // namespace rfa

@@ -9,7 +9,7 @@
 // is part of the library image on every GPU that loads it.
 #include <mutex>
 
-#include "tiles.cuh"
+#include "common.cuh"
 
 namespace rfa {
 
@@ -65,9 +65,9 @@ extern "C" int rfa_causal_bwd_noalloc(const void* q, const void* k, const void* 
   RFA_REQUIRE(q && k && v && g && gq && gk && gv, RFA_EINVAL, "causal_bwd_noalloc: null pointer");
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) && aligned16(gq) && aligned16(gk) && aligned16(gv),
               RFA_EALIGN, "causal_bwd_noalloc: 16-byte alignment required");
-  RFA_REQUIRE(T * (int64_t)BH <= kNoAllocMaxTokenHeads, RFA_EWORKSPACE,
-              "causal_bwd_noalloc: T*BH = %lld exceeds the built-in scratch (max %lld token-heads); "
-              "use rfa_causal_bwd with a caller workspace", (long long)(T * (int64_t)BH), (long long)kNoAllocMaxTokenHeads);
+  RFA_REQUIRE(T <= kNoAllocMaxTokenHeads / BH, RFA_EWORKSPACE,      // a division: T * BH could overflow for absurd T
+              "causal_bwd_noalloc: T=%lld x BH=%d exceeds the built-in scratch (max %lld token-heads); "
+              "use rfa_causal_bwd with a caller workspace", (long long)T, BH, (long long)kNoAllocMaxTokenHeads);
   if (T == 0) return 0;
   float* scratch = nullptr;
   if (int e = noalloc_scratch(&scratch)) return e;

@@ -292,11 +292,12 @@ inline int make_tmap_rows(CUtensorMap* m, const void* base, uint64_t T, uint64_t
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return -1;
   // The encoder is a driver call and needs a context current on the calling thread.  A thread that has
-  // only ever been handed pooled memory (an autograd worker, say) may not have one bound yet: any
-  // runtime call that touches the device binds the primary context.
+  // only ever been handed pooled memory (an autograd worker, say) may not have one bound yet: setting the
+  // thread's current device again binds the primary context (and allocates nothing).
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
-    cudaFree(nullptr);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -2;
     ctx_bound = true;
   }
   cuuint64_t dims[3] = {width, BH, T};

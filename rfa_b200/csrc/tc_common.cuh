@@ -2,8 +2,8 @@
 // device status word of this translation unit, small epilogue helpers.
 #pragma once
 
+#include "common.cuh"
 #include "sm100.cuh"
-#include "tiles.cuh"
 
 namespace rfa {
 
@@ -12,10 +12,27 @@ using namespace sm100;
 constexpr int kTC = 128;                       // tokens per chunk
 constexpr uint32_t kBox = 128 * 128;           // bytes of one [128 rows][64 halves] swizzled box
 
-// Sticky per-translation-unit status: code of the first bounded wait that ran out (0 = none).
+// Sticky per-translation-unit status: code of the first bounded wait that ran out (0 = none).  A wait gives up after
+// kSpinLimit (2^20) mbarrier.try_wait attempts, each of which suspends the thread for up to a few microseconds:
+// about four seconds of wall-clock time, far beyond any legitimate wait inside these kernels (a chunk takes
+// microseconds).  The kernel then leaves early and its outputs are invalid; besides the device word, the code
+// (100 * RFA_TC_FAMILY + site) is written to a word of mapped host memory when the host has enabled one
+// (rfa_status_mirror_enable), which the host can look at after any later call without synchronising.
+#ifndef RFA_TC_FAMILY
+#error "define RFA_TC_FAMILY (1..9) before including tc_common.cuh"
+#endif
 static __device__ int g_tc_status;
+static __device__ int* g_tc_mirror;
 
-__device__ __forceinline__ void tc_fail(int code) { atomicCAS(&g_tc_status, 0, code); }
+__device__ __forceinline__ void tc_fail(int code) {
+  if (atomicCAS(&g_tc_status, 0, code) == 0) {
+    int* m = g_tc_mirror;
+    if (m) {
+      *reinterpret_cast<volatile int*>(m) = 100 * RFA_TC_FAMILY + code;
+      __threadfence_system();
+    }
+  }
+}
 
 // Host: read and clear this translation unit's status word (device must be idle).
 static int tc_status_read_clear() {
@@ -24,48 +41,16 @@ static int tc_status_read_clear() {
   cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
   return v;
 }
+// Host: point this translation unit's kernels (on the current device) at the mapped host word.
+static int tc_mirror_set(int* host_word) {
+  return (int)cudaMemcpyToSymbol(g_tc_mirror, &host_word, sizeof(host_word));
+}
+// defines the two host hooks of a kernel family that api.cu calls
+#define RFA_TC_UNIT(name)                                        \
+  int tc_status_##name() { return tc_status_read_clear(); }      \
+  int tc_mirror_##name(int* w) { return tc_mirror_set(w); }
 
 #ifdef __CUDACC__
-// Optional event trace of CTA (0,0) for tuning (compile with -DRFA_TRACE): each record is
-// (event id, chunk, globaltimer ns).  Not part of normal builds.
-#ifdef RFA_TRACE
-// four roles x 1024 records, store-only (no atomics, nothing waits on the stores)
-static __device__ unsigned long long g_trace[4 * 1024 * 2];
-__device__ __forceinline__ void trace_ev(int role, int& n, int id, int chunk) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && n < 1024) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    g_trace[(role * 1024 + n) * 2] = ((unsigned long long)id << 32) | (unsigned int)chunk;
-    g_trace[(role * 1024 + n) * 2 + 1] = t;
-    ++n;
-  }
-}
-__device__ __forceinline__ void trace_clock(int role, int& n, int id) {      // SM cycle counter instead of the ns timer
-  if (blockIdx.x == 0 && blockIdx.y == 0 && n < 1024) {
-    g_trace[(role * 1024 + n) * 2] = ((unsigned long long)id << 32);
-    g_trace[(role * 1024 + n) * 2 + 1] = (unsigned long long)clock64();
-    ++n;
-  }
-}
-#define RFA_TRACE_CLOCK(id) trace_clock(trace_role_, trace_n_, (id))
-#define RFA_TRACE_DECL(role) const int trace_role_ = (role); int trace_n_ = 0;
-#define RFA_TRACE_EV(id, chunk) trace_ev(trace_role_, trace_n_, (id), (chunk))
-// defines  extern "C" int NAME(unsigned long long* out)  copying this translation unit's records (4*1024 pairs)
-#define RFA_TRACE_DUMP_FN(NAME)                                      \
-  extern "C" int NAME(unsigned long long* out) {                     \
-    static unsigned long long zeros[4 * 1024 * 2];                   \
-    cudaDeviceSynchronize();                                         \
-    cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));             \
-    cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));               \
-    return 4 * 1024;                                                 \
-  }
-#else
-#define RFA_TRACE_CLOCK(id)
-#define RFA_TRACE_DUMP_FN(NAME)
-#define RFA_TRACE_DECL(role)
-#define RFA_TRACE_EV(id, chunk) ((void)0)
-#endif
-
 // The k-steps of one product, issued by the whole MMA warp (see umma_ss_w).  Operand k-step j sits at
 // base + (j & 3) * step + (j >> 2) * block  (descriptor units of 16 bytes): K-major two-box tiles use
 // (kStepK, kBlockK), MN-major tiles (kStepMN, kBlockMN); a packed fp16 operand in tensor memory advances

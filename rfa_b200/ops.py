@@ -18,7 +18,23 @@ K_BUILT, D_BUILT = 128, 64      # geometry the attention kernels are built for
 def _guard(t: Tensor):
     if not t.is_cuda:
         raise RuntimeError(f"rfa_b200 kernels take CUDA tensors only (there is no CPU path); got a {t.device} tensor")
-    return torch.cuda.device(t.device)
+    return _Guard(t.device)
+
+
+class _Guard:
+    """Make the tensor's device current for the call and, on first use of a device, switch on the status mirror."""
+
+    def __init__(self, device):
+        self.ctx = torch.cuda.device(device)
+        self.index = device.index if device.index is not None else torch.cuda.current_device()
+
+    def __enter__(self):
+        self.ctx.__enter__()
+        _lib.watch_device(self.index)
+        return self
+
+    def __exit__(self, *a):
+        return self.ctx.__exit__(*a)
 
 
 def _workspace(T: int, BH: int, K: int, d: int, like: Tensor) -> Tuple[Tensor, int]:
@@ -108,6 +124,9 @@ def causal_bwd_q(q, k, v, g, s_in, z_in, want_dseg: bool):
     d = v.shape[-1]
     q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
     gq = torch.empty_like(q)
+    if T == 0:      # an empty shard: nothing to launch (empty tensors have no address); its reverse-state total is zero
+        zeros = (torch.zeros(BH, K, d, device=q.device), torch.zeros(BH, K, device=q.device)) if want_dseg else (None, None)
+        return gq, zeros[0], zeros[1], torch.empty(256, dtype=torch.uint8, device=q.device)
     ds = torch.empty(BH, K, d, dtype=torch.float32, device=q.device) if want_dseg else None
     dz = torch.empty(BH, K, dtype=torch.float32, device=q.device) if want_dseg else None
     ws, n = _workspace(T, BH, K, d, q)
@@ -122,6 +141,8 @@ def causal_bwd_kv(q, k, v, g, ds_in, dz_in, ws: Tensor):
     d = v.shape[-1]
     q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
     gk, gv = torch.empty_like(k), torch.empty_like(v)
+    if T == 0:
+        return gk, gv
     with _guard(q):
         check(_lib.load().rfa_causal_bwd_kv(ptr(q), ptr(k), ptr(v), ptr(g), ptr(gk), ptr(gv), ptr(ds_in), ptr(dz_in),
                                             ptr(ws), ws.numel(), T, BH, K, d, stream_of(q)), "rfa_causal_bwd_kv")
@@ -158,6 +179,8 @@ def state_total(phi_k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor]:
     T, BH, K = phi_k.shape
     d = v.shape[-1]
     phi_k, v = phi_k.contiguous(), v.contiguous()
+    if T == 0:      # an empty shard contributes nothing
+        return torch.zeros(BH, K, d, device=phi_k.device), torch.zeros(BH, K, device=phi_k.device)
     sms = torch.cuda.get_device_properties(phi_k.device).multi_processor_count
     nseg = max(1, min(sms // max(BH, 1), T // 512))
     s = torch.empty(BH, nseg, K, d, dtype=torch.float32, device=phi_k.device)
@@ -217,8 +240,13 @@ def decode_step(phi_q: Tensor, phi_k: Tensor, v: Tensor, s: Tensor, z: Tensor, o
     phi_q, phi_k, v = phi_q.contiguous(), phi_k.contiguous(), v.contiguous()
     if not (s.is_contiguous() and z.is_contiguous()):
         raise ValueError("decode_step: state tensors must be contiguous (they are updated in place)")
+    if not (phi_q.dtype == phi_k.dtype == v.dtype) or s.dtype != z.dtype:
+        raise TypeError(f"decode_step: phi_q, phi_k, v must share a dtype and so must s, z (got {phi_q.dtype}, {phi_k.dtype}, "
+                        f"{v.dtype}; {s.dtype}, {z.dtype})")
     if out is None:
         out = torch.empty(B, H, d, dtype=v.dtype, device=v.device)
+    elif out.dtype != v.dtype or not out.is_contiguous():
+        raise TypeError("decode_step: out must be contiguous and of v's dtype")
     with _guard(v):
         check(_lib.load().rfa_decode_step(ptr(phi_q), ptr(phi_k), ptr(v), dtype_code(v), ptr(s), ptr(z), dtype_code(s),
                                           ptr(out), B * H, K, d, stream_of(v)), "rfa_decode_step")
@@ -233,8 +261,15 @@ def decode_step_fused(q: Tensor, k: Tensor, v: Tensor, w: Tensor, scale: float, 
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     if w.dtype != torch.float32 or not w.is_contiguous():
         raise ValueError("decode_step_fused: w must be a contiguous fp32 [H,D,d] tensor")
+    if not (q.dtype == k.dtype == v.dtype) or s.dtype != z.dtype:
+        raise TypeError(f"decode_step_fused: q, k, v must share a dtype and so must s, z (got {q.dtype}, {k.dtype}, {v.dtype}; "
+                        f"{s.dtype}, {z.dtype})")
+    if not (s.is_contiguous() and z.is_contiguous()):
+        raise ValueError("decode_step_fused: state tensors must be contiguous (they are updated in place)")
     if out is None:
         out = torch.empty(B, H, d, dtype=v.dtype, device=v.device)
+    elif out.dtype != v.dtype or not out.is_contiguous():
+        raise TypeError("decode_step_fused: out must be contiguous and of v's dtype")
     with _guard(v):
         check(_lib.load().rfa_decode_step_fused(ptr(q), ptr(k), ptr(v), dtype_code(v), ptr(w), float(scale), ptr(s),
                                                 ptr(z), dtype_code(s), ptr(out), B * H, H, D, d, stream_of(v)),

@@ -81,7 +81,8 @@ def _run(rank, world, T, sharded):
         return errs
 
 
-@pytest.mark.parametrize("world,T", [(2, 64), (3, 50)])
+# (4, 20): runs of 8 tokens leave the last rank an EMPTY shard, which must still join both exchanges
+@pytest.mark.parametrize("world,T", [(2, 64), (3, 50), (4, 20)])
 def test_sequence_sharded_equals_unsharded(world, T):
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
