@@ -36,6 +36,7 @@ BYTES_FWD = 2 * K_FEAT * 2 + 2 * D_HEAD * 2                       # 768
 BYTES_BWD_Q = 2 * K_FEAT * 2 + 2 * D_HEAD * 2 + K_FEAT * 2          # 1024  (q,k,v,g in; gq out)
 BYTES_BWD_KV = 2 * K_FEAT * 2 + 2 * D_HEAD * 2 + K_FEAT * 2 + D_HEAD * 2   # 1152  (q,k,v,g in; gk,gv out)
 BYTES_PATH = 2176                                                 # fwd 768 + bwd (768 in + 640 out)
+LAUNCHES_PER_STEP = 3                                             # causal_fwd, causal_bwd_q, causal_bwd_kv
 WORKLOAD = f"causal RFA fwd+bwd, B{B} H{H} T{T} d{D_HEAD} D{D_PROJ} fp16, RFA.apply boundary"
 
 
@@ -125,12 +126,23 @@ def timed(fn, iters, stream):
     return e0.elapsed_time(e1) / iters
 
 
-def cpu_port_sample(threads=None):
-    """Upstream's PyTorch path restated on the CPU (oracle), fwd+bwd, on a BH slice of the workload.
+def host_threads():
+    """All the host cores this process may use.  A launcher that starts one process per GPU exports
+    OMP_NUM_THREADS=1, which would make the CPU arm a one-core number: set the count explicitly."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
+def cpu_port_sample():
+    """Upstream's PyTorch path restated on the CPU (oracle), fwd+bwd, on a BH slice of the workload: the first 32 of the
+    128 (batch, head) sequences of make_inputs-style features at full T.
     Returns (tokens_per_s for the FULL workload by linear scaling in BH, cores, description, seconds)."""
     from oracle import rfa_oracle as O
-    if threads:
-        torch.set_num_threads(threads)
+    cores = host_threads()
     bh = 32
     g = torch.Generator().manual_seed(0)
     q = torch.randn(T, bh, K_FEAT, generator=g) * 0.1
@@ -143,10 +155,45 @@ def cpu_port_sample(threads=None):
     O.causal_backward(q, k, v, up)
     dt = time.perf_counter() - t0
     full = dt * (BH / bh)
-    return TOKENS_PER_STEP / full, torch.get_num_threads(), f"BH={bh} of {BH} heads at full T={T}, fp32, scaled linearly in BH", dt
+    return TOKENS_PER_STEP / full, cores, f"BH={bh} of {BH} heads at full T={T}, fp32, scaled linearly in BH", dt
+
+
+def cpu_config1():
+    """BASELINE config 1 exactly as specified, on the host cores: batch 2, heads 4, seq 512, head dim 64, D = 64, fp32;
+    q,k,v ~ N(0,1) from seed 0, W = 4 orthogonal 64x64 matrices (numpy seed 1), features by random_project (which
+    L2-normalises), loss = sum(out * seeded N(0,1)); feature map + forward + backward (upstream utils.py:100-120,
+    rfa.py:47-103 restated by the oracle).  Median of 5 runs after one warm-up."""
+    from oracle import rfa_oracle as O
+    cores = host_threads()
+    b, h, t = 2, 4, 512
+    torch.manual_seed(0)
+    xq, xk, v = (torch.randn(t, b, h, D_HEAD) for _ in range(3))
+    w = torch.from_numpy(O.draw_matrices("orf", h, D_HEAD, D_PROJ, 1)).float()
+    up = torch.randn(t, b * h, D_HEAD)
+    times = []
+    for i in range(6):
+        t0 = time.perf_counter()
+        q = O.random_project(xq, w).view(t, b * h, K_FEAT)
+        k = O.random_project(xk, w).view(t, b * h, K_FEAT)
+        O.causal_forward(q, k, v.view(t, b * h, D_HEAD))
+        O.causal_backward(q, k, v.view(t, b * h, D_HEAD), up)
+        if i:
+            times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    return {"workload": "config 1: B2 H4 T512 d64 D64 fp32, seeds 0/1, feature map + causal fwd + bwd", "seconds": sec,
+            "tokens_per_s": b * t / sec, "cores": cores, "kind": "port"}
+
+
+def workload_config(world):
+    """The `config` object of the JSON line: the same keys and values for both arms."""
+    return {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": B * world, "heads": H, "seq_len": T,
+            "l2": "inputs+outputs 570 MB per step, larger than the 126 MB L2; no flush",
+            "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"}
 
 
 def run_reference(args, rank):
+    """The CPU arm: upstream's PyTorch path (restated by the oracle; the upstream package is Python and its checkout
+    does not travel to the GPU box) on all host cores, each step a bounded sample of the workload."""
     if rank != 0:
         return
     samples = []
@@ -155,15 +202,43 @@ def run_reference(args, rank):
         if i >= args.warmup:
             samples.append((tps, dt))
     tps = statistics.median(s[0] for s in samples)
-    ms = TOKENS_PER_STEP / tps * 1e3
+    ms = statistics.median(s[1] for s in samples) * 1e3         # what one step of THIS arm took: the bounded sample
     line = {"impl": "reference", "metric": "causal_rfa_fwd_bwd_tokens_per_s", "value": tps, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "note": "CPU restatement of upstream rfa.py:47-103 (PyTorch), host cores"},
-            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+            "config": workload_config(args.gpus),
+            "note": "CPU restatement of upstream rfa.py:47-103 (PyTorch) on the host cores; one step = the bounded sample "
+                    "(a quarter of the workload's heads), value = tokens/s of the full workload by linear scaling in heads",
+            "sample_fraction": 32 / BH,
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc,
+                             "sample_seconds": statistics.median(s[1] for s in samples), "config1": cpu_config1()},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def check_timed_buffers(q, k, v, up, out, gq, gk, gv, heads=(0, 37, 77, 127)):
+    """The buffers the timed steps have just written, compared with the CPU oracle on a subset of the (batch, head)
+    sequences: rel-L2 and max-abs per output (gate: 2e-3 / 1e-2)."""
+    from oracle import rfa_oracle as O
+    idx = list(heads)
+    qf, kf, vf, gf = (t[:, idx].float().cpu() for t in (q, k, v, up))
+    ro = O.causal_forward(qf, kf, vf)
+    rq, rk, rv = O.causal_backward(qf, kf, vf, gf)
+    res = {"heads": idx, "gate": {"rel_l2": 2e-3, "max_abs": 1e-2}}
+    ok = True
+    for name, a, b in (("out", out, ro), ("gq", gq, rq), ("gk", gk, rk), ("gv", gv, rv)):
+        a = a[:, idx].float().cpu()
+        r, m = O.rel_l2(a, b), O.max_abs(a, b)
+        res[name] = {"rel_l2": r, "max_abs": m}
+        ok = ok and r <= 2e-3 and m <= 1e-2 and bool(torch.isfinite(a).all())
+    res["ok"] = ok
+    return res
+
+
+# DRAM bytes per launch of the three kernels at this workload (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+# capture each; the summaries with the commands are in profiles/causal_tc_kernels_B8H16T2048.md)
+NCU_TRAFFIC = {"causal_fwd": 185.0e6, "causal_bwd_q": 246.0e6, "causal_bwd_kv": 270.0e6}
 
 
 def upstream_cuda_leg(q, k, v, up, stream, ours_ms):
@@ -268,20 +343,21 @@ def extras(device, stream, hbm):
     return out
 
 
-def run_long(args, rank, local_rank, world):
-    """Long-sequence causal fwd+bwd: batch 1, heads 32, seq 131072, sharded over heads at 2 GPUs and over
-    heads x sequence at 4 and 8 (sequence shards exchange boundary states: rfa_b200.sharded)."""
+LONG_H, LONG_T = 32, 131072
+
+
+def long_sequence(steps, warmup, rank, world, device, use_graph=True):
+    """Long-sequence causal fwd+bwd (BASELINE config 5): batch 1, heads 32, seq 131072, sharded over heads at 2 GPUs and
+    over heads x sequence at 4 and 8 (sequence shards exchange boundary states: rfa_b200.sharded).  The process group,
+    if any, is already initialised.  Returns (result dict on rank 0 / None elsewhere, release) -- call release() before
+    the process group is destroyed: it drops the captured graph, which holds the communicator's collectives."""
     import torch.distributed as dist
     from rfa_b200 import sharded
-    Hh, Tt = 32, 131072
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    Hh, Tt = LONG_H, LONG_T
     group = None
     g_h = 2 if world >= 2 else 1
     g_s = world // g_h
     if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
         for i in range(g_h):
             grp = dist.new_group(list(range(i * g_s, (i + 1) * g_s)))
             if rank // g_s == i:
@@ -305,13 +381,14 @@ def run_long(args, rank, local_rank, world):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-    for _ in range(args.warmup):
+    for _ in range(max(warmup, 3)):
         step()
     barrier()
-    # The step is ~40 short launches plus two all-gathers: issued eagerly it is bound by the host.  Capture it in a CUDA
-    # graph (kernels, NCCL all-gathers and the autograd backward alike); fall back to eager issue if capture fails.
-    run, mode = step, "eager"
-    if not args.no_graph:
+    # The step is a handful of short launches around two all-gathers: issued eagerly its host time shows.  Capture it in
+    # a CUDA graph (kernels, NCCL all-gathers and the autograd backward alike); measure eagerly if capture fails.
+    held = {"run": step, "graph": None}
+    mode = "eager"
+    if use_graph:
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(stream)
@@ -324,39 +401,70 @@ def run_long(args, rank, local_rank, world):
                 step()
             graph.replay()
             torch.cuda.synchronize()
-            run, mode = graph.replay, "cuda graph"
+            held["graph"], held["run"], mode = graph, graph.replay, "cuda graph"
         except Exception as e:                      # noqa: BLE001 -- report and measure eagerly
             mode = f"eager (graph capture failed: {type(e).__name__})"
             torch.cuda.synchronize()
     barrier()
-    with ClockSampler(local_rank) as clk:
-        ms = timed(run, args.steps, stream)
+    with ClockSampler(device.index) as clk:
+        ms = timed(held["run"], steps, stream)
         barrier()
     t = torch.tensor([ms], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    if rank == 0:
-        hbm, peak_src = peaks()
-        nbytes = Tt * Hh * BYTES_PATH
-        print(json.dumps({
-            "metric": "long_causal_rfa_fwd_bwd_tokens_per_s", "value": Tt / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"causal RFA fwd+bwd, B1 H{Hh} T{Tt} d64 D64 fp16", "heads_x_sequence_shards": [g_h, g_s],
-                       "l2": "9.1 GB per step, far larger than L2", "issue": mode},
-            "clocks": clk.summary, "gpu_launches": None,
-            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9 / world, "peak": hbm, "unit": "GB/s per GPU",
-                         "frac": nbytes / (ms * 1e-3) / 1e9 / world / hbm, "peak_source": peak_src, "traffic": None}}), flush=True)
-    if world > 1:
-        dist.barrier()
+
+    def release():
+        held["run"] = None
+        held["graph"] = None            # the graph's destructor runs here, before any communicator is torn down
         torch.cuda.synchronize()
-        if mode == "cuda graph":
-            # tearing the process group down under a captured graph that holds NCCL kernels did not return here; every
-            # rank has finished its work and rank 0 has printed, so leave without running the destructors
-            sys.stdout.flush()
-            os._exit(0)
-        dist.destroy_process_group()
+
+    if rank != 0:
+        return None, release
+    hbm, peak_src = peaks()
+    nbytes = Tt * Hh * BYTES_PATH
+    return {
+        "metric": "long_causal_rfa_fwd_bwd_tokens_per_s", "value": Tt / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"causal RFA fwd+bwd, B1 H{Hh} T{Tt} d64 D64 fp16", "heads_x_sequence_shards": [g_h, g_s],
+                   "l2": "9.1 GB per step, far larger than L2", "issue": mode},
+        "clocks": clk.summary,
+        "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9 / world, "peak": hbm, "unit": "GB/s per GPU",
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / world / hbm, "peak_source": peak_src, "traffic": None}}, release
+
+
+def leave(world, releases=()):
+    """Orderly exit of a multi-rank run: drop captured graphs first (a communicator whose collectives a live graph
+    still holds does not tear down), then destroy the process group; if that still does not return within 30 s,
+    every rank has finished and rank 0 has printed, so leave without the destructors."""
+    import threading
+    import torch.distributed as dist
+    for r in releases:
+        r()
+    if world <= 1:
+        return
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    giveup = threading.Timer(30.0, lambda: os._exit(0))
+    giveup.daemon = True
+    giveup.start()
+    dist.destroy_process_group()
+    giveup.cancel()
+
+
+def run_long(args, rank, local_rank, world):
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    res, release = long_sequence(args.steps, args.warmup, rank, world, device, use_graph=not args.no_graph)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    leave(world, [release])
 
 
 def main():
@@ -469,6 +577,18 @@ def main():
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hg))
     d2h = sum(x.numel() * x.element_size() for x in ho)
 
+    parity = check_timed_buffers(q, k, v, up, out, gq, gk, gv) if rank == 0 else None
+
+    # ---- the long-sequence workload (config 5) at this N: the sequence-sharded path with its exchange of states
+    long_res, release = None, (lambda: None)
+    if not args.no_extras:
+        hq = hk = hv = hg = ho = pipe = None      # the pinned buffers and the pipeline's device buffers are no longer needed
+        torch.cuda.empty_cache()
+        try:
+            long_res, release = long_sequence(min(args.steps, 10), 3, rank, world, device, use_graph=not args.no_graph)
+        except Exception as e:  # noqa: BLE001
+            long_res = {"error": repr(e)}
+
     if rank == 0:
         units = T * BH
         kbytes = {"causal_fwd": BYTES_FWD, "causal_bwd_q": BYTES_BWD_Q, "causal_bwd_kv": BYTES_BWD_KV}
@@ -478,33 +598,35 @@ def main():
             "metric": "causal_rfa_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": B, "global_batch": B * world, "heads": H, "seq_len": T,
-                       "l2": "inputs+outputs 570 MB per step, larger than the 126 MB L2; no flush",
-                       "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"},
+            "config": workload_config(world),
             "clocks": clk.summary,
             "e2e": {"value": world * TOKENS_PER_STEP / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "h2d_GBps_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_GBps_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
                     "api": "rfa_b200.host_pipeline.HostPipelinedRFA.step (upload / compute / download streams), pinned host buffers"},
-            "gpu_launches": 3 * args.steps,
+            "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+            "parity": parity,
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                         "frac": achieved / hbm, "peak_source": peak_src, "traffic": None,
+                         "frac": achieved / hbm, "peak_source": peak_src, "traffic": NCU_TRAFFIC.get(dom),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one capture of this kernel at this "
+                                           "workload (profiles/)",
                          "algorithmic_bytes_per_launch": units * kbytes[dom], "ms_per_launch": per[dom],
                          "per_kernel_ms": per,
                          "path": {"bytes_per_step": units * BYTES_PATH,
                                   "achieved": units * BYTES_PATH / (ms_per_step * 1e-3) / 1e9,
                                   "frac": units * BYTES_PATH / (ms_per_step * 1e-3) / 1e9 / hbm}},
         }
+        if not args.no_extras:
+            line["extra"] = {"long_sequence": long_res}
         if world == 1:
             tps, cores, desc, dt = cpu_port_sample()
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc,
-                                    "seconds": dt}
+                                    "seconds": dt, "config1": cpu_config1()}
             if not args.no_extras:
-                line["extra"] = extras(device, stream, hbm)
+                line["extra"].update(extras(device, stream, hbm))
                 line["extra"]["upstream_cuda_kernels"] = upstream_cuda_leg(q, k, v, up, stream, ms_per_step)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    leave(world, [release])
 
 
 if __name__ == "__main__":

@@ -3,8 +3,9 @@ that it can be timed and compared on the GPU box.  TEST / BASELINE INFRASTRUCTUR
 
     python oracle/build_ref.py            # needs the upstream checkout and ~10 minutes
 
-Sources are compiled where they lie (the cuda/ directory of the upstream checkout; set
-RFA_REFERENCE_CUDA to point elsewhere); nothing is copied.  The only accommodation is an include
+Sources are compiled where they lie: the cuda/ directory of the upstream checkout, named by the
+environment variable RFA_REFERENCE_CUDA or, without it, looked for in a directory "reference"
+beside this repository; nothing is copied.  The only accommodation is an include
 directory holding an empty THC/THC.h, a header PyTorch no longer ships and upstream does not
 actually use.  Flags follow upstream's setup.py:21-27 except the target architecture
 (compute_100 instead of compute_75).  Output: oracle/_ref/rfa_cuda_ref.so, a PyTorch
@@ -19,7 +20,8 @@ import torch
 from torch.utils import cpp_extension
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SRC = os.environ.get("RFA_REFERENCE_CUDA", "/root/reference/random_feature_attention/cuda")
+SRC = os.environ.get("RFA_REFERENCE_CUDA") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference",
+                                                            "random_feature_attention", "cuda")
 OUT = os.path.join(HERE, "_ref")
 
 

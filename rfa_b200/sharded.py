@@ -27,9 +27,35 @@ import torch.distributed as dist
 from torch import Tensor
 
 
+class InProcessShards:
+    """Stands in for a process group when the shards of one sequence run ONE AFTER ANOTHER in a single process (a
+    sequence whose activations do not fit the device at once; a one-GPU check of the sharded path).  Set ``rank``
+    before each shard's call.  Forward calls must come in rank order 0, 1, ... and backward calls in the opposite
+    order, because a shard's carry is the sum of what the shards before (backward: after) it have deposited here."""
+
+    def __init__(self, world: int):
+        self.world, self.rank = int(world), 0
+        self._deposits = {False: {}, True: {}}
+
+    def exclusive_scan(self, local: Tensor, reverse: bool) -> Tensor:
+        box = self._deposits[reverse]
+        box[self.rank] = local.detach().clone()
+        need = range(self.rank + 1, self.world) if reverse else range(self.rank)
+        missing = [r for r in need if r not in box]
+        if missing:
+            raise RuntimeError(f"InProcessShards: shard {self.rank} ran before shard(s) {missing} "
+                               f"({'backward' if reverse else 'forward'} order violated)")
+        total = torch.zeros_like(local)
+        for r in need:
+            total += box[r]
+        return total
+
+
 def exclusive_scan_over_ranks(local: Tensor, group=None, reverse: bool = False) -> Tensor:
     """Sum of ``local`` over the ranks strictly before (``reverse``: strictly after) this
     rank in ``group``.  One all-gather of the per-rank tensors, then a local sum."""
+    if isinstance(group, InProcessShards):
+        return group.exclusive_scan(local, reverse)
     if not (dist.is_available() and dist.is_initialized()):
         return torch.zeros_like(local)            # single process: nothing comes before or after
     world = dist.get_world_size(group)
@@ -48,6 +74,8 @@ def exclusive_scan_over_ranks(local: Tensor, group=None, reverse: bool = False) 
 
 
 def _group_size(group) -> int:
+    if isinstance(group, InProcessShards):
+        return group.world
     if not (dist.is_available() and dist.is_initialized()):
         return 1
     return dist.get_world_size(group)

@@ -30,8 +30,10 @@ import typing
 import numpy as np
 import torch
 
-REF = os.environ.get("RFA_REFERENCE", "/root/reference/random_feature_attention")
 OUT = os.path.dirname(os.path.abspath(__file__))
+# the upstream package directory: RFA_REFERENCE, or a checkout named "reference" beside this repository
+REF = os.environ.get("RFA_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(OUT))), "reference",
+                                                      "random_feature_attention")
 
 
 def load_upstream():
