@@ -33,7 +33,7 @@ TOKENS_PER_STEP = B * T
 # algorithmic bytes per (token, head): fwd reads q,k (2*K*2) + v (d*2), writes out (d*2);
 # bwd reads q,k,v,g and writes gq,gk (2*K*2) + gv (d*2)
 BYTES_FWD = 2 * K_FEAT * 2 + 2 * D_HEAD * 2                       # 768
-BYTES_BWD_Q = 2 * K_FEAT * 2 + 2 * D_HEAD * 2 + K_FEAT * 2          # 1024  (q,k,v,g in; gq out)
+BYTES_BWD_Q = K_FEAT * 2 + 3 * D_HEAD * 2 + K_FEAT * 2              # 896   (k,v,g and the saved out in; gq out: q is not read)
 BYTES_BWD_KV = 2 * K_FEAT * 2 + 2 * D_HEAD * 2 + K_FEAT * 2 + D_HEAD * 2   # 1152  (q,k,v,g in; gk,gv out)
 BYTES_PATH = 2176                                                 # fwd 768 + bwd (768 in + 640 out)
 LAUNCHES_PER_STEP = 3                                             # causal_fwd, causal_bwd_q, causal_bwd_kv
@@ -238,7 +238,7 @@ def check_timed_buffers(q, k, v, up, out, gq, gk, gv, heads=(0, 37, 77, 127)):
 
 # DRAM bytes per launch of the three kernels at this workload (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture each; the summaries with the commands are in profiles/causal_tc_kernels_B8H16T2048.md)
-NCU_TRAFFIC = {"causal_fwd": 185.0e6, "causal_bwd_q": 246.0e6, "causal_bwd_kv": 270.0e6}
+NCU_TRAFFIC = {"causal_fwd": 185.0e6, "causal_bwd_q": None, "causal_bwd_kv": 270.0e6}
 
 
 def upstream_cuda_leg(q, k, v, up, stream, ours_ms):
@@ -502,6 +502,13 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     hbm, peak_src = peaks()
     stream = torch.cuda.current_stream()
+    # pinned buffers and the copy-issuing thread next to the GPU's PCIe root (undone before the CPU baseline is timed)
+    # (the CPU worker threads are started first, so that they keep the full core set for the CPU baseline)
+    from rfa_b200.host_pipeline import bind_to_gpu_numa_node
+    if world == 1:
+        host_threads()
+        torch.randn(1 << 22).sum().item()
+    affinity_before = bind_to_gpu_numa_node(local_rank)
     q, k, v, up, _ = make_inputs(rank, device)
     gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     out = torch.empty_like(v)
@@ -510,11 +517,17 @@ def main():
     ws = torch.empty(max(nws, 256), dtype=torch.uint8, device=device)
     P, st = ops.ptr, stream.cuda_stream
 
+    # what RFA.apply runs: the forward keeps its raw denominators (and segment states) in the workspace, the backward's
+    # first sweep reads them and the forward's output instead of recomputing scores and numerators
+    kept = ops._lib.WS_STATES | ops._lib.WS_DEN
+
     def fwd():
-        ops.check(lib.rfa_causal_fwd(P(q), P(k), P(v), P(out), None, None, None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD, st), "fwd")
+        ops.check(lib.rfa_causal_fwd_staged(P(q), P(k), P(v), P(out), None, None, None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD,
+                                            0, 1, st), "fwd")
 
     def bwd_q():
-        ops.check(lib.rfa_causal_bwd_q(P(q), P(k), P(v), P(up), P(gq), None, None, None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD, st), "bwd_q")
+        ops.check(lib.rfa_causal_bwd_q_staged(P(q), P(k), P(v), P(up), P(out), P(gq), None, None, None, P(ws), nws, T, BH, K_FEAT,
+                                              D_HEAD, kept, st), "bwd_q")
 
     def bwd_kv():
         ops.check(lib.rfa_causal_bwd_kv(P(q), P(k), P(v), P(up), P(gk), P(gv), None, None, P(ws), nws, T, BH, K_FEAT, D_HEAD, st), "bwd_kv")
@@ -577,6 +590,8 @@ def main():
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hg))
     d2h = sum(x.numel() * x.element_size() for x in ho)
 
+    if affinity_before is not None:
+        os.sched_setaffinity(0, affinity_before)
     parity = check_timed_buffers(q, k, v, up, out, gq, gk, gv) if rank == 0 else None
 
     # ---- the long-sequence workload (config 5) at this N: the sequence-sharded path with its exchange of states
@@ -603,6 +618,7 @@ def main():
             "e2e": {"value": world * TOKENS_PER_STEP / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "h2d_GBps_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_GBps_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
+                    "numa_bound": affinity_before is not None,
                     "api": "rfa_b200.host_pipeline.HostPipelinedRFA.step (upload / compute / download streams), pinned host buffers"},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps,
             "parity": parity,

@@ -141,6 +141,62 @@ int rfa_causal_bwd_noalloc(const void* q, const void* k, const void* v, const vo
                            void* gq, void* gk, void* gv,
                            int64_t T, int BH, int K, int d, rfa_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Staged forms of the causal path: the same kernels, for callers that keep the
+ * workspace (and the forward's output) from one call to the next -- an autograd
+ * function between forward and backward, the shards of a split sequence between
+ * their local steps and the exchange.  No counterpart upstream, whose backward
+ * recomputes everything from (q, k, v) (rfa.py:126-145, cuda/backward.cu:303-371)
+ * and whose kernels walk a whole sequence in one CTA (cuda/forward.cu:112-125).
+ *
+ * ws_has says what the workspace already holds FOR THESE SAME ARGUMENTS:
+ *   RFA_WS_PARTIALS  per-segment sums of k (x) v and k, left by
+ *                    rfa_causal_shard_total (the forward then skips that pass);
+ *   RFA_WS_STATES    the states entering each segment, left by any forward call
+ *                    with the same s_in/z_in (the backward then skips both the
+ *                    pass and the scan);
+ *   RFA_WS_DEN       the raw denominators q_t . z_t, left by a forward call with
+ *                    save_den != 0.  Together with the forward's output `out`
+ *                    the forward-direction sweep then recomputes neither the
+ *                    scores nor the numerators and reads q only when a
+ *                    reverse-state total is asked for or the sequence is cut
+ *                    into segments.
+ * A call that names something the workspace does not hold computes garbage.
+ *
+ * rfa_causal_shard_total: total_packed [BH, K*d + K] = [sum k (x) v | sum k] over
+ * this call's tokens.  rfa_exclusive_scan_gathered: from gathered
+ * [world, BH, K*d + K] (every shard's packed total, e.g. after an all-gather) the
+ * sum over the shards before (reverse != 0: after) shard `rank`, as s_out
+ * [BH,K,d] and z_out [BH,K].  rfa_causal_bwd_q_staged: as rfa_causal_bwd_q, with
+ * the reverse-state total written packed (dtotal_packed, may be NULL) and `out`
+ * (may be NULL without RFA_WS_DEN).  rfa_causal_bwd_saved: both sweeps.
+ * ---------------------------------------------------------------------- */
+enum { RFA_WS_EMPTY = 0, RFA_WS_PARTIALS = 1, RFA_WS_STATES = 2, RFA_WS_DEN = 4 };
+
+int rfa_causal_fwd_staged(const void* q, const void* k, const void* v, void* out,
+                          const float* s_in, const float* z_in,
+                          float* s_out, float* z_out,
+                          void* workspace, size_t workspace_bytes,
+                          int64_t T, int BH, int K, int d,
+                          int ws_has, int save_den, rfa_stream_t stream);
+int rfa_causal_shard_total(const void* k, const void* v, float* total_packed,
+                           void* workspace, size_t workspace_bytes,
+                           int64_t T, int BH, int K, int d, rfa_stream_t stream);
+int rfa_exclusive_scan_gathered(const float* gathered, int world, int rank, int reverse,
+                                float* s_out, float* z_out,
+                                int BH, int K, int d, rfa_stream_t stream);
+int rfa_causal_bwd_q_staged(const void* q, const void* k, const void* v, const void* g,
+                            const void* out, void* gq,
+                            const float* s_in, const float* z_in, float* dtotal_packed,
+                            void* workspace, size_t workspace_bytes,
+                            int64_t T, int BH, int K, int d, int ws_has, rfa_stream_t stream);
+int rfa_causal_bwd_saved(const void* q, const void* k, const void* v, const void* g,
+                         const void* out, void* gq, void* gk, void* gv,
+                         const float* s_in, const float* z_in,
+                         const float* ds_in, const float* dz_in,
+                         void* workspace, size_t workspace_bytes,
+                         int64_t T, int BH, int K, int d, int ws_has, rfa_stream_t stream);
+
 /* The two halves of the backward, for a sequence sharded across devices:
  * _bwd_q runs the forward-direction sweep (gq; leaves per-token scalars in the
  * workspace) and writes this shard's own reverse-state total to ds_seg/dz_seg;

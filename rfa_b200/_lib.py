@@ -16,6 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "librfa_b200.so")
 
 RFA_F16, RFA_F32 = 0, 1
+WS_EMPTY, WS_PARTIALS, WS_STATES, WS_DEN = 0, 1, 2, 4      # what a kept workspace holds (include/rfa_b200.h)
 _DTYPE_CODE = {torch.float16: RFA_F16, torch.float32: RFA_F32}
 
 _i64, _int, _f32, _vp, _sz = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t
@@ -34,6 +35,11 @@ SIGNATURES = {
     "rfa_causal_bwd": (_int, [_vp] * 4 + [_vp] * 3 + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_causal_bwd_q": (_int, [_vp] * 4 + [_vp] + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_causal_bwd_kv": (_int, [_vp] * 4 + [_vp] * 2 + [_vp] * 2 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
+    "rfa_causal_fwd_staged": (_int, [_vp] * 4 + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _int, _int, _vp]),
+    "rfa_causal_shard_total": (_int, [_vp] * 3 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
+    "rfa_exclusive_scan_gathered": (_int, [_vp, _int, _int, _int, _vp, _vp, _int, _int, _int, _vp]),
+    "rfa_causal_bwd_q_staged": (_int, [_vp] * 6 + [_vp] * 3 + [_vp, _sz, _i64, _int, _int, _int, _int, _vp]),
+    "rfa_causal_bwd_saved": (_int, [_vp] * 8 + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _int, _vp]),
     "rfa_causal_bwd_noalloc_max_token_heads": (_i64, []),
     "rfa_causal_bwd_noalloc": (_int, [_vp] * 4 + [_vp] * 3 + [_i64, _int, _int, _int, _vp]),
     "rfa_cross_state_fwd": (_int, [_vp] * 5 + [_i64, _int, _int, _int, _int, _vp]),

@@ -24,8 +24,12 @@ constexpr int kSegAlign = 128;
 
 // tensor-core forward (causal_tc.cu)
 int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __half* out, const float* s_seg,
-                         const float* z_seg, float* s_out, float* z_out, int64_t T, int BH, int nseg, int64_t tseg,
-                         cudaStream_t st);
+                         const float* z_seg, float* s_out, float* z_out, float* den_out, int64_t T, int BH, int nseg,
+                         int64_t tseg, cudaStream_t st);
+// forward-direction sweep from the forward's saved output and raw denominators (causal_bwd_q_saved_tc.cu)
+int launch_causal_bwd_q_saved_tc(const __half* q, const __half* k, const __half* v, const __half* g, const __half* out,
+                                 const float* den_raw, __half* gq, const float* s_seg, const float* z_seg, float* ws_gz,
+                                 float* ds_seg, float* dz_seg, int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st);
 // tensor-core backward, forward-direction sweep (causal_bwd_tc.cu)
 int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gq,
                            const float* s_seg, const float* z_seg, float* ws_den, float* ws_gz, float* ds_seg,
@@ -84,25 +88,60 @@ static CausalWs carve_ws(void* base, int64_t T, int BH, const CausalPlan& p) {
   return w;
 }
 
-// In-place exclusive scan over the segment axis of seg [BH][nseg][n] (forward or
-// reverse order), seeded with carry [BH][n] (may be null); optionally also the plain
-// sum over segments into total [BH][n].
-__global__ void scan_states_kernel(float* __restrict__ seg, const float* __restrict__ carry,
-                                   float* __restrict__ total, int BH, int nseg, int n, int reverse,
-                                   int do_scan) {
+constexpr int kStateN = kK * kD + kK;          // floats of one packed state [S (K*d) | z (K)]
+
+// element e of the packed state of (bh, segment): S and z live in two arrays
+__device__ __forceinline__ float* state_elem(float* s_seg, float* z_seg, size_t bh, int nseg, int sg, int e) {
+  return e < kK * kD ? s_seg + (bh * nseg + sg) * (size_t)(kK * kD) + e : z_seg + (bh * nseg + sg) * (size_t)kK + (e - kK * kD);
+}
+
+// In-place exclusive scan over the segment axis of s_seg [BH][nseg][K*d] and z_seg [BH][nseg][K] (forward or reverse
+// order), seeded with carry_s [BH][K*d] / carry_z [BH][K] (may be null).
+__global__ void scan_states_kernel(float* __restrict__ s_seg, float* __restrict__ z_seg, const float* __restrict__ carry_s,
+                                   const float* __restrict__ carry_z, int BH, int nseg, int reverse) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)BH * n) return;
-  const size_t bh = i / n, e = i % n;
-  float run = carry ? carry[i] : 0.f, sum = 0.f;
+  if (i >= (size_t)BH * kStateN) return;
+  const size_t bh = i / kStateN;
+  const int e = (int)(i % kStateN);
+  float run = 0.f;
+  if (carry_s) run = e < kK * kD ? carry_s[bh * (kK * kD) + e] : carry_z[bh * kK + (e - kK * kD)];
   for (int j = 0; j < nseg; ++j) {
-    const int sgi = reverse ? nseg - 1 - j : j;
-    float* p = seg + (bh * nseg + sgi) * n + e;
+    float* p = state_elem(s_seg, z_seg, bh, nseg, reverse ? nseg - 1 - j : j, e);
     const float t = *p;
-    if (do_scan) *p = run;
+    *p = run;
     run += t;
-    sum += t;
   }
-  if (total) total[i] = sum;
+}
+
+// Sum over the segment axis -> packed [BH][K*d + K] and / or the two plain arrays tot_s [BH][K*d], tot_z [BH][K].
+__global__ void total_states_kernel(const float* __restrict__ s_seg, const float* __restrict__ z_seg, float* __restrict__ packed,
+                                    float* __restrict__ tot_s, float* __restrict__ tot_z, int BH, int nseg) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)BH * kStateN) return;
+  const size_t bh = i / kStateN;
+  const int e = (int)(i % kStateN);
+  float sum = 0.f;
+  for (int j = 0; j < nseg; ++j)
+    sum += *state_elem(const_cast<float*>(s_seg), const_cast<float*>(z_seg), bh, nseg, j, e);
+  if (packed) packed[i] = sum;
+  if (tot_s) {
+    if (e < kK * kD) tot_s[bh * (kK * kD) + e] = sum; else tot_z[bh * kK + (e - kK * kD)] = sum;
+  }
+}
+
+// gathered [world][BH][K*d + K]: the packed totals of all shards.  out = sum over the shards before (reverse: after)
+// shard `rank`, written as the two plain arrays a kernel takes as its carry.
+__global__ void scan_gathered_kernel(const float* __restrict__ gathered, int world, int rank, int reverse,
+                                     float* __restrict__ out_s, float* __restrict__ out_z, int BH) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n = (size_t)BH * kStateN;
+  if (i >= n) return;
+  float sum = 0.f;
+  const int lo = reverse ? rank + 1 : 0, hi = reverse ? world : rank;
+  for (int r = lo; r < hi; ++r) sum += gathered[(size_t)r * n + i];
+  const size_t bh = i / kStateN;
+  const int e = (int)(i % kStateN);
+  if (e < kK * kD) out_s[bh * (kK * kD) + e] = sum; else out_z[bh * kK + (e - kK * kD)] = sum;
 }
 
 // ---------------------------------------------------------------------------
@@ -115,19 +154,24 @@ static int check_geometry(const char* what, int64_t T, int BH, int K, int d) {
   return 0;
 }
 
-static int scan_launch(float* seg, const float* carry, float* total, int BH, int nseg, int n, int reverse,
-                       int do_scan, cudaStream_t st) {
-  const size_t items = (size_t)BH * n;
-  scan_states_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(seg, carry, total, BH, nseg, n, reverse, do_scan);
+static unsigned state_blocks(int BH) { return (unsigned)(((size_t)BH * kStateN + 255) / 256); }
+
+static int scan_launch(float* s_seg, float* z_seg, const float* carry_s, const float* carry_z, int BH, int nseg, int reverse,
+                       cudaStream_t st) {
+  scan_states_kernel<<<state_blocks(BH), 256, 0, st>>>(s_seg, z_seg, carry_s, carry_z, BH, nseg, reverse);
   return check_launch("scan_states");
 }
 
-// Forward states entering every segment -> ws.s_seg / ws.z_seg (nseg > 1 only).
-static int build_segment_states(const __half* k, const __half* v, const float* s_in, const float* z_in,
-                                const CausalWs& ws, const CausalPlan& p, int64_t T, int BH, cudaStream_t st) {
-  if (int e = launch_cross_state_fwd_tc(k, v, nullptr, ws.s_seg, ws.z_seg, T, BH, 1, p.nseg, p.tseg, st)) return e;
-  if (int e = scan_launch(ws.s_seg, s_in, nullptr, BH, p.nseg, kK * kD, 0, 1, st)) return e;
-  return scan_launch(ws.z_seg, z_in, nullptr, BH, p.nseg, kK, 0, 1, st);
+static int total_launch(const float* s_seg, const float* z_seg, float* packed, float* tot_s, float* tot_z, int BH, int nseg,
+                        cudaStream_t st) {
+  total_states_kernel<<<state_blocks(BH), 256, 0, st>>>(s_seg, z_seg, packed, tot_s, tot_z, BH, nseg);
+  return check_launch("total_states");
+}
+
+// Per-segment sums of k (x) v and k -> ws.s_seg / ws.z_seg (one CTA per (batch, head, segment)).
+static int segment_partials(const __half* k, const __half* v, const CausalWs& ws, const CausalPlan& p, int64_t T, int BH,
+                            cudaStream_t st) {
+  return launch_cross_state_fwd_tc(k, v, nullptr, ws.s_seg, ws.z_seg, T, BH, 1, p.nseg, p.tseg, st);
 }
 
 static int check_ws(const char* what, void* workspace, size_t bytes, int64_t T, int BH, const CausalPlan& p, CausalWs* out) {
@@ -148,16 +192,18 @@ extern "C" size_t rfa_causal_workspace_bytes(int64_t T, int BH, int K, int d) {
   return carve_ws(nullptr, T, BH, p).bytes;
 }
 
-extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void* out,
-                              const float* s_in, const float* z_in, float* s_out, float* z_out,
-                              void* workspace, size_t workspace_bytes,
-                              int64_t T, int BH, int K, int d, rfa_stream_t stream) {
+// ---- forward ---------------------------------------------------------------------------------------------------
+extern "C" int rfa_causal_fwd_staged(const void* q, const void* k, const void* v, void* out,
+                                     const float* s_in, const float* z_in, float* s_out, float* z_out,
+                                     void* workspace, size_t workspace_bytes,
+                                     int64_t T, int BH, int K, int d, int ws_has, int save_den, rfa_stream_t stream) {
   if (int e = check_geometry("causal_fwd", T, BH, K, d)) return e;
   RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (s_out == nullptr) == (z_out == nullptr), RFA_EINVAL,
               "causal_fwd: s/z pointers must be given in pairs");
   RFA_REQUIRE(T == 0 || (q && k && v && out), RFA_EINVAL, "causal_fwd: null pointer");   // empty arrays have no address
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(s_in) && aligned16(z_in) &&
                   aligned16(s_out) && aligned16(z_out), RFA_EALIGN, "causal_fwd: 16-byte alignment required");
+  RFA_REQUIRE((ws_has & ~RFA_WS_PARTIALS) == 0, RFA_EINVAL, "causal_fwd: ws_has may only name RFA_WS_PARTIALS (got %d)", ws_has);
   const CausalPlan p = plan_causal(T, BH);
   cudaStream_t st = as_stream(stream);
   const float *s_seg = s_in, *z_seg = z_in;
@@ -173,57 +219,128 @@ extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void*
     }
     return check_launch("causal_fwd(T=0)");
   }
-  if (p.nseg > 1) {
-    CausalWs ws;
+  CausalWs ws{};
+  if (p.nseg > 1 || save_den)
     if (int e = check_ws("causal_fwd", workspace, workspace_bytes, T, BH, p, &ws)) return e;
-    if (int e = build_segment_states((const __half*)k, (const __half*)v, s_in, z_in, ws, p, T, BH, st)) return e;
+  if (p.nseg > 1) {
+    if (!(ws_has & RFA_WS_PARTIALS))
+      if (int e = segment_partials((const __half*)k, (const __half*)v, ws, p, T, BH, st)) return e;
+    if (int e = scan_launch(ws.s_seg, ws.z_seg, s_in, z_in, BH, p.nseg, 0, st)) return e;
     s_seg = ws.s_seg;
     z_seg = ws.z_seg;
   }
   return launch_causal_fwd_tc((const __half*)q, (const __half*)k, (const __half*)v, (__half*)out, s_seg, z_seg, s_out,
-                              z_out, T, BH, p.nseg, p.tseg, st);
+                              z_out, save_den ? ws.den : nullptr, T, BH, p.nseg, p.tseg, st);
 }
 
-extern "C" int rfa_causal_bwd_q(const void* q, const void* k, const void* v, const void* g, void* gq,
-                                const float* s_in, const float* z_in, float* ds_seg, float* dz_seg,
-                                void* workspace, size_t workspace_bytes,
-                                int64_t T, int BH, int K, int d, rfa_stream_t stream) {
-  if (int e = check_geometry("causal_bwd_q", T, BH, K, d)) return e;
-  RFA_REQUIRE(T == 0 || (q && k && v && g && gq), RFA_EINVAL, "causal_bwd_q: null pointer");   // empty arrays have no address
-  RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (ds_seg == nullptr) == (dz_seg == nullptr), RFA_EINVAL,
-              "causal_bwd_q: s/z pointers must be given in pairs");
-  RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) && aligned16(gq) && aligned16(s_in) &&
-                  aligned16(z_in) && aligned16(ds_seg) && aligned16(dz_seg), RFA_EALIGN,
-              "causal_bwd_q: 16-byte alignment required");
-  const CausalPlan p = plan_causal(T, BH);
+extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void* out,
+                              const float* s_in, const float* z_in, float* s_out, float* z_out,
+                              void* workspace, size_t workspace_bytes,
+                              int64_t T, int BH, int K, int d, rfa_stream_t stream) {
+  return rfa_causal_fwd_staged(q, k, v, out, s_in, z_in, s_out, z_out, workspace, workspace_bytes, T, BH, K, d, RFA_WS_EMPTY, 0,
+                               stream);
+}
+
+// This shard's (or call's) own total of k (x) v and k, packed [BH][K*d + K]; leaves the per-segment partial sums in the
+// workspace for rfa_causal_fwd_staged(..., RFA_WS_PARTIALS, ...).
+extern "C" int rfa_causal_shard_total(const void* k, const void* v, float* total_packed, void* workspace, size_t workspace_bytes,
+                                      int64_t T, int BH, int K, int d, rfa_stream_t stream) {
+  if (int e = check_geometry("causal_shard_total", T, BH, K, d)) return e;
+  RFA_REQUIRE(total_packed && (T == 0 || (k && v)), RFA_EINVAL, "causal_shard_total: null pointer");
+  RFA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(total_packed), RFA_EALIGN, "causal_shard_total: 16-byte alignment required");
   cudaStream_t st = as_stream(stream);
   if (T == 0) {
-    if (ds_seg) {
-      cudaMemsetAsync(ds_seg, 0, (size_t)BH * kK * kD * sizeof(float), st);
-      cudaMemsetAsync(dz_seg, 0, (size_t)BH * kK * sizeof(float), st);
+    cudaMemsetAsync(total_packed, 0, (size_t)BH * kStateN * sizeof(float), st);
+    return check_launch("causal_shard_total(T=0)");
+  }
+  const CausalPlan p = plan_causal(T, BH);
+  CausalWs ws;
+  if (int e = check_ws("causal_shard_total", workspace, workspace_bytes, T, BH, p, &ws)) return e;
+  if (int e = segment_partials((const __half*)k, (const __half*)v, ws, p, T, BH, st)) return e;
+  return total_launch(ws.s_seg, ws.z_seg, total_packed, nullptr, nullptr, BH, p.nseg, st);
+}
+
+extern "C" int rfa_exclusive_scan_gathered(const float* gathered, int world, int rank, int reverse, float* s_out, float* z_out,
+                                           int BH, int K, int d, rfa_stream_t stream) {
+  if (int e = check_geometry("exclusive_scan_gathered", 0, BH, K, d)) return e;
+  RFA_REQUIRE(gathered && s_out && z_out, RFA_EINVAL, "exclusive_scan_gathered: null pointer");
+  RFA_REQUIRE(world > 0 && rank >= 0 && rank < world, RFA_EINVAL, "exclusive_scan_gathered: rank %d of %d", rank, world);
+  scan_gathered_kernel<<<state_blocks(BH), 256, 0, as_stream(stream)>>>(gathered, world, rank, reverse ? 1 : 0, s_out, z_out, BH);
+  return check_launch("rfa_exclusive_scan_gathered");
+}
+
+// ---- backward, forward-direction sweep ------------------------------------------------------------------------------
+static int bwd_q_impl(const void* q, const void* k, const void* v, const void* g, const void* out, void* gq,
+                      const float* s_in, const float* z_in, float* ds_tot, float* dz_tot, float* dtotal_packed,
+                      void* workspace, size_t workspace_bytes, int64_t T, int BH, int K, int d, int ws_has,
+                      rfa_stream_t stream) {
+  if (int e = check_geometry("causal_bwd_q", T, BH, K, d)) return e;
+  RFA_REQUIRE(T == 0 || (q && k && v && g && gq), RFA_EINVAL, "causal_bwd_q: null pointer");   // empty arrays have no address
+  RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (ds_tot == nullptr) == (dz_tot == nullptr), RFA_EINVAL,
+              "causal_bwd_q: s/z pointers must be given in pairs");
+  RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) && aligned16(gq) && aligned16(s_in) &&
+                  aligned16(z_in) && aligned16(ds_tot) && aligned16(dz_tot) && aligned16(out) && aligned16(dtotal_packed),
+              RFA_EALIGN, "causal_bwd_q: 16-byte alignment required");
+  RFA_REQUIRE((ws_has & ~(RFA_WS_STATES | RFA_WS_DEN)) == 0, RFA_EINVAL,
+              "causal_bwd_q: ws_has may only name RFA_WS_STATES and RFA_WS_DEN (got %d)", ws_has);
+  RFA_REQUIRE(!(ws_has & RFA_WS_DEN) || out, RFA_EINVAL, "causal_bwd_q: RFA_WS_DEN needs the forward's output as well");
+  const CausalPlan p = plan_causal(T, BH);
+  cudaStream_t st = as_stream(stream);
+  const bool want_tot = ds_tot != nullptr || dtotal_packed != nullptr;
+  if (T == 0) {
+    if (ds_tot) {
+      cudaMemsetAsync(ds_tot, 0, (size_t)BH * kK * kD * sizeof(float), st);
+      cudaMemsetAsync(dz_tot, 0, (size_t)BH * kK * sizeof(float), st);
     }
+    if (dtotal_packed) cudaMemsetAsync(dtotal_packed, 0, (size_t)BH * kStateN * sizeof(float), st);
     return check_launch("causal_bwd_q(T=0)");
   }
   CausalWs ws;
   if (int e = check_ws("causal_bwd_q", workspace, workspace_bytes, T, BH, p, &ws)) return e;
   const float *s_seg = s_in, *z_seg = z_in;
   if (p.nseg > 1) {
-    if (int e = build_segment_states((const __half*)k, (const __half*)v, s_in, z_in, ws, p, T, BH, st)) return e;
+    if (!(ws_has & RFA_WS_STATES)) {    // the states entering each segment: partial sums, then an exclusive scan
+      if (int e = segment_partials((const __half*)k, (const __half*)v, ws, p, T, BH, st)) return e;
+      if (int e = scan_launch(ws.s_seg, ws.z_seg, s_in, z_in, BH, p.nseg, 0, st)) return e;
+    }
     s_seg = ws.s_seg;
     z_seg = ws.z_seg;
   }
-  const bool want_dseg = p.nseg > 1 || ds_seg != nullptr;
-  if (int e = launch_causal_bwd_q_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g,
-                                     (__half*)gq, s_seg, z_seg, ws.den, ws.gz, want_dseg ? ws.ds_seg : nullptr,
-                                     want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg, st))
-    return e;
-  if (ds_seg) {   // this shard's own total, before any carry is known
-    if (int e = scan_launch(ws.ds_seg, nullptr, ds_seg, BH, p.nseg, kK * kD, 1, 0, st)) return e;
-    if (int e = scan_launch(ws.dz_seg, nullptr, dz_seg, BH, p.nseg, kK, 1, 0, st)) return e;
+  const bool want_dseg = p.nseg > 1 || want_tot;
+  if (ws_has & RFA_WS_DEN) {
+    if (int e = launch_causal_bwd_q_saved_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g,
+                                             (const __half*)out, ws.den, (__half*)gq, s_seg, z_seg, ws.gz,
+                                             want_dseg ? ws.ds_seg : nullptr, want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg,
+                                             p.tseg, st))
+      return e;
+  } else {
+    if (int e = launch_causal_bwd_q_tc((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g,
+                                       (__half*)gq, s_seg, z_seg, ws.den, ws.gz, want_dseg ? ws.ds_seg : nullptr,
+                                       want_dseg ? ws.dz_seg : nullptr, T, BH, p.nseg, p.tseg, st))
+      return e;
   }
+  if (want_tot)   // this shard's own total, before any carry is known
+    return total_launch(ws.ds_seg, ws.dz_seg, dtotal_packed, ds_tot, dz_tot, BH, p.nseg, st);
   return 0;
 }
 
+extern "C" int rfa_causal_bwd_q(const void* q, const void* k, const void* v, const void* g, void* gq,
+                                const float* s_in, const float* z_in, float* ds_seg, float* dz_seg,
+                                void* workspace, size_t workspace_bytes,
+                                int64_t T, int BH, int K, int d, rfa_stream_t stream) {
+  return bwd_q_impl(q, k, v, g, nullptr, gq, s_in, z_in, ds_seg, dz_seg, nullptr, workspace, workspace_bytes, T, BH, K, d,
+                    RFA_WS_EMPTY, stream);
+}
+
+extern "C" int rfa_causal_bwd_q_staged(const void* q, const void* k, const void* v, const void* g, const void* out, void* gq,
+                                       const float* s_in, const float* z_in, float* dtotal_packed,
+                                       void* workspace, size_t workspace_bytes,
+                                       int64_t T, int BH, int K, int d, int ws_has, rfa_stream_t stream) {
+  return bwd_q_impl(q, k, v, g, out, gq, s_in, z_in, nullptr, nullptr, dtotal_packed, workspace, workspace_bytes, T, BH, K, d,
+                    ws_has, stream);
+}
+
+// ---- backward, reverse sweep ----------------------------------------------------------------------------------------
 extern "C" int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, const void* g, void* gk, void* gv,
                                  const float* ds_in, const float* dz_in, void* workspace, size_t workspace_bytes,
                                  int64_t T, int BH, int K, int d, rfa_stream_t stream) {
@@ -238,9 +355,8 @@ extern "C" int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, co
   CausalWs ws;
   if (int e = check_ws("causal_bwd_kv", workspace, workspace_bytes, T, BH, p, &ws)) return e;
   const float *ds_seg = ds_in, *dz_seg = dz_in;
-  if (p.nseg > 1) {   // segment totals left by _bwd_q -> reverse exclusive scan seeded with the carry
-    if (int e = scan_launch(ws.ds_seg, ds_in, nullptr, BH, p.nseg, kK * kD, 1, 1, st)) return e;
-    if (int e = scan_launch(ws.dz_seg, dz_in, nullptr, BH, p.nseg, kK, 1, 1, st)) return e;
+  if (p.nseg > 1) {   // segment totals left by the forward-direction sweep -> reverse exclusive scan seeded with the carry
+    if (int e = scan_launch(ws.ds_seg, ws.dz_seg, ds_in, dz_in, BH, p.nseg, 1, st)) return e;
     ds_seg = ws.ds_seg;
     dz_seg = ws.dz_seg;
   }
@@ -253,6 +369,16 @@ extern "C" int rfa_causal_bwd(const void* q, const void* k, const void* v, const
                               const float* ds_in, const float* dz_in, void* workspace, size_t workspace_bytes,
                               int64_t T, int BH, int K, int d, rfa_stream_t stream) {
   if (int e = rfa_causal_bwd_q(q, k, v, g, gq, s_in, z_in, nullptr, nullptr, workspace, workspace_bytes, T, BH, K, d, stream))
+    return e;
+  return rfa_causal_bwd_kv(q, k, v, g, gk, gv, ds_in, dz_in, workspace, workspace_bytes, T, BH, K, d, stream);
+}
+
+// Backward from the forward's saved results: out and a workspace that rfa_causal_fwd_staged(..., save_den = 1) filled.
+extern "C" int rfa_causal_bwd_saved(const void* q, const void* k, const void* v, const void* g, const void* out,
+                                    void* gq, void* gk, void* gv, const float* s_in, const float* z_in,
+                                    const float* ds_in, const float* dz_in, void* workspace, size_t workspace_bytes,
+                                    int64_t T, int BH, int K, int d, int ws_has, rfa_stream_t stream) {
+  if (int e = rfa_causal_bwd_q_staged(q, k, v, g, out, gq, s_in, z_in, nullptr, workspace, workspace_bytes, T, BH, K, d, ws_has, stream))
     return e;
   return rfa_causal_bwd_kv(q, k, v, g, gk, gv, ds_in, dz_in, workspace, workspace_bytes, T, BH, K, d, stream);
 }

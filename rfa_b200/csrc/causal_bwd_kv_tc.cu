@@ -263,7 +263,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       // ---- gs = g / den over the staged g tile; gz of this thread's query row
       float inv = 1.f, gz = 0.f;
       if (t0 + row < t_end) {
-        inv = 1.f / ws_den[(size_t)bh * T + t0 + row];
+        inv = 1.f / fmaxf(ws_den[(size_t)bh * T + t0 + row], kEps);   // raw or already clamped
         gz = ws_gz[(size_t)bh * T + t0 + row];
       }
       if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kFwThreads, 1)
 causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                      const float* __restrict__ s_seg, const float* __restrict__ z_seg,
-                     float* __restrict__ s_out, float* __restrict__ z_out,
+                     float* __restrict__ s_out, float* __restrict__ z_out, float* __restrict__ den_out,
                      int64_t T, int BH, int nseg, int64_t tseg) {
   extern __shared__ unsigned char tc_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~uintptr_t(1023));
@@ -300,7 +300,12 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_before_sync();
       mbar_arrive(&bars[fNFree + st]);
       // ---- out = N / max(rowsum + q.z_prev, 1) -> staging tile -> TMA store
-      const float inv = 1.f / fmaxf(rowsum + __uint_as_float(nz[0]), kEps);
+      const float raw = rowsum + __uint_as_float(nz[0]);
+      const float inv = 1.f / fmaxf(raw, kEps);
+      if (den_out) {                               // the raw denominators [BH][T], kept for a backward that does not recompute them
+        const int64_t t = t_begin + (int64_t)c * kTC + row;
+        if (t < t_end) den_out[(size_t)bh * T + t] = raw;
+      }
       if (c > 0) {                                 // the previous chunk's store must have drained the staging tile
         if (ytid == 0) tma_store_wait_read<0>();
         if (!epi_sync(&bars[fY], y_phase)) { tc_fail(13); ok = false; break; }
@@ -351,15 +356,15 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
 // ---------------------------------------------------------------------------
 int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __half* out, const float* s_seg,
-                         const float* z_seg, float* s_out, float* z_out, int64_t T, int BH, int nseg, int64_t tseg,
-                         cudaStream_t st) {
+                         const float* z_seg, float* s_out, float* z_out, float* den_out, int64_t T, int BH, int nseg,
+                         int64_t tseg, cudaStream_t st) {
   CUtensorMap tq, tk, tv, to;
   if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tk, k, T, BH, kK, kTC) ||
       make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&to, out, T, BH, kD, kTC))
     return fail(RFA_EDEVICE, "causal_fwd: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(causal_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmem);
   if (e != cudaSuccess) return fail((int)e, "causal_fwd: cannot reserve %u bytes of shared memory: %s", kFwSmem, cudaGetErrorString(e));
-  causal_fwd_tc_kernel<<<dim3(BH, nseg), kFwThreads, kFwSmem, st>>>(tq, tk, tv, to, s_seg, z_seg, s_out, z_out, T, BH, nseg, tseg);
+  causal_fwd_tc_kernel<<<dim3(BH, nseg), kFwThreads, kFwSmem, st>>>(tq, tk, tv, to, s_seg, z_seg, s_out, z_out, den_out, T, BH, nseg, tseg);
   return check_launch("rfa_causal_fwd");
 }
 

@@ -117,6 +117,102 @@ def causal_bwd(q: Tensor, k: Tensor, v: Tensor, g: Tensor, s_in: Optional[Tensor
     return gq, gk, gv
 
 
+# --------------------------------------------------------------------------- causal, staged (kept workspace / saved output)
+STATE_N = K_BUILT * D_BUILT + K_BUILT      # floats of one packed state [S | z]
+
+
+def causal_fwd_saved(q: Tensor, k: Tensor, v: Tensor, s_in: Optional[Tensor] = None, z_in: Optional[Tensor] = None,
+                     ws: Optional[Tensor] = None, ws_has: int = 0):
+    """Forward that keeps what the backward can reuse.  Returns (out, workspace, ws_has): the workspace then holds the
+    raw denominators and, when the sequence is cut into segments, the states entering each of them.  ``ws`` / ``ws_has``
+    hand in a workspace that ``shard_total`` has already filled for the same k, v."""
+    require_half(q, k, v)
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty(T, BH, d, dtype=torch.float16, device=q.device)
+    if T == 0:
+        return out, torch.empty(256, dtype=torch.uint8, device=q.device), 0
+    if ws is None:
+        ws, _ = _workspace(T, BH, K, d, q)
+        ws_has = 0
+    with _guard(q):
+        check(_lib.load().rfa_causal_fwd_staged(ptr(q), ptr(k), ptr(v), ptr(out), ptr(s_in), ptr(z_in), None, None,
+                                                ptr(ws), ws.numel(), T, BH, K, d, ws_has & _lib.WS_PARTIALS, 1, stream_of(q)),
+              "rfa_causal_fwd_staged")
+    return out, ws, _lib.WS_STATES | _lib.WS_DEN
+
+
+def causal_bwd_saved(q: Tensor, k: Tensor, v: Tensor, g: Tensor, out: Tensor, ws: Tensor, ws_has: int,
+                     s_in: Optional[Tensor] = None, z_in: Optional[Tensor] = None):
+    """Backward from the forward's output and kept workspace (``causal_fwd_saved``)."""
+    require_half(q, k, v, g, out)
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    q, k, v, g, out = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), out.contiguous()
+    gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if T == 0:
+        return gq, gk, gv
+    with _guard(q):
+        check(_lib.load().rfa_causal_bwd_saved(ptr(q), ptr(k), ptr(v), ptr(g), ptr(out), ptr(gq), ptr(gk), ptr(gv), ptr(s_in),
+                                               ptr(z_in), None, None, ptr(ws), ws.numel(), T, BH, K, d, ws_has, stream_of(q)),
+              "rfa_causal_bwd_saved")
+    return gq, gk, gv
+
+
+def shard_total(k: Tensor, v: Tensor, packed: Optional[Tensor] = None):
+    """This shard's own [sum k (x) v | sum k], packed [BH, K*d + K] fp32 (into ``packed`` when given, e.g. a slice of an
+    all-gather buffer), and the workspace holding the per-segment partial sums for ``causal_fwd_saved``."""
+    require_half(k, v)
+    T, BH, K = k.shape
+    d = v.shape[-1]
+    k, v = k.contiguous(), v.contiguous()
+    if packed is None:
+        packed = torch.empty(BH, K * d + K, dtype=torch.float32, device=k.device)
+    if T == 0:
+        packed.zero_()
+        return packed, None
+    ws, _ = _workspace(T, BH, K, d, k)
+    with _guard(k):
+        check(_lib.load().rfa_causal_shard_total(ptr(k), ptr(v), ptr(packed), ptr(ws), ws.numel(), T, BH, K, d, stream_of(k)),
+              "rfa_causal_shard_total")
+    return packed, ws
+
+
+def scan_gathered(gathered: Tensor, rank: int, reverse: bool, K: int = K_BUILT, d: int = D_BUILT):
+    """gathered [world, BH, K*d + K] fp32 (every shard's packed total) -> the carry of shard ``rank``: the sum over the
+    shards before (``reverse``: after) it, as (s [BH,K,d], z [BH,K])."""
+    world, BH, n = gathered.shape
+    assert n == K * d + K and gathered.dtype == torch.float32 and gathered.is_contiguous()
+    s = torch.empty(BH, K, d, dtype=torch.float32, device=gathered.device)
+    z = torch.empty(BH, K, dtype=torch.float32, device=gathered.device)
+    with _guard(gathered):
+        check(_lib.load().rfa_exclusive_scan_gathered(ptr(gathered), world, rank, int(reverse), ptr(s), ptr(z), BH, K, d,
+                                                      stream_of(gathered)), "rfa_exclusive_scan_gathered")
+    return s, z
+
+
+def causal_bwd_q_staged(q, k, v, g, out, s_in, z_in, ws: Tensor, ws_has: int, packed: Optional[Tensor] = None,
+                        want_total: bool = True):
+    """Forward-direction half of the backward on a kept workspace.  Returns (gq, packed reverse-state total or None)."""
+    require_half(q, k, v, g)
+    T, BH, K = q.shape
+    d = v.shape[-1]
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    gq = torch.empty_like(q)
+    if want_total and packed is None:
+        packed = torch.empty(BH, K * d + K, dtype=torch.float32, device=q.device)
+    if T == 0:
+        if want_total:
+            packed.zero_()
+        return gq, packed if want_total else None
+    with _guard(q):
+        check(_lib.load().rfa_causal_bwd_q_staged(ptr(q), ptr(k), ptr(v), ptr(g), ptr(out), ptr(gq), ptr(s_in), ptr(z_in),
+                                                  ptr(packed) if want_total else None, ptr(ws), ws.numel(), T, BH, K, d, ws_has,
+                                                  stream_of(q)), "rfa_causal_bwd_q_staged")
+    return gq, packed if want_total else None
+
+
 def causal_bwd_q(q, k, v, g, s_in, z_in, want_dseg: bool):
     """Forward-direction half of the backward.  Returns (gq, ds_seg, dz_seg, workspace)."""
     require_half(q, k, v, g)

@@ -5,14 +5,16 @@
 ``attn[t] = q_t^T S_t / max(q_t . z_t, EPS)`` with the inclusive running sums
 ``S_t = sum_{s<=t} k_s v_s^T`` and ``z_t = sum_{s<=t} k_s`` (upstream rfa.py:57-64).
 
-``forward_cuda`` / ``backward_cuda`` run the sm_100a kernels; ``forward_torch`` /
-``backward_torch`` are the PyTorch twins upstream keeps beside them for
-checking (any device, any float dtype).  ``forward``/``backward`` always use the
-kernels -- there is no fallback.
+``forward_cuda`` / ``backward_cuda`` run the sm_100a kernels with upstream's signatures
+(the backward recomputes everything from q, k, v, as upstream's does); ``forward_torch`` /
+``backward_torch`` are the PyTorch twins upstream keeps beside them for checking (any
+device, any float dtype).  ``RFA.apply`` itself keeps the forward's output, raw
+denominators and segment states for its backward, which then skips the recomputation
+(upstream saves q, k, v only, rfa.py:116); there is no fallback to PyTorch.
 """
 import torch
 
-from . import rfa_cuda
+from . import ops, rfa_cuda
 
 EPS = 1.0
 
@@ -70,11 +72,15 @@ class RFA(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v):
-        ctx.save_for_backward(q, k, v)
-        return RFA.forward_cuda(q, k, v)
+        if not (ctx.needs_input_grad[0] or ctx.needs_input_grad[1] or ctx.needs_input_grad[2]):
+            return RFA.forward_cuda(q, k, v)
+        out, ws, has = ops.causal_fwd_saved(q, k, v)
+        ctx.save_for_backward(q, k, v, out, ws)
+        ctx.ws_has = has
+        return out
 
     @staticmethod
     def backward(ctx, grad_attn):
-        q, k, v = ctx.saved_tensors
-        grad_q, grad_k, grad_v = RFA.backward_cuda(q, k, v, grad_attn.contiguous())
+        q, k, v, out, ws = ctx.saved_tensors
+        grad_q, grad_k, grad_v = ops.causal_bwd_saved(q, k, v, grad_attn.contiguous().to(q.dtype), out, ws, ctx.ws_has)
         return grad_q, grad_k, grad_v

@@ -6,9 +6,11 @@ Because the attention state is a plain sum over past tokens, one exchange per di
 suffices (upstream has no multi-device path; its kernel walks the whole sequence in one
 CTA, cuda/forward.cu:112-125):
 
-forward   1. every rank reduces its own tokens to (S_r, z_r)          -- no dependency
-          2. exclusive prefix sum over ranks: carry_r = sum_{j<r} (S_j, z_j)   (one all-gather)
-          3. the local causal kernel runs with that carry
+forward   1. every rank reduces its own tokens to (S_r, z_r)          -- no dependency; the per-segment
+             partial sums stay in the workspace, so the local kernel does not read k, v a second time for them
+          2. exclusive prefix sum over ranks: carry_r = sum_{j<r} (S_j, z_j)   (one all-gather + one small kernel)
+          3. the local causal kernel runs with that carry and keeps its output, raw denominators and segment
+             states for the backward
 backward  1. the forward-direction sweep runs with the saved carry and also yields this
              rank's own reverse-state total (dS_r, dz_r)
           2. exclusive SUFFIX sum over ranks: carry_r = sum_{j>r} (dS_j, dz_j)  (one all-gather)
@@ -62,15 +64,18 @@ def exclusive_scan_over_ranks(local: Tensor, group=None, reverse: bool = False) 
     rank = dist.get_rank(group)
     if world == 1:
         return torch.zeros_like(local)
-    local = local.contiguous()
-    flat = local.reshape(1, -1)
-    gathered = torch.empty((world, flat.shape[1]), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(gathered, flat, group=group)
-    gathered = gathered.view((world,) + tuple(local.shape))
+    gathered = _all_gather(local, group, world)
     sel = gathered[rank + 1:] if reverse else gathered[:rank]
     if sel.shape[0] == 0:
         return torch.zeros_like(local)
     return sel.sum(dim=0)
+
+
+def _all_gather(local: Tensor, group, world: int) -> Tensor:
+    local = local.contiguous()
+    gathered = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(gathered.view(world, -1), local.view(1, -1), group=group)
+    return gathered
 
 
 def _group_size(group) -> int:
@@ -81,34 +86,62 @@ def _group_size(group) -> int:
     return dist.get_world_size(group)
 
 
+def _carry(kern, packed: Tensor, group, reverse: bool, K: int, d: int):
+    """The exchange step: every shard's packed total [BH, K*d + K] -> this shard's carry (s [BH,K,d], z [BH,K]).
+    With a real process group the gathered totals are reduced by one kernel when the kernel set has one."""
+    if not isinstance(group, InProcessShards) and hasattr(kern, "scan_gathered"):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        return kern.scan_gathered(_all_gather(packed, group, world), rank, reverse)
+    total = exclusive_scan_over_ranks(packed, group, reverse)
+    n = K * d
+    return total[:, :n].reshape(-1, K, d).contiguous(), total[:, n:].contiguous()
+
+
 class _CudaKernels:
-    """The four local steps on the sm_100a kernels."""
+    """The local steps on the sm_100a kernels.  Totals travel packed ``[BH, K*d + K]`` (S then z).  What a step keeps for
+    a later one is a tuple of tensors (the kept workspace: per-segment sums, then segment-entry states and raw
+    denominators, then the per-token scalars of the first backward sweep; and the forward's output) plus one plain
+    value; the autograd function stores the tensors with ``save_for_backward``."""
 
     @staticmethod
-    def segment_state(k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor]:
+    def local_total(k: Tensor, v: Tensor):
         from . import ops
-        return ops.state_total(k, v)
+        return ops.shard_total(k, v)
 
     @staticmethod
-    def forward(q, k, v, s_in, z_in):
+    def scan_gathered(gathered: Tensor, rank: int, reverse: bool):
         from . import ops
-        return ops.causal_fwd(q, k, v, s_in, z_in)
+        return ops.scan_gathered(gathered, rank, reverse)
 
     @staticmethod
-    def backward_q(q, k, v, g, s_in, z_in):
-        from . import ops
-        gq, ds, dz, ws = ops.causal_bwd_q(q, k, v, g, s_in, z_in, True)
-        return gq, ds, dz, ws
+    def forward(q, k, v, s_in, z_in, ws):
+        from . import _lib, ops
+        out, ws, has = ops.causal_fwd_saved(q, k, v, s_in, z_in, ws, _lib.WS_PARTIALS if ws is not None else 0)
+        return out, (out, ws), has
 
     @staticmethod
-    def backward_kv(q, k, v, g, ds_in, dz_in, ctx):
+    def backward_q(q, k, v, g, s_in, z_in, kept, has):
         from . import ops
-        return ops.causal_bwd_kv(q, k, v, g, ds_in, dz_in, ctx)
+        out, ws = kept
+        gq, dpacked = ops.causal_bwd_q_staged(q, k, v, g, out, s_in, z_in, ws, has)
+        return gq, dpacked, ws
 
     @staticmethod
-    def backward_full(q, k, v, g):
+    def backward_kv(q, k, v, g, ds_in, dz_in, ws):
         from . import ops
-        return ops.causal_bwd(q, k, v, g, None, None, None, None)
+        return ops.causal_bwd_kv(q, k, v, g, ds_in, dz_in, ws)
+
+    @staticmethod
+    def forward_alone(q, k, v):
+        from . import ops
+        out, ws, has = ops.causal_fwd_saved(q, k, v)
+        return out, (out, ws), has
+
+    @staticmethod
+    def backward_alone(q, k, v, g, kept, has):
+        from . import ops
+        out, ws = kept
+        return ops.causal_bwd_saved(q, k, v, g, out, ws, has)
 
 
 class SequenceShardedRFA(torch.autograd.Function):
@@ -121,37 +154,28 @@ class SequenceShardedRFA(torch.autograd.Function):
         kern = SequenceShardedRFA.kernels
         ctx.group = group
         ctx.alone = _group_size(group) == 1
+        K, d = q.shape[-1], v.shape[-1]
         if ctx.alone:                              # the whole sequence is here: no carry in either direction
-            ctx.save_for_backward(q, k, v)
-            return kern.forward(q, k, v, None, None)
-        s_loc, z_loc = kern.segment_state(k, v)
-        packed = torch.cat([s_loc.reshape(s_loc.shape[0], -1), z_loc], dim=1)          # [BH, K*d + K]
-        carry = exclusive_scan_over_ranks(packed, group)
-        n = s_loc[0].numel()
-        s_in = carry[:, :n].reshape(s_loc.shape).contiguous()
-        z_in = carry[:, n:].contiguous()
-        ctx.group = group
-        ctx.save_for_backward(q, k, v, s_in, z_in)
-        return kern.forward(q, k, v, s_in, z_in)
+            out, kept, ctx.meta = kern.forward_alone(q, k, v)
+            ctx.save_for_backward(q, k, v, *kept)
+            return out
+        packed, fwd_ctx = kern.local_total(k, v)
+        s_in, z_in = _carry(kern, packed, group, False, K, d)
+        out, kept, ctx.meta = kern.forward(q, k, v, s_in, z_in, fwd_ctx)
+        ctx.save_for_backward(q, k, v, s_in, z_in, *kept)
+        return out
 
     @staticmethod
     def backward(ctx, g):
         kern = SequenceShardedRFA.kernels
         g = g.contiguous()
         if ctx.alone:
-            q, k, v = ctx.saved_tensors
-            if hasattr(kern, "backward_full"):
-                return tuple(kern.backward_full(q, k, v, g)) + (None,)
-            gq, _, _, sweep_ctx = kern.backward_q(q, k, v, g, None, None)
-            gk, gv = kern.backward_kv(q, k, v, g, None, None, sweep_ctx)
-            return gq, gk, gv, None
-        q, k, v, s_in, z_in = ctx.saved_tensors
-        gq, ds_loc, dz_loc, sweep_ctx = kern.backward_q(q, k, v, g, s_in, z_in)
-        packed = torch.cat([ds_loc.reshape(ds_loc.shape[0], -1), dz_loc], dim=1)
-        carry = exclusive_scan_over_ranks(packed, ctx.group, reverse=True)
-        n = ds_loc[0].numel()
-        ds_in = carry[:, :n].reshape(ds_loc.shape).contiguous()
-        dz_in = carry[:, n:].contiguous()
+            q, k, v, *kept = ctx.saved_tensors
+            return tuple(kern.backward_alone(q, k, v, g, tuple(kept), ctx.meta)) + (None,)
+        q, k, v, s_in, z_in, *kept = ctx.saved_tensors
+        K, d = q.shape[-1], v.shape[-1]
+        gq, dpacked, sweep_ctx = kern.backward_q(q, k, v, g, s_in, z_in, tuple(kept), ctx.meta)
+        ds_in, dz_in = _carry(kern, dpacked, ctx.group, True, K, d)
         gk, gv = kern.backward_kv(q, k, v, g, ds_in, dz_in, sweep_ctx)
         return gq, gk, gv, None
 

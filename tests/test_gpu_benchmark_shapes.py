@@ -24,9 +24,12 @@ def test_headline_workload_all_heads_vs_oracle(dev):
     q, k, v, up, _ = bench.make_inputs(0, dev)
     T, BH = q.shape[0], q.shape[1]
     assert (T, BH) == (2048, 128)
-    out = ops.causal_fwd(q, k, v)
-    gq, gk, gv = ops.causal_bwd(q, k, v, up)
+    out, ws, has = ops.causal_fwd_saved(q, k, v)              # what RFA.apply and the benchmark run
+    gq, gk, gv = ops.causal_bwd_saved(q, k, v, up, out, ws, has)
+    rec = (ops.causal_fwd(q, k, v),) + tuple(ops.causal_bwd(q, k, v, up))      # upstream's signature: recompute from q, k, v
     torch.cuda.synchronize()
+    for name, a, b in zip(("out", "gq", "gk", "gv"), (out, gq, gk, gv), rec):
+        assert_close(a, b.float().cpu(), f"c2 {name}: saved-output path vs recomputing path", rel=1e-3)
     worst = {}
     for lo in range(0, BH, 32):
         sl = slice(lo, lo + 32)

@@ -68,6 +68,47 @@ def test_causal_vs_oracle_shapes(dev, T, BH):
     assert_close(out, ro, "out"); assert_close(gq, rq, "gq"); assert_close(gk, rk, "gk"); assert_close(gv, rv, "gv")
 
 
+@pytest.mark.parametrize("T,BH", [(1, 1), (63, 2), (65, 2), (131, 3), (513, 2), (1100, 2), (2048, 5), (4096, 130)])
+def test_causal_saved_output_backward_vs_oracle(dev, T, BH):
+    """The backward that reuses the forward's output, raw denominators and segment states (what RFA.apply runs) instead of
+    recomputing them: ragged lengths, the segmented plan (T >= 1024 with few heads: also reads q for the segment totals)
+    and more heads than SMs."""
+    from rfa_b200 import ops
+    q, k, v, g = feats(T, BH, seed=T * 5 + BH)
+    qh, kh, vh, gh = (t.half().to(dev) for t in (q, k, v, g))
+    out, ws, has = ops.causal_fwd_saved(qh, kh, vh)
+    gq, gk, gv = ops.causal_bwd_saved(qh, kh, vh, gh, out, ws, has)
+    gq2, gk2, gv2 = ops.causal_bwd_saved(qh, kh, vh, gh, out, ws, has)          # the kept workspace survives a backward
+    torch.cuda.synchronize()
+    heads = slice(0, min(BH, 6))
+    ro = O.causal_forward(q[:, heads], k[:, heads], v[:, heads])
+    rq, rk, rv = O.causal_backward(q[:, heads], k[:, heads], v[:, heads], g[:, heads])
+    assert_close(out[:, heads], ro, "out"); assert_close(gq[:, heads], rq, "gq")
+    assert_close(gk[:, heads], rk, "gk"); assert_close(gv[:, heads], rv, "gv")
+    assert torch.equal(gq, gq2) and torch.equal(gk, gk2) and torch.equal(gv, gv2)
+    rec = ops.causal_bwd(qh, kh, vh, gh)                                           # the recomputing backward agrees
+    for name, a, b in zip(("gq", "gk", "gv"), (gq, gk, gv), rec):
+        assert_close(a, b.float().cpu(), f"{name} vs recomputing backward", rel=1e-3)
+
+
+def test_causal_saved_output_backward_with_carries(dev):
+    """Saved-output backward of the second part of a split sequence: state carried in, reverse-state total out."""
+    from rfa_b200 import ops
+    T, BH, cut = 1500, 2, 1100
+    q, k, v, g = feats(T, BH, seed=91)
+    rq, rk, rv = O.causal_backward(q, k, v, g)
+    c = lambda t: t.half().to(dev)
+    _, s, z = ops.causal_fwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), return_state=True)
+    out2, ws, has = ops.causal_fwd_saved(c(q[cut:]), c(k[cut:]), c(v[cut:]), s, z)
+    gq2, dpacked = ops.causal_bwd_q_staged(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), out2, s, z, ws, has)
+    gk2, gv2 = ops.causal_bwd_kv(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), None, None, ws)
+    ds, dz = dpacked[:, :128 * 64].reshape(BH, 128, 64).contiguous(), dpacked[:, 128 * 64:].contiguous()
+    gq1, gk1, gv1 = ops.causal_bwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), c(g[:cut]), None, None, ds, dz)
+    assert_close(out2, O.causal_forward(q, k, v)[cut:], "out (second part)")
+    assert_close(torch.cat([gq1, gq2]), rq, "gq"); assert_close(torch.cat([gk1, gk2]), rk, "gk")
+    assert_close(torch.cat([gv1, gv2]), rv, "gv")
+
+
 def test_causal_unclamped_large_denominators(dev):
     """Positive features so that q.z >> 1 everywhere except the first tokens."""
     gen = torch.Generator().manual_seed(4)

@@ -86,3 +86,10 @@ def test_masked_rfa_is_upstreams_quadratic_variant():
     a = torch.einsum("tbhk,sbhk->bhts", pq, pk) * torch.tril(torch.ones(T, T))
     ref = torch.einsum("bhts,sbhd->tbhd", a / a.sum(-1, keepdim=True), v).reshape(T, B, H * 8)
     assert torch.allclose(out, ref, atol=1e-5)
+
+
+def test_cpu_list_parsing_for_numa_binding():
+    from rfa_b200.host_pipeline import _cpulist, gpu_numa_cpus
+    assert _cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert _cpulist("") == []
+    assert gpu_numa_cpus(0, sysfs="/nonexistent") is None       # no GPU / no sysfs entry: nothing to bind to

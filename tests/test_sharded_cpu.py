@@ -14,26 +14,35 @@ from oracle import rfa_oracle as O
 
 
 class OracleKernels:
-    """Same four steps as rfa_b200.sharded._CudaKernels, computed by the oracle in fp64."""
+    """Same steps as rfa_b200.sharded._CudaKernels, computed by the oracle in fp64 (it keeps nothing between steps)."""
 
     @staticmethod
-    def segment_state(k, v):
-        return O.segment_state(k, v)
+    def local_total(k, v):
+        s, z = O.segment_state(k, v)
+        return torch.cat([s.reshape(s.shape[0], -1), z], dim=1), None
 
     @staticmethod
-    def forward(q, k, v, s_in, z_in):
-        return O.causal_forward(q, k, v, s0=s_in, z0=z_in)
+    def forward(q, k, v, s_in, z_in, fwd_ctx):
+        return O.causal_forward(q, k, v, s0=s_in, z0=z_in), (), None
 
     @staticmethod
-    def backward_q(q, k, v, g, s_in, z_in):
+    def backward_q(q, k, v, g, s_in, z_in, kept, meta):
         gq, _, _, ds, dz = O.causal_backward(q, k, v, g, s0=s_in, z0=z_in, return_dstate=True)
-        return gq, ds, dz, (s_in, z_in)
+        return gq, torch.cat([ds.reshape(ds.shape[0], -1), dz], dim=1), (s_in, z_in)
 
     @staticmethod
     def backward_kv(q, k, v, g, ds_in, dz_in, ctx):
         s_in, z_in = ctx
         _, gk, gv = O.causal_backward(q, k, v, g, s0=s_in, z0=z_in, ds_in=ds_in, dz_in=dz_in)
         return gk, gv
+
+    @staticmethod
+    def forward_alone(q, k, v):
+        return O.causal_forward(q, k, v), (), None
+
+    @staticmethod
+    def backward_alone(q, k, v, g, kept, meta):
+        return O.causal_backward(q, k, v, g)
 
 
 def _free_port():
@@ -110,17 +119,16 @@ def test_shard_bounds_cover_the_sequence():
 
 def test_a_lone_shard_skips_the_exchange():
     """Without a process group (or in a group of one) the whole sequence is local: no shard total is computed, no
-    carry is exchanged, and the result equals the plain oracle.  Kernels without a one-call backward fall back to
-    the two sweeps with empty carries."""
+    carry is exchanged, and the result equals the plain oracle."""
     from rfa_b200 import sharded
 
     calls = []
 
     class Counting(OracleKernels):
         @staticmethod
-        def segment_state(k, v):
-            calls.append("segment_state")
-            return OracleKernels.segment_state(k, v)
+        def local_total(k, v):
+            calls.append("local_total")
+            return OracleKernels.local_total(k, v)
 
     saved = sharded.SequenceShardedRFA.kernels
     sharded.SequenceShardedRFA.kernels = Counting
@@ -137,6 +145,40 @@ def test_a_lone_shard_skips_the_exchange():
         ro = O.causal_forward(q.detach(), k.detach(), v.detach())
         rq, rk, rv = O.causal_backward(q.detach(), k.detach(), v.detach(), g)
         for a, b in ((out.detach(), ro), (q.grad, rq), (k.grad, rk), (v.grad, rv)):
+            assert torch.allclose(a, b, rtol=1e-10, atol=1e-12)
+    finally:
+        sharded.SequenceShardedRFA.kernels = saved
+
+
+def test_in_process_shards_equal_the_unsharded_oracle():
+    """Shards of one sequence run one after another in one process (forward in rank order, backward in reverse)."""
+    from rfa_b200 import sharded
+    saved = sharded.SequenceShardedRFA.kernels
+    sharded.SequenceShardedRFA.kernels = OracleKernels
+    try:
+        gen = torch.Generator().manual_seed(5)
+        T, BH, K, d, world = 40, 2, 16, 8, 3
+        q = torch.rand(T, BH, K, generator=gen, dtype=torch.float64) * 0.4
+        k = torch.rand(T, BH, K, generator=gen, dtype=torch.float64) * 0.4
+        v = torch.randn(T, BH, d, generator=gen, dtype=torch.float64)
+        g = torch.randn(T, BH, d, generator=gen, dtype=torch.float64)
+        group = sharded.InProcessShards(world)
+        bounds = [sharded.shard_bounds(T, world, r, align=8) for r in range(world)]
+        leaves, outs = [], []
+        for r, (lo, hi) in enumerate(bounds):
+            group.rank = r
+            leaves.append(tuple(t[lo:hi].clone().requires_grad_(True) for t in (q, k, v)))
+            outs.append(sharded.sequence_sharded_causal_rfa(*leaves[-1], group))
+        group.rank = 0
+        with pytest.raises(RuntimeError, match="order violated"):       # shard 0 cannot go backward before the later shards
+            outs[0].backward(g[bounds[0][0]:bounds[0][1]], retain_graph=True)
+        for r in reversed(range(world)):
+            group.rank = r
+            outs[r].backward(g[bounds[r][0]:bounds[r][1]])
+        ro = O.causal_forward(q, k, v)
+        want = (ro,) + tuple(O.causal_backward(q, k, v, g))
+        got = (torch.cat([o.detach() for o in outs]),) + tuple(torch.cat([l[i].grad for l in leaves]) for i in range(3))
+        for a, b in zip(got, want):
             assert torch.allclose(a, b, rtol=1e-10, atol=1e-12)
     finally:
         sharded.SequenceShardedRFA.kernels = saved
