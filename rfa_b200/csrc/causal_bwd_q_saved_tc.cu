@@ -11,9 +11,11 @@
 // read at all unless the reverse-state total of the run is wanted (WANT_DSEG: segmented or sharded sequences), and the
 // saved output rows are read straight from global memory into registers one chunk ahead (they feed CUDA cores only).
 //
-// Warp roles (448 threads): warp 0 TMA producer; warp 1 MMA issuer; warps 2..5 scale group (den, gz, gs); warps
-// 10..13 pack group (dA -> masked fp16); warps 6..9 output/state group (grad_q, state export, z).  dA is
-// double-buffered in TMEM.  grad_q leaves through a staged TMA store when the q tiles are not resident
+// Warp roles (448 threads): warp 0 TMA producer; warp 1 MMA issuer; warps 2..5 scale group (den, gz, gs; dzseg);
+// warps 10..13 pack/state group (dA -> masked fp16, then the scan's serial step: z += colsum(K), S -> fp16 operand
+// tile); warps 6..9 output group (grad_q only).  Keeping the state export out of the output group matters: the
+// issuer's next state update waits for the export, the output group waits for the issuer's dQ, and with both in one
+// group the two waits chain into one long cycle per chunk.  dA is double-buffered in TMEM.  grad_q leaves through a staged TMA store when the q tiles are not resident
 // (!WANT_DSEG: their shared memory holds two staging tiles), else straight from registers.  All waits are bounded.
 #include <type_traits>
 
@@ -37,7 +39,7 @@ template <bool WANT_DSEG> struct BsLayout {
 
 // TMEM: two dA buffers (fp32 dA -> fp16 dA packed into their first 64 columns), dQ, S, dSseg
 constexpr uint32_t bsColA = 0, bsColDQ = 256, bsColS = 384, bsColDS = 448;
-enum { sFullK = 0, sFullV = 2, sEmpty = 4, sG = 6, sDA = 8, sDA16 = 10, sDQ = 12, sSt = 14, sDQFree = 16, sS = 17, sY = 18, sNum = 19 };
+enum { sFullK = 0, sFullV = 2, sEmpty = 4, sG = 6, sDA = 8, sDA16 = 10, sDQ = 12, sSt = 14, sDQFree = 16, sS = 17, sY = 18, sZ = 19, sNum = 22 };
 // sFullK guards the K (and Q) tiles of a stage, sFullV its V and g tiles.  Barriers that a waiter may reach late are
 // kept per stage / buffer (index c & 1) so that their producer cannot complete two phases before the waiter looks.
 
@@ -75,7 +77,9 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[sFullK + i], 1);
       mbar_init(&bars[sFullV + i], 1);
-      mbar_init(&bars[sEmpty + i], 129);      // the issuer's commit + the output group's last reads
+      // the issuer's commit + the last reads of the output group (gz), the pack/state group (K) and, with WANT_DSEG,
+      // the scale group (Q)
+      mbar_init(&bars[sEmpty + i], WANT_DSEG ? 385 : 257);
       mbar_init(&bars[sG + i], 128);
       mbar_init(&bars[sDA + i], 1);
       mbar_init(&bars[sDA16 + i], 128);
@@ -83,6 +87,9 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       mbar_init(&bars[sSt + i], 128);         // S tile i holds the state before a chunk c with c & 1 == i
     }
     mbar_init(&bars[sDQFree], 128); mbar_init(&bars[sS], 1); mbar_init(&bars[sY], 128);
+    // z before chunk c is in buffer c % 3, announced on barrier c % 3: three, because the pack/state group can be two
+    // versions ahead of the output group, and a barrier that completes two phases before its waiter looks strands it
+    for (int i = 0; i < 3; ++i) mbar_init(&bars[sZ + i], 128);
     mbar_fence_init();
     tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
     if (WANT_DSEG) tma_prefetch_desc(&tm_q); else tma_prefetch_desc(&tm_gq);
@@ -152,10 +159,9 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
         return true;
       };
       bool ok = nchunk > 0;
-      // The products of chunk c that read the state tile before chunk c (dQ = gs S^T) must be issued before the state
-      // update of chunk c + 1 lets the output group export over ... the OTHER tile; tile c & 1 is next written after the
-      // state update of chunk c + 1 completes, and this thread issues dQ(c) before that update, so program order
-      // (the tensor pipe runs one thread's products in order) keeps the read ahead of the write.
+      // dQ(c) = gs S^T reads the state tile c & 1, which is next overwritten by the export that follows the state update
+      // of chunk c + 1: this thread issues that update after dQ(c), the tensor pipe runs one thread's products in order,
+      // and the export waits for the update's commit, so the read stays ahead of the write.
       if (ok) ok = issue_state(0);
       if (ok) ok = issue_da(0);
 #pragma unroll 1
@@ -167,18 +173,16 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
         umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + bsColDQ, dGk + so, dSk + st * kTile, idKK, 0);     // dQ = gs S_prev^T
         if (WANT_DSEG)                                                                      // dSseg += Q^T gs
           umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + bsColDS, dQm + so, dGm + so, idMM64, c > 0 ? 1u : 0u);
-        // the next chunk's state update and dA go in front of this chunk's last product, so that the pack group is
-        // handed chunk c + 1 as soon as it has finished chunk c
-        if (c + 1 < nchunk) {
-          ok = issue_state(c + 1);
-          if (ok) ok = issue_da(c + 1);
-          if (!ok) break;
-        }
         if (!mbar_wait(&bars[sDA16 + st], (c >> 1) & 1)) { tc_fail(6); break; }
         tc_fence_after_sync();
         umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + bsColDQ, tmem + bsColA + st * 128, dKm + so, idKM128, 1);         // dQ += dA K
         umma_commit(&bars[sDQ + st]);
         umma_commit(&bars[sEmpty + st]);       // every product that reads this stage is complete when this arrives
+        // the next chunk's state update and dA: the pack/state group works on them while the output group drains dQ
+        if (c + 1 < nchunk) {
+          ok = issue_state(c + 1);
+          if (ok) ok = issue_da(c + 1);
+        }
       }
     }
   } else if (warp < 6) {
@@ -187,7 +191,15 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
     const int row = quarter * 32 + lane;           // token row of the chunk
     // this thread's row of the saved output and its raw denominator, fetched one chunk ahead
     uint4 ou[8];
-    float raw = 1.f;
+    float raw = 1.f, dz_acc = 0.f;
+    // (the rows are asked into L2 a chunk earlier still: a load from DRAM takes about as long as a whole chunk)
+    auto ask = [&](int c) {
+      const int64_t t = t_begin + (int64_t)c * kTC + row;
+      if (c < nchunk && t < t_end) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(out_ptr + ((size_t)t * BH + bh) * kD));
+        if ((lane & 7) == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(den_raw + (size_t)bh * T + t));
+      }
+    };
     auto fetch = [&](int c) {
       const int64_t t = t_begin + (int64_t)c * kTC + row;
       if (c < nchunk && t < t_end) {
@@ -202,6 +214,7 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       }
     };
     fetch(0);
+    ask(1);
     for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       unsigned char* grow = sm + st * L::Stage + L::G;
@@ -232,15 +245,58 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       fence_async_smem();
       mbar_arrive(&bars[sG + st]);
       fetch(c + 1);
+      ask(c + 2);
+      if (WANT_DSEG) {                             // dzseg += Q^T gz: needs every row's gz and the staged Q tile
+        if (!mbar_wait(&bars[sG + st], (c >> 1) & 1)) { tc_fail(11); break; }
+        if (!mbar_wait(&bars[sFullK + st], (c >> 1) & 1)) { tc_fail(12); break; }
+        dz_acc += column_sum2(sm + st * L::Stage + L::Q, quarter, lane, rg_buf + st * 128);
+        mbar_arrive(&bars[sEmpty + st]);
+      }
     }
+    if (WANT_DSEG) dz_seg[slot * kK + row] = dz_acc;       // (zero when the run has no tokens)
   } else if (warp >= 10) {
-    // ------------------------------------------------------------------ pack group: dA = mask(gs V^T + gz) -> fp16 over itself
+    // ------------------------------------------------------------------ pack/state group: dA -> masked fp16; z, S export
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
+    const int row = quarter * 32 + lane;           // token row of the chunk (dA) / state row k (S, z)
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    unsigned char* s_tile = sm + L::S;
+    {   // the state entering this run of tokens -> TMEM (fp32) and operand tile 0; z version 0
+      uint32_t r[64];
+#pragma unroll
+      for (int n = 0; n < 64; ++n) r[n] = s_in ? __float_as_uint(s_in[(size_t)row * kD + n]) : 0u;
+      store_state_row(s_tile, row, r);
+      if (s_in) {
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + bsColS + c0, r + c0);
+        tmem_st_wait();
+      }
+      z_buf[row] = z_in ? z_in[row] : 0.f;
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[sSt + 0]);
+      mbar_arrive(&bars[sZ + 0]);
+    }
+    float zrun = z_in ? z_in[row] : 0.f;           // z[row] before the current chunk
     for (int c = 0; c < nchunk; ++c) {
       const int st = c & 1;
       const uint32_t colA = bsColA + st * 128;
+      unsigned char* stage = sm + st * L::Stage;
+      // ---- first the scan's serial step (the issuer's next state update waits for it): the state after this chunk ->
+      //      the other fp16 operand tile.  Its previous reader (dQ = gs S^T of chunk c - 1) was issued before this
+      //      chunk's state update by the same thread, so sS alone orders the overwrite.
+      if (!mbar_wait(&bars[sS], c & 1)) { tc_fail(16); break; }
+      tc_fence_after_sync();
+      if (c + 1 < nchunk) {
+        uint32_t r[64];
+        tmem_ld32(tmem + lane_addr + bsColS, r);
+        tmem_ld32(tmem + lane_addr + bsColS + 32, r + 32);
+        tmem_ld_wait();
+        store_state_row(s_tile + ((c + 1) & 1) * kBox, row, r);
+        fence_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[sSt + ((c + 1) & 1)]);
+      }
+      // ---- dA of this chunk
       if (!mbar_wait(&bars[sG + st], (c >> 1) & 1)) { tc_fail(10); break; }      // gz of this row is in shared memory
       const float gz = rg_buf[st * 128 + row];
       if (!mbar_wait(&bars[sDA + st], (c >> 1) & 1)) { tc_fail(14); break; }
@@ -275,65 +331,37 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[sDA16 + st]);
+      // ---- z before the next chunk = z + colsum(K).  Buffer (c + 1) % 3 last held version c - 2, whose reader (the output
+      //      group's epilogue of chunk c - 2) read it before it released dQ for chunk c - 1, which precedes this chunk's dA.
+      if (!mbar_wait(&bars[sFullK + st], (c >> 1) & 1)) { tc_fail(15); break; }
+      zrun += column_sum2(stage + L::K, quarter, lane, nullptr);
+      mbar_arrive(&bars[sEmpty + st]);             // this group's last read of the stage's tiles
+      z_buf[((c + 1) % 3) * 128 + row] = zrun;
+      mbar_arrive(&bars[sZ + (c + 1) % 3]);
     }
   } else {
-    // ------------------------------------------------------------------ output / state group (warps 6..9)
+    // ------------------------------------------------------------------ output group (warps 6..9): grad_q
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;           // token row of the chunk / state row k
+    const int row = quarter * 32 + lane;           // token row of the chunk
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int ytid = tid - 192;
-    unsigned char* s_tile = sm + L::S;
-    {
-      uint32_t r[64];
-#pragma unroll
-      for (int n = 0; n < 64; ++n) r[n] = s_in ? __float_as_uint(s_in[(size_t)row * kD + n]) : 0u;
-      store_state_row(s_tile, row, r);
-      if (s_in) {
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + bsColS + c0, r + c0);
-        tmem_st_wait();
-      }
-      z_buf[row] = z_in ? z_in[row] : 0.f;
-      fence_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[sSt + 0]);
-    }
     bool ok = true;
-    float dz_acc = 0.f;
     uint32_t y_phase = 0;
     for (int c = 0; ok && c < nchunk; ++c) {
       const int st = c & 1;
-      unsigned char* stage = sm + st * L::Stage;
       const int64_t t0 = t_begin + (int64_t)c * kTC;
       const float* zs = z_buf + (c % 3) * 128;
-      const float* gzs = rg_buf + st * 128;
-      // ---- z before the next chunk = z + colsum(K): needs only the staged K tile.  Buffer (c + 1) % 3 was last read in
-      //      the epilogue of chunk c - 2, which every thread of the group left before the group barrier of chunk c - 1.
-      if (!mbar_wait(&bars[sFullK + st], (c >> 1) & 1)) { tc_fail(15); ok = false; break; }
-      z_buf[((c + 1) % 3) * 128 + row] = zs[row] + column_sum2(stage + L::K, quarter, lane, nullptr);
-      // ---- the state after this chunk -> the other fp16 operand tile.  Its previous readers (the product of chunk
-      //      c - 1 that read the state before chunk c - 1) were issued before this chunk's state update by the same
-      //      thread, so sS alone orders the overwrite.
-      if (!mbar_wait(&bars[sS], c & 1)) { tc_fail(16); ok = false; break; }
-      tc_fence_after_sync();
-      if (c + 1 < nchunk) {
-        uint32_t r[64];
-        tmem_ld32(tmem + lane_addr + bsColS, r);
-        tmem_ld32(tmem + lane_addr + bsColS + 32, r + 32);
-        tmem_ld_wait();
-        store_state_row(s_tile + ((c + 1) & 1) * kBox, row, r);
-        fence_async_smem();
-        tc_fence_before_sync();
-        mbar_arrive(&bars[sSt + ((c + 1) & 1)]);
-      }
-      // ---- gz of every row of this chunk is in shared memory once sG completed
+      // ---- gz of this row (shared memory, complete once sG completed); the buffer is rewritten two chunks on, after
+      //      the stage has been released
       if (!mbar_wait(&bars[sG + st], (c >> 1) & 1)) { tc_fail(17); ok = false; break; }
-      if (WANT_DSEG) dz_acc += column_sum2(stage + L::Q, quarter, lane, gzs);      // dzseg += Q^T gz
-      const float gz = gzs[row];
-      mbar_arrive(&bars[sEmpty + st]);             // this group's last read of the stage's tiles
-      // ---- group barrier: z of this chunk is visible to every thread; the staging tile of chunk c - 2 has been read out
-      if (!WANT_DSEG && ytid == 0 && c >= 2) tma_store_wait_read<1>();
-      if (!epi_sync(&bars[sY], y_phase)) { tc_fail(12); ok = false; break; }
+      const float gz = rg_buf[st * 128 + row];
+      mbar_arrive(&bars[sEmpty + st]);
+      if (!mbar_wait(&bars[sZ + c % 3], (c / 3) & 1)) { tc_fail(19); ok = false; break; }
+      // ---- !WANT_DSEG: the staging tile of chunk c - 2 has been read out by its store
+      if (!WANT_DSEG) {
+        if (ytid == 0 && c >= 2) tma_store_wait_read<1>();
+        if (!epi_sync(&bars[sY], y_phase)) { tc_fail(12); ok = false; break; }
+      }
       // ---- grad_q = dQ + gz z_prev^T -> fp16
       if (!mbar_wait(&bars[sDQ + st], (c >> 1) & 1)) { tc_fail(18); ok = false; break; }
       tc_fence_after_sync();
@@ -343,16 +371,20 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t a[32];
+        float4 zv[8];
         tmem_ld32(tmem + lane_addr + bsColDQ + piece * 32, a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) zv[j] = *reinterpret_cast<const float4*>(zs + piece * 32 + j * 4);
         tmem_ld_wait();
-        if (piece == 3) { tc_fence_before_sync(); mbar_arrive(&bars[sDQFree]); }   // dQ is in registers: the next chunk may overwrite it
+        // dQ and this chunk's z are in registers: the next chunk may overwrite dQ (and, later, the z buffer)
+        if (piece == 3) { tc_fence_before_sync(); mbar_arrive(&bars[sDQFree]); }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           uint32_t o[8];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int k0 = piece * 32 + j * 16 + e * 8, a0 = j * 16 + e * 8;
-            const float4 z0 = *reinterpret_cast<const float4*>(zs + k0), z1 = *reinterpret_cast<const float4*>(zs + k0 + 4);
+            const int a0 = j * 16 + e * 8;
+            const float4 z0 = zv[a0 / 4], z1 = zv[a0 / 4 + 1];
             o[e * 4 + 0] = pack_half2(fmaf(gz, z0.x, __uint_as_float(a[a0 + 0])), fmaf(gz, z0.y, __uint_as_float(a[a0 + 1])));
             o[e * 4 + 1] = pack_half2(fmaf(gz, z0.z, __uint_as_float(a[a0 + 2])), fmaf(gz, z0.w, __uint_as_float(a[a0 + 3])));
             o[e * 4 + 2] = pack_half2(fmaf(gz, z1.x, __uint_as_float(a[a0 + 4])), fmaf(gz, z1.y, __uint_as_float(a[a0 + 5])));
@@ -392,7 +424,6 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       for (int n = 0; n < 16; ++n)
         dst[n] = make_float4(__uint_as_float(r[4 * n]), __uint_as_float(r[4 * n + 1]), __uint_as_float(r[4 * n + 2]),
                              __uint_as_float(r[4 * n + 3]));
-      dz_seg[slot * kK + row] = dz_acc;
     }
     if (!WANT_DSEG && ytid == 0) tma_store_wait<0>();
   }
