@@ -10,13 +10,16 @@
 // The score matrices are computed TRANSPOSED (keys on the TMEM lanes) so that their fp16
 // versions can stay in tensor memory as the A operands of the dK / dV products.
 //
-// Warp roles (480 threads): warp 0 TMA producer, warps 1 and 10 MMA issuers, warps 2..5 score
-// group 1 (packs Pt), warps 11..14 score group 2 (scales g in place, packs dAt), warps 6..9
-// output/state group (grad_k, grad_v, state export, dz).  Issuing one tcgen05.mma costs the issuing thread about as long as the
-// tensor pipe needs to execute it (N <= 128), so the 48 MMAs of a chunk are split over two
-// issuers: A (At, dAt, dK) and B (dV, dS).  The products that read the exported state tile are
-// issued first in a chunk and the state update right after g is scaled, which keeps the serial
-// chain of the scan (state MMA -> export -> next chunk's readers) short.  All waits are bounded.
+// Warp roles (480 threads): warp 0 TMA producer, warps 1 and 10 MMA issuers, warps 2..5 score/state group (packs Pt,
+// then the scan's serial step: exports the reverse state, dz += Q^T gz), warps 11..14 score group 2 (scales g in
+// place, packs dAt), warps 6..9 output group (grad_v, grad_k straight from registers).  Issuing one tcgen05.mma costs
+// the issuing thread about as long as the tensor pipe needs to execute it (N <= 128), so the 48 MMAs of a chunk are
+// split over two issuers: A (At, dAt, dK) and B (dV, dS).  The products that read the exported state tile are issued
+// first in a chunk and the state update right after g is scaled, which keeps the serial chain of the scan (state MMA
+// -> export -> next chunk's readers) short.  The gradients leave through plain 32-byte global stores: a stage is then
+// free for its next load as soon as the chunk's products are complete, instead of serving as the staging area of a
+// TMA store first (a load under full memory traffic takes about 3 us here, as long as a whole chunk, so what delays
+// its issue delays the chunk).  All waits are bounded.
 #include <type_traits>
 
 #define RFA_TC_FAMILY 3
@@ -28,25 +31,24 @@ constexpr int kKvThreads = 480;
 
 constexpr uint32_t kvQ = 0, kvK = 2 * kBox, kvV = 4 * kBox, kvG = 5 * kBox, kvStage = 6 * kBox;   // 98304 per stage
 constexpr uint32_t kvS = 2 * kvStage;            // dS as an operand: [128 k][64 n] fp16, swizzled
-constexpr uint32_t kvDz = kvS + kBox;            // fp32 [2][128]: dz entering chunk i lives in buffer i & 1
-constexpr uint32_t kvGz = kvDz + 1024;           // fp32 [2][128]: gz of the chunk's query rows
+constexpr uint32_t kvDz = kvS + kBox;            // fp32 [3][128]: dz entering chunk i lives in buffer i % 3
+constexpr uint32_t kvGz = kvDz + 1536;           // fp32 [2][128]: gz of the chunk's query rows
 constexpr uint32_t kvBar = kvGz + 1024;
 constexpr uint32_t kvSmem = kvBar + 256 + 1024;
 
 constexpr uint32_t kvColAt = 0, kvColDAt = 128, kvColDK = 256, kvColDV = 384, kvColDS = 448;
-enum { vFull = 0, vEmpty = 2, vAt = 4, vG = 5, vDAt = 7, vP = 8, vDA16 = 9, vDK = 10, vDV = 11, vDKFree = 12, vDVFree = 13,
-       vS = 14, vSt = 15, vY = 16, vSR = 17, vStaged = 18, vNum = 20 };
+enum { vFullKQ = 0, vFullVG = 2, vEmpty = 4, vAt = 6, vG = 7, vDAt = 9, vP = 10, vDA16 = 11, vDK = 12, vDV = 13, vDKFree = 14,
+       vDVFree = 15, vS = 16, vSt = 17, vSR = 18, vDz = 19, vNum = 22 };
+// vFullKQ / vFullVG: the K, Q tiles and the V, g tiles of a stage have landed (requested in the order g, V, K, Q).
 // vSR: both issuers have finished reading the exported state tile (one commit each per chunk).
-// vEmpty: the Q and g tiles of a stage may be refilled (every product of the chunk is complete, dz has been summed);
-// vStaged: grad_k / grad_v are staged in its K and V tiles -- the producer thread stores them and refills those two
-// once the store has read them, so the output group never waits for a store.
-// vG is one barrier per stage: the output group waits on it late in a chunk, when the score group may already
-// have completed the next chunk's phase; with one barrier per stage a waiter is never two phases behind.
+// vEmpty: a stage may be refilled: both issuers' last products of the chunk are complete and dz has been summed over Q.
+// vG is one barrier per stage and vDz one per buffer (i % 3): their waiters may reach them late, when the producer
+// could already have completed the same barrier's next phase; kept apart, a waiter is never two phases behind.
 
 __global__ void __launch_bounds__(kKvThreads, 1)
 causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_g,
-                        const __grid_constant__ CUtensorMap tm_gk, const __grid_constant__ CUtensorMap tm_gv,
+                        __half* __restrict__ gk_ptr, __half* __restrict__ gv_ptr,
                         const float* __restrict__ ws_den, const float* __restrict__ ws_gz,
                         const float* __restrict__ ds_seg, const float* __restrict__ dz_seg,
                         int64_t T, int BH, int nseg, int64_t tseg) {
@@ -66,16 +68,18 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const float* dz_in = dz_seg ? dz_seg + slot * kK : nullptr;
 
   if (tid == 0) {
-    mbar_init(&bars[vFull], 2); mbar_init(&bars[vFull + 1], 2);      // two requests per use: (g, Q) and (K, V)
-    mbar_init(&bars[vStaged], 128); mbar_init(&bars[vStaged + 1], 128);
-    mbar_init(&bars[vEmpty], 128); mbar_init(&bars[vEmpty + 1], 128);
-    mbar_init(&bars[vAt], 1); mbar_init(&bars[vG], 128); mbar_init(&bars[vG + 1], 128); mbar_init(&bars[vDAt], 1); mbar_init(&bars[vP], 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[vFullKQ + i], 1); mbar_init(&bars[vFullVG + i], 1);
+      mbar_init(&bars[vEmpty + i], 130);     // one commit from each issuer + the score/state group's column sums over Q
+      mbar_init(&bars[vG + i], 128);
+    }
+    mbar_init(&bars[vAt], 1); mbar_init(&bars[vDAt], 1); mbar_init(&bars[vP], 128);
     mbar_init(&bars[vDA16], 128); mbar_init(&bars[vDK], 1); mbar_init(&bars[vDV], 1);
     mbar_init(&bars[vDKFree], 128); mbar_init(&bars[vDVFree], 128); mbar_init(&bars[vS], 1);
-    mbar_init(&bars[vSt], 128); mbar_init(&bars[vY], 128); mbar_init(&bars[vSR], 2);
+    mbar_init(&bars[vSt], 128); mbar_init(&bars[vSR], 2);
+    for (int i = 0; i < 3; ++i) mbar_init(&bars[vDz + i], 128);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_g);
-    tma_prefetch_desc(&tm_gk); tma_prefetch_desc(&tm_gv);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -85,43 +89,23 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
-    // It also issues the stores of the staged gradients, and refills a stage in two halves: g and Q as soon as the
-    // chunk two earlier has no further use for them, K and V once its staged gradients have been read out.
     if (lane == 0) {
-      auto chunk_t0 = [&](int j) { return (int)(t_begin + (int64_t)(nchunk - 1 - j) * kTC); };
-      auto store_chunk = [&](int j) {
-        unsigned char* base = sm + (j & 1) * kvStage;
-        tma_store_3d(&tm_gk, base + kvK, 0, bh, chunk_t0(j));
-        tma_store_3d(&tm_gk, base + kvK + kBox, 64, bh, chunk_t0(j));
-        tma_store_3d(&tm_gv, base + kvV, 0, bh, chunk_t0(j));
-        tma_store_commit();
-      };
-      bool ok = true;
       for (int i = 0; i < nchunk; ++i) {
         const int st = i & 1;
         unsigned char* base = sm + st * kvStage;
-        const int t0 = chunk_t0(i);
-        uint64_t* fb = &bars[vFull + st];
-        if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); ok = false; break; }
-        mbar_arrive_expect_tx(fb, 3 * kBox);
-        tma_load_3d(base + kvG, &tm_g, fb, 0, bh, t0);
-        tma_load_3d(base + kvQ, &tm_q, fb, 0, bh, t0);
-        tma_load_3d(base + kvQ + kBox, &tm_q, fb, 64, bh, t0);
-        if (i >= 2) {
-          if (!mbar_wait(&bars[vStaged + st], ((i >> 1) + 1) & 1)) { tc_fail(25); ok = false; break; }
-          store_chunk(i - 2);
-          tma_store_wait_read<0>();                  // the K and V tiles have been read out
-        }
-        mbar_arrive_expect_tx(fb, 3 * kBox);
-        tma_load_3d(base + kvK, &tm_k, fb, 0, bh, t0);
-        tma_load_3d(base + kvK + kBox, &tm_k, fb, 64, bh, t0);
-        tma_load_3d(base + kvV, &tm_v, fb, 0, bh, t0);
+        const int t0 = (int)(t_begin + (int64_t)(nchunk - 1 - i) * kTC);
+        if (i >= 2 && !mbar_wait(&bars[vEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
+        uint64_t* fv = &bars[vFullVG + st];
+        uint64_t* fk = &bars[vFullKQ + st];
+        mbar_arrive_expect_tx(fv, 2 * kBox);           // g first: the longer of the chunk's two chains starts with its scaling
+        tma_load_3d(base + kvG, &tm_g, fv, 0, bh, t0);
+        tma_load_3d(base + kvV, &tm_v, fv, 0, bh, t0);
+        mbar_arrive_expect_tx(fk, 4 * kBox);
+        tma_load_3d(base + kvK, &tm_k, fk, 0, bh, t0);
+        tma_load_3d(base + kvK + kBox, &tm_k, fk, 64, bh, t0);
+        tma_load_3d(base + kvQ, &tm_q, fk, 0, bh, t0);
+        tma_load_3d(base + kvQ + kBox, &tm_q, fk, 64, bh, t0);
       }
-      for (int j = (nchunk >= 2 ? nchunk - 2 : 0); ok && j < nchunk; ++j) {
-        if (!mbar_wait(&bars[vStaged + (j & 1)], (j >> 1) & 1)) { tc_fail(26); break; }
-        store_chunk(j);
-      }
-      tma_store_wait<0>();
     }
   } else if (warp == 1 || warp == 10) {
     // ------------------------------------------------------------------ MMA issuers
@@ -149,7 +133,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         };
         bool ok = true;
         if (nchunk > 0) {
-          ok = mbar_wait(&bars[vFull], 0);
+          ok = mbar_wait(&bars[vFullKQ], 0);
           if (ok) { tc_fence_after_sync(); issue_At(0); } else tc_fail(2);
         }
 #pragma unroll 1
@@ -157,19 +141,22 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           const int st = i & 1;
           const uint64_t so = (uint64_t)st * dStage;
           const uint32_t ph = i & 1;
-          // dK = V dS_next^T first: it reads the state tile, which the output group wants to overwrite
+          // dAt = V gs^T first: it heads the chunk's longest chain (dAt -> pack -> dK += dAt Q)
+          if (!mbar_wait(&bars[vFullVG + st], (i >> 1) & 1)) { tc_fail(9); break; }
+          if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(5); break; }
+          tc_fence_after_sync();
+          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDAt, dVk + so, dGk + so, idKK, 0);          // dAt = V gs^T
+          umma_commit(&bars[vDAt]);
+          // dK = V dS_next^T: it reads the state tile, which the score/state group overwrites once both issuers are done
+          // with it, and it needs the output group to have drained the previous chunk's dK
           if (!mbar_wait(&bars[vSt], ph)) { tc_fail(3); break; }
           if (i > 0 && !mbar_wait(&bars[vDKFree], (i - 1) & 1)) { tc_fail(4); break; }
           tc_fence_after_sync();
           umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDK, dVk + so, dSk, idKK, 0);
           umma_commit(&bars[vSR]);
-          if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(5); break; }
-          tc_fence_after_sync();
-          umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + kvColDAt, dVk + so, dGk + so, idKK, 0);          // dAt = V gs^T
-          umma_commit(&bars[vDAt]);
           // the next chunk's scores as soon as its tiles are in and Pt of this chunk has been consumed (dV complete)
           bool next_issued = (i + 1 >= nchunk);
-          if (!next_issued && mbar_test(&bars[vFull + (st ^ 1)], ((i + 1) >> 1) & 1) && mbar_test(&bars[vDV], ph)) {
+          if (!next_issued && mbar_test(&bars[vFullKQ + (st ^ 1)], ((i + 1) >> 1) & 1) && mbar_test(&bars[vDV], ph)) {
             tc_fence_after_sync();
             issue_At(st ^ 1);
             next_issued = true;
@@ -178,8 +165,9 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           tc_fence_after_sync();
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + kvColDK, tmem + kvColDAt, dQm + so, idKM128, 1);                // dK += dAt Q
           umma_commit(&bars[vDK]);
+          umma_commit(&bars[vEmpty + st]);           // this issuer's last product that reads the stage
           if (!next_issued) {
-            if (!mbar_wait(&bars[vFull + (st ^ 1)], ((i + 1) >> 1) & 1)) { tc_fail(7); break; }
+            if (!mbar_wait(&bars[vFullKQ + (st ^ 1)], ((i + 1) >> 1) & 1)) { tc_fail(7); break; }
             if (!mbar_wait(&bars[vDV], ph)) { tc_fail(8); break; }
             tc_fence_after_sync();
             issue_At(st ^ 1);
@@ -192,7 +180,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           const int st = i & 1;
           const uint64_t so = (uint64_t)st * dStage;
           const uint32_t ph = i & 1;
-          if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(20); break; }
+          if (!mbar_wait(&bars[vFullKQ + st], (i >> 1) & 1)) { tc_fail(20); break; }
           if (!mbar_wait(&bars[vSt], ph)) { tc_fail(21); break; }
           if (i > 0 && !mbar_wait(&bars[vDVFree], (i - 1) & 1)) { tc_fail(22); break; }
           tc_fence_after_sync();
@@ -207,13 +195,34 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           tc_fence_after_sync();
           umma_chain_ts<8, kStepMN, kBlockMN>(lead, tmem + kvColDV, tmem + kvColAt, dGm + so, idKM64, 1);                  // dV += Pt gs
           umma_commit(&bars[vDV]);
+          umma_commit(&bars[vEmpty + st]);           // this issuer's last product that reads the stage
         }
       }
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------------ score group 1: Pt[s][t] = At[s][t] for t >= s
+    // ------------------------------------------------------------------ score/state group: Pt[s][t] = At[s][t] for t >= s;
+    //                                                                     reverse state export; dz += Q^T gz
     const int quarter = warp & 3;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;   // key row s = quarter * 32 + lane
+    const int row = quarter * 32 + lane;           // key row s of the chunk / state row k
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    unsigned char* s_tile = sm + kvS;
+    {   // the reverse state entering this run of tokens -> TMEM (fp32) and the operand tile; dz version 0
+      uint32_t r[64];
+#pragma unroll
+      for (int n = 0; n < 64; ++n) r[n] = ds_in ? __float_as_uint(ds_in[(size_t)row * kD + n]) : 0u;
+      store_state_row(s_tile, row, r);
+      if (ds_in) {
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + kvColDS + c0, r + c0);
+        tmem_st_wait();
+      }
+      dzs[row] = dz_in ? dz_in[row] : 0.f;
+      fence_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars[vSt]);
+      mbar_arrive(&bars[vDz + 0]);
+    }
+    float dz_run = dz_in ? dz_in[row] : 0.f;       // dz[row] entering the current chunk
     for (int i = 0; i < nchunk; ++i) {
       const uint32_t ph = i & 1;
       if (!mbar_wait(&bars[vAt], ph)) { tc_fail(11); break; }
@@ -248,25 +257,60 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[vP]);
+      // ---- the state update is complete and both issuers have finished reading the old state tile: reverse state
+      //      after this chunk -> fp16 operand tile (the serial chain of the scan)
+      const int st = i & 1;
+      if (!mbar_wait(&bars[vS], ph)) { tc_fail(15); break; }
+      if (!mbar_wait(&bars[vSR], ph)) { tc_fail(18); break; }
+      tc_fence_after_sync();
+      if (i + 1 < nchunk) {
+        uint32_t r[64];
+        tmem_ld32(tmem + lane_addr + kvColDS, r);
+        tmem_ld32(tmem + lane_addr + kvColDS + 32, r + 32);
+        tmem_ld_wait();
+        store_state_row(s_tile, row, r);
+        fence_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[vSt]);
+      }
+      // ---- dz entering the next chunk = dz + Q^T gz (gz of every row is there once vG completed; the state update
+      //      waited on it).  Buffer (i + 1) % 3 last held version i - 2, which the output group read in its iteration
+      //      i - 2, before it released dV of chunk i - 1, which precedes this chunk's state update.
+      if (!mbar_wait(&bars[vFullKQ + st], (i >> 1) & 1)) { tc_fail(16); break; }
+      if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); break; }
+      dz_run += column_sum2(sm + st * kvStage + kvQ, quarter, lane, gz_buf + st * 128);
+      mbar_arrive(&bars[vEmpty + st]);             // this group's last read of the stage's tiles
+      dzs[((i + 1) % 3) * 128 + row] = dz_run;
+      mbar_arrive(&bars[vDz + (i + 1) % 3]);
     }
   } else if (warp >= 11) {
     // ------------------------------------------------------------------ score group 2: gs = g / den, then dAt
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // query row t (scaling g) / key row s (packing)
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    // this thread's two per-token scalars from sweep 1, fetched one chunk ahead: a load from global memory takes about
+    // as long as half a chunk under full traffic, and the scaling of g heads the chunk's longest chain
+    float den_next = 1.f, gz_next = 0.f;
+    auto fetch = [&](int i) {
+      const int64_t t = t_begin + (int64_t)(nchunk - 1 - i) * kTC + row;
+      if (i < nchunk && t < t_end) {
+        den_next = __ldg(ws_den + (size_t)bh * T + t);
+        gz_next = __ldg(ws_gz + (size_t)bh * T + t);
+      } else {
+        den_next = 1.f;
+        gz_next = 0.f;
+      }
+    };
+    fetch(0);
     for (int i = 0; i < nchunk; ++i) {
       const int st = i & 1;
       const uint32_t ph = i & 1;
       unsigned char* stage = sm + st * kvStage;
-      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
       float* gzs = gz_buf + (i & 1) * 128;
       // ---- gs = g / den over the staged g tile; gz of this thread's query row
-      float inv = 1.f, gz = 0.f;
-      if (t0 + row < t_end) {
-        inv = 1.f / fmaxf(ws_den[(size_t)bh * T + t0 + row], kEps);   // raw or already clamped
-        gz = ws_gz[(size_t)bh * T + t0 + row];
-      }
-      if (!mbar_wait(&bars[vFull + st], (i >> 1) & 1)) { tc_fail(10); break; }
+      const float inv = 1.f / fmaxf(den_next, kEps);       // raw or already clamped denominators
+      const float gz = gz_next;
+      if (!mbar_wait(&bars[vFullVG + st], (i >> 1) & 1)) { tc_fail(10); break; }
       {
         unsigned char* grow = stage + kvG;
         // all eight loads of the row first (independent), then the scaling, then the stores
@@ -286,6 +330,7 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       fence_async_smem();
       mbar_arrive(&bars[vG + st]);
+      fetch(i + 1);
       // ---- dAt[s][t] = (v_s . gs_t + gz_t) for t >= s; gz of all rows is there once vG completed
       if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(12); break; }
       if (!mbar_wait(&bars[vDAt], ph)) { tc_fail(13); break; }
@@ -326,92 +371,64 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       mbar_arrive(&bars[vDA16]);
     }
   } else if (warp < 10) {
-    // ------------------------------------------------------------------ output / state group
+    // ------------------------------------------------------------------ output group: grad_v, grad_k
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;           // key row s of the chunk / state row k
+    const int row = quarter * 32 + lane;           // key row s of the chunk
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int ytid = tid - 192;
-    unsigned char* s_tile = sm + kvS;
-    {
-      uint32_t r[64];
-#pragma unroll
-      for (int n = 0; n < 64; ++n) r[n] = ds_in ? __float_as_uint(ds_in[(size_t)row * kD + n]) : 0u;
-      store_state_row(s_tile, row, r);
-      if (ds_in) {
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) tmem_st16(tmem + lane_addr + kvColDS + c0, r + c0);
-        tmem_st_wait();
-      }
-      dzs[row] = dz_in ? dz_in[row] : 0.f;
-      fence_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[vSt]);
-    }
-    bool ok = true;
-    uint32_t y_phase = 0;
-    for (int i = 0; ok && i < nchunk; ++i) {
-      const int st = i & 1;
+    for (int i = 0; i < nchunk; ++i) {
       const uint32_t ph = i & 1;
-      unsigned char* stage = sm + st * kvStage;
-      const float* gzs = gz_buf + (i & 1) * 128;
-      const float* dz_cur = dzs + (i & 1) * 128;
-      // every thread has written its dz entering this chunk and finished the previous chunk's reads of the other buffer
-      if (!epi_sync(&bars[vY], y_phase)) { tc_fail(14); ok = false; break; }
-      // ---- the state update is complete and both issuers have finished reading the old state tile
-      if (!mbar_wait(&bars[vS], ph)) { tc_fail(15); ok = false; break; }
-      if (!mbar_wait(&bars[vSR], ph)) { tc_fail(18); ok = false; break; }
-      tc_fence_after_sync();
-      // ---- reverse state after this chunk -> fp16 operand tile (the serial chain of the scan)
-      if (i + 1 < nchunk) {
-        uint32_t r[64];
-        tmem_ld32(tmem + lane_addr + kvColDS, r);
-        tmem_ld32(tmem + lane_addr + kvColDS + 32, r + 32);
-        tmem_ld_wait();
-        store_state_row(s_tile, row, r);
-        fence_async_smem();
-        tc_fence_before_sync();
-        mbar_arrive(&bars[vSt]);
-      }
-      // ---- dz += Q^T gz while the chunk's other products are in flight (the state MMA waited on vG, so gz is there);
-      //      the new dz goes to the other buffer
-      if (!mbar_wait(&bars[vG + st], (i >> 1) & 1)) { tc_fail(17); ok = false; break; }
-      dzs[((i + 1) & 1) * 128 + row] = dz_cur[row] + column_sum2(stage + kvQ, quarter, lane, gzs);
+      const int64_t t0 = t_begin + (int64_t)(nchunk - 1 - i) * kTC;
+      const bool live = t0 + row < t_end;
+      const float* dz_cur = dzs + (i % 3) * 128;
       // ---- grad_v: issuer B's last product of the chunk
-      uint32_t r[64];
-      if (!mbar_wait(&bars[vDV], ph)) { tc_fail(13); ok = false; break; }
+      {
+        uint32_t r[64];
+        if (!mbar_wait(&bars[vDV], ph)) { tc_fail(13); break; }
+        tc_fence_after_sync();
+        tmem_ld32(tmem + lane_addr + kvColDV, r);
+        tmem_ld32(tmem + lane_addr + kvColDV + 32, r + 32);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[vDVFree]);
+        __half* vrow = gv_ptr + ((size_t)(t0 + row) * BH + bh) * kD;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {              // 32 bytes (one sector) per store
+          uint32_t o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = pack_half2(__uint_as_float(r[j * 16 + 2 * e]), __uint_as_float(r[j * 16 + 2 * e + 1]));
+          if (live) st_global_v8(vrow + j * 16, o);
+        }
+      }
+      // ---- grad_k = dK + dz (dz entering this chunk): issuer A's last product
+      if (!mbar_wait(&bars[vDz + i % 3], (i / 3) & 1)) { tc_fail(14); break; }
+      if (!mbar_wait(&bars[vDK], ph)) { tc_fail(19); break; }
       tc_fence_after_sync();
-      tmem_ld32(tmem + lane_addr + kvColDV, r);
-      tmem_ld32(tmem + lane_addr + kvColDV + 32, r + 32);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&bars[vDVFree]);
-      // issuer A's last product is complete as well: no product reads the stage any more.  Its Q and g tiles can be
-      // refilled; V and K become staging.
-      if (!mbar_wait(&bars[vDK], ph)) { tc_fail(19); ok = false; break; }
-      tc_fence_after_sync();
-      mbar_arrive(&bars[vEmpty + st]);
-      store_state_row(stage + kvV, row, r);
-      // ---- grad_k = dK + dz_next -> K tile
+      __half* krow = gk_ptr + ((size_t)(t0 + row) * BH + bh) * kK;
 #pragma unroll 1
       for (int piece = 0; piece < 4; ++piece) {
         uint32_t a[32];
+        float4 zv[8];
         tmem_ld32(tmem + lane_addr + kvColDK + piece * 32, a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) zv[j] = *reinterpret_cast<const float4*>(dz_cur + piece * 32 + j * 4);
         tmem_ld_wait();
+        // dK and this chunk's dz are in registers: the next chunk may overwrite dK (and, later, the dz buffer)
         if (piece == 3) { tc_fence_before_sync(); mbar_arrive(&bars[vDKFree]); }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int k0 = piece * 32 + j * 8;
-          const float4 z0 = *reinterpret_cast<const float4*>(dz_cur + k0), z1 = *reinterpret_cast<const float4*>(dz_cur + k0 + 4);
-          uint4 u;
-          u.x = pack_half2(__uint_as_float(a[j * 8 + 0]) + z0.x, __uint_as_float(a[j * 8 + 1]) + z0.y);
-          u.y = pack_half2(__uint_as_float(a[j * 8 + 2]) + z0.z, __uint_as_float(a[j * 8 + 3]) + z0.w);
-          u.z = pack_half2(__uint_as_float(a[j * 8 + 4]) + z1.x, __uint_as_float(a[j * 8 + 5]) + z1.y);
-          u.w = pack_half2(__uint_as_float(a[j * 8 + 6]) + z1.z, __uint_as_float(a[j * 8 + 7]) + z1.w);
-          *reinterpret_cast<uint4*>(stage + kvK + row_chunk2(row, piece * 4 + j)) = u;
+        for (int j = 0; j < 2; ++j) {
+          uint32_t o[8];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int a0 = j * 16 + e * 8;
+            const float4 z0 = zv[a0 / 4], z1 = zv[a0 / 4 + 1];
+            o[e * 4 + 0] = pack_half2(__uint_as_float(a[a0 + 0]) + z0.x, __uint_as_float(a[a0 + 1]) + z0.y);
+            o[e * 4 + 1] = pack_half2(__uint_as_float(a[a0 + 2]) + z0.z, __uint_as_float(a[a0 + 3]) + z0.w);
+            o[e * 4 + 2] = pack_half2(__uint_as_float(a[a0 + 4]) + z1.x, __uint_as_float(a[a0 + 5]) + z1.y);
+            o[e * 4 + 3] = pack_half2(__uint_as_float(a[a0 + 6]) + z1.z, __uint_as_float(a[a0 + 7]) + z1.w);
+          }
+          if (live) st_global_v8(krow + piece * 32 + j * 16, o);
         }
       }
-      fence_async_smem();
-      mbar_arrive(&bars[vStaged + st]);            // the producer thread stores the two tiles and refills them
     }
   }
   tc_fence_before_sync();
@@ -422,14 +439,13 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, const __half* g, __half* gk, __half* gv,
                             const float* ws_den, const float* ws_gz, const float* ds_seg, const float* dz_seg,
                             int64_t T, int BH, int nseg, int64_t tseg, cudaStream_t st) {
-  CUtensorMap tq, tk, tv, tg, tgk, tgv;
+  CUtensorMap tq, tk, tv, tg;
   if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tk, k, T, BH, kK, kTC) ||
-      make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&tg, g, T, BH, kD, kTC) ||
-      make_tmap_rows(&tgk, gk, T, BH, kK, kTC) || make_tmap_rows(&tgv, gv, T, BH, kD, kTC))
+      make_tmap_rows(&tv, v, T, BH, kD, kTC) || make_tmap_rows(&tg, g, T, BH, kD, kTC))
     return fail(RFA_EDEVICE, "causal_bwd_kv: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(causal_bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kvSmem);
   if (e != cudaSuccess) return fail((int)e, "causal_bwd_kv: cannot reserve %u bytes of shared memory: %s", kvSmem, cudaGetErrorString(e));
-  causal_bwd_kv_tc_kernel<<<dim3(BH, nseg), kKvThreads, kvSmem, st>>>(tq, tk, tv, tg, tgk, tgv, ws_den, ws_gz, ds_seg, dz_seg,
+  causal_bwd_kv_tc_kernel<<<dim3(BH, nseg), kKvThreads, kvSmem, st>>>(tq, tk, tv, tg, gk, gv, ws_den, ws_gz, ds_seg, dz_seg,
                                                                      T, BH, nseg, tseg);
   return check_launch("rfa_causal_bwd_kv");
 }

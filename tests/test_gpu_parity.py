@@ -187,7 +187,8 @@ def test_host_pipeline_matches_direct_calls(dev):
     torch.cuda.synchronize()
     for hin, hout in steps:
         dq, dk, dv, dg = (t.to(dev) for t in hin)
-        ref = (ops.causal_fwd(dq, dk, dv),) + tuple(ops.causal_bwd(dq, dk, dv, dg))
+        attn, ws, has = ops.causal_fwd_saved(dq, dk, dv)           # the calls the pipeline makes per step
+        ref = (attn,) + tuple(ops.causal_bwd_saved(dq, dk, dv, dg, attn, ws, has))
         for a, b in zip(hout, ref):
             assert torch.equal(a, b.cpu())
 
