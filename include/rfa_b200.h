@@ -86,6 +86,19 @@ int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w,
                         int64_t rows, int H, int d, int D, float scale,
                         rfa_stream_t stream);
 
+/* Effective random matrices for a whole step in one launch:
+ *   out[i] = sigma[i] * bank[idx[i]] * inv_tau[i],  i < n_out
+ * bank [n_bank, D, d] (fp16 or fp32, resident on the device), idx [n_out] int64,
+ * sigma [n_out, d] fp32 or NULL, inv_tau [n_out] fp32 or NULL, out [n_out, D, d]
+ * fp32.  An index outside the bank sets *bad_index_flag (a device int the caller
+ * zeroes) and yields zeros.  replaces the host-side gather of
+ * sample_random_matrices (utils.py:62-87) plus build_random_matrices per layer
+ * (utils.py:90-97). */
+int rfa_gather_random_matrices(const void* bank, int bank_dtype, int64_t n_bank,
+                               const int64_t* idx, int64_t n_out,
+                               const float* sigma, const float* inv_tau, float* out,
+                               int D, int d, int* bad_index_flag, rfa_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Causal RFA.  q,k [T,BH,K] fp16, v/out/g [T,BH,d] fp16, time-major.
  *   out_t = q_t^T S_t / max(q_t . z_t, 1),  S_t = S_in + sum_{s<=t} k_s v_s^T,

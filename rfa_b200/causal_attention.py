@@ -20,6 +20,34 @@ from .utils import (EPS, build_random_matrices, normalize_attn_weights, random_p
                     upgrade_state_dict_named)
 
 
+class _StatefulRFA(torch.autograd.Function):
+    """Causal RFA over a run of tokens with the state carried in AND out, differentiable in all five inputs:
+    (q, k, v [T,BH,.] fp16; s_in [BH,K,d], z_in [BH,K] fp32) -> (out, s_out, z_out).  The gradient with respect to the
+    incoming state is the run's own reverse-state total (sum_t q_t (x) g_t/den_t, sum_t q_t gz_t) plus whatever flows
+    back into the outgoing state, which is exactly the reverse carry of the second backward sweep."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, s_in, z_in):
+        out, s_out, z_out = ops.causal_fwd(q, k, v, s_in, z_in, return_state=True)
+        ctx.save_for_backward(q, k, v, s_in, z_in)
+        return out, s_out, z_out
+
+    @staticmethod
+    def backward(ctx, g_out, g_s, g_z):
+        q, k, v, s_in, z_in = ctx.saved_tensors
+        g = g_out.contiguous().to(q.dtype)
+        gq, ds_tot, dz_tot, ws = ops.causal_bwd_q(q, k, v, g, s_in, z_in, True)
+        ds_in = None if g_s is None else g_s.contiguous().float()
+        dz_in = None if g_z is None else g_z.contiguous().float()
+        if (ds_in is None) != (dz_in is None):          # the kernels take the reverse carry as a pair
+            ds_in = torch.zeros_like(ds_tot) if ds_in is None else ds_in
+            dz_in = torch.zeros_like(dz_tot) if dz_in is None else dz_in
+        gk, gv = ops.causal_bwd_kv(q, k, v, g, ds_in, dz_in, ws)
+        if ds_in is not None:
+            ds_tot, dz_tot = ds_tot + ds_in, dz_tot + dz_in
+        return gq, gk, gv, ds_tot, dz_tot
+
+
 def incremental_rfa(*, phi_q: Tensor, phi_k: Tensor, v: Tensor,
                     s: Optional[Tensor] = None, z: Optional[Tensor] = None):
     """Advance the running state by ``tgt_len`` tokens and attend.
@@ -29,15 +57,24 @@ def incremental_rfa(*, phi_q: Tensor, phi_k: Tensor, v: Tensor,
     2*proj_dim]``.  Returns ``(attn [tgt_len, bsz, num_heads*head_dim], s, z)``.
 
     Differences from upstream (causal_attention.py:17-54), both for accuracy/speed:
-    a fresh state is created in fp32 (upstream: v's dtype), and a state that is
-    passed in is UPDATED IN PLACE and returned (upstream allocates a new one per
-    token).  No autograd through this path (it is the inference loop)."""
+    a fresh state is created in fp32 (upstream: v's dtype), and -- when no gradient
+    is being recorded, the inference loop -- a state that is passed in is UPDATED IN
+    PLACE and returned (upstream allocates a new one per token).  With autograd
+    recording and an input that requires grad the call is differentiable like
+    upstream's: it then returns NEW state tensors and leaves the ones passed in alone."""
     tgt_len, bsz, num_heads, feat = phi_q.shape
     head_dim = v.size(-1)
     if s is None:
         assert z is None
         s = torch.zeros(bsz, num_heads, feat, head_dim, device=v.device, dtype=torch.float32)
         z = torch.zeros(bsz, num_heads, feat, device=v.device, dtype=torch.float32)
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (phi_q, phi_k, v, s, z)):
+        BH = bsz * num_heads
+        h = lambda t: t.contiguous().view(tgt_len, BH, -1).to(torch.float16)
+        attn, s_new, z_new = _StatefulRFA.apply(h(phi_q), h(phi_k), h(v), s.reshape(BH, feat, head_dim).float().contiguous(),
+                                                z.reshape(BH, feat).float().contiguous())
+        return (attn.to(v.dtype).reshape(tgt_len, bsz, num_heads * head_dim), s_new.view(bsz, num_heads, feat, head_dim),
+                z_new.view(bsz, num_heads, feat))
     with torch.no_grad():
         if tgt_len == 1:
             attn = ops.decode_step(phi_q[0], phi_k[0], v[0], s, z).unsqueeze(0)
@@ -124,6 +161,18 @@ class CausalAttention(nn.Module):
             nn.init.constant_(self.sigma, 1.)
         if self.out_proj.bias is not None:
             nn.init.constant_(self.out_proj.bias, 0.0)
+
+    @staticmethod
+    def reorder_incremental_state(saved_state: Dict[str, Optional[Tensor]], new_order: Tensor) -> Dict[str, Optional[Tensor]]:
+        """Beam search: keep, per new batch slot i, the running state of old slot ``new_order[i]`` -- one gather per
+        state tensor along the batch axis of ``prev_s [bsz, heads, 2*proj_dim, head_dim]`` and ``prev_z``.  (Upstream
+        keeps the state in a plain dict, causal_attention.py:249-265, and leaves the reordering to its decoder, which
+        is not part of the shipped sources.)"""
+        for key in ("prev_s", "prev_z"):
+            t = saved_state.get(key)
+            if t is not None:
+                saved_state[key] = t.index_select(0, new_order.to(device=t.device, dtype=torch.long))
+        return saved_state
 
     def _heads(self, t: Tensor) -> Tensor:
         return t.contiguous().view(t.size(0), t.size(1), self.num_heads, self.head_dim)

@@ -290,3 +290,47 @@ extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, c
 #undef RFA_LAUNCH
   return check_launch("rfa_feature_map_bwd");
 }
+
+// ---------------------------------------------------------------------------
+// Effective random matrices of a whole step in one launch: out[i] = sigma[i] * bank[idx[i]] * inv_tau[i]
+// (upstream gathers the sampled matrices on the host, utils.py:62-87, and applies sigma / tau per layer with separate
+// PyTorch ops, utils.py:90-97).  bank [n_bank, D, d] fp16 or fp32 stays resident on the device.
+// ---------------------------------------------------------------------------
+namespace rfa {
+template <typename TB>
+__global__ void gather_matrices_kernel(const TB* __restrict__ bank, int64_t n_bank, const int64_t* __restrict__ idx,
+                                       const float* __restrict__ sigma, const float* __restrict__ inv_tau,
+                                       float* __restrict__ out, int64_t n_out, int D, int d, int* __restrict__ bad) {
+  const int64_t per = (int64_t)D * d;
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_out * per) return;
+  const int64_t i = e / per, r = e % per;
+  const int64_t src = idx[i];
+  if (src < 0 || src >= n_bank) {          // a pick outside the bank: flag it and write zeros instead of reading out of bounds
+    if (r == 0) atomicExch(bad, 1);
+    out[e] = 0.f;
+    return;
+  }
+  float w = to_f(bank[src * per + r]);
+  if (sigma) w *= sigma[i * d + r % d];
+  if (inv_tau) w *= inv_tau[i];
+  out[e] = w;
+}
+}  // namespace rfa
+
+extern "C" int rfa_gather_random_matrices(const void* bank, int bank_dtype, int64_t n_bank, const int64_t* idx, int64_t n_out,
+                                          const float* sigma, const float* inv_tau, float* out, int D, int d, int* bad_index_flag,
+                                          rfa_stream_t stream) {
+  RFA_REQUIRE(bank && idx && out && bad_index_flag, RFA_EINVAL, "gather_random_matrices: null pointer");
+  RFA_REQUIRE(n_bank > 0 && n_out >= 0 && D > 0 && d > 0, RFA_EINVAL, "gather_random_matrices: n_bank=%lld n_out=%lld D=%d d=%d",
+              (long long)n_bank, (long long)n_out, D, d);
+  RFA_REQUIRE(bank_dtype == RFA_F16 || bank_dtype == RFA_F32, RFA_EUNSUPPORTED, "gather_random_matrices: bank dtype %d", bank_dtype);
+  if (n_out == 0) return 0;
+  const int64_t total = n_out * D * d;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (bank_dtype == RFA_F16)
+    gather_matrices_kernel<__half><<<blocks, 256, 0, as_stream(stream)>>>((const __half*)bank, n_bank, idx, sigma, inv_tau, out, n_out, D, d, bad_index_flag);
+  else
+    gather_matrices_kernel<float><<<blocks, 256, 0, as_stream(stream)>>>((const float*)bank, n_bank, idx, sigma, inv_tau, out, n_out, D, d, bad_index_flag);
+  return check_launch("rfa_gather_random_matrices");
+}

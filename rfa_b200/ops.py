@@ -73,6 +73,26 @@ def feature_map_bwd(x: Tensor, w: Tensor, g_phi: Tensor, scale: float, need_gw: 
     return g_x, g_w
 
 
+def gather_random_matrices(bank: Tensor, picks: Tensor, sigma: Optional[Tensor] = None,
+                           inv_tau: Optional[Tensor] = None) -> Tensor:
+    """bank [N, D, d] (fp16 / fp32, on the device), picks [n] int64 -> [n, D, d] fp32 = sigma[i] * bank[picks[i]] * inv_tau[i]
+    (sigma [n, d], inv_tau [n], both optional), one launch."""
+    N, D, d = bank.shape
+    bank = bank.contiguous()
+    picks = picks.to(device=bank.device, dtype=torch.int64).contiguous()
+    n = picks.numel()
+    out = torch.empty(n, D, d, dtype=torch.float32, device=bank.device)
+    if sigma is not None:
+        sigma = sigma.to(device=bank.device, dtype=torch.float32).reshape(n, d).contiguous()
+    if inv_tau is not None:
+        inv_tau = inv_tau.to(device=bank.device, dtype=torch.float32).reshape(n).contiguous()
+    bad = torch.zeros(1, dtype=torch.int32, device=bank.device)
+    with _guard(bank):
+        check(_lib.load().rfa_gather_random_matrices(ptr(bank), dtype_code(bank), N, ptr(picks), n, ptr(sigma), ptr(inv_tau),
+                                                     ptr(out), D, d, ptr(bad), stream_of(bank)), "rfa_gather_random_matrices")
+    return out, bad
+
+
 # --------------------------------------------------------------------------- causal
 def causal_fwd(q: Tensor, k: Tensor, v: Tensor, s_in: Optional[Tensor] = None, z_in: Optional[Tensor] = None,
                return_state: bool = False):

@@ -64,17 +64,75 @@ def load_random_matrices(*, head_dim: int, proj_dim: int, dtype: torch.dtype = t
     return torch.nn.Parameter(bank, requires_grad=False)
 
 
+def sample_matrix_indices(*, num_layers: int, num_heads: int, bank_size: int,
+                          generator: Optional[torch.Generator] = None) -> Tensor:
+    """``num_layers * num_heads`` distinct indices into the bank.  With a ``torch.Generator`` the draw is reproducible
+    and identical on every rank that seeds it alike; without one it consumes numpy's global RNG exactly as upstream
+    does (utils.py:73-76), which differs from rank to rank unless the caller seeds numpy everywhere."""
+    n = num_layers * num_heads
+    if generator is None:
+        return torch.from_numpy(np.random.choice(bank_size, size=n, replace=False)).to(torch.int64)
+    return torch.randperm(bank_size, generator=generator, device=generator.device)[:n].to(torch.int64)
+
+
 def sample_random_matrices(*, num_layers: int, num_heads: int, random_matrices: Tensor,
-                           is_training: bool = True):
-    """Training: ``num_layers * num_heads`` distinct matrices drawn from the bank with
-    numpy's global RNG, returned as a list of ``[num_heads, proj_dim, head_dim]`` per
-    layer.  Evaluation: the first ``num_heads`` matrices (one tensor shared by all
-    layers).  (upstream utils.py:62-87)"""
+                           is_training: bool = True, generator: Optional[torch.Generator] = None):
+    """Training: ``num_layers * num_heads`` distinct matrices drawn from the bank, returned as a list of
+    ``[num_heads, proj_dim, head_dim]`` per layer.  Evaluation: the first ``num_heads`` matrices (one tensor shared by
+    all layers).  (upstream utils.py:62-87; ``generator`` is an addition, see ``sample_matrix_indices``)"""
     if not is_training:
         return random_matrices[list(range(num_heads))]
-    picks = np.random.choice(random_matrices.size(0), size=num_layers * num_heads, replace=False)
-    chosen = random_matrices[picks]
+    picks = sample_matrix_indices(num_layers=num_layers, num_heads=num_heads, bank_size=random_matrices.size(0),
+                                  generator=generator)
+    chosen = random_matrices[picks.to(random_matrices.device)]
     return list(chosen.split(num_heads, dim=0))
+
+
+class _GatherMatrices(torch.autograd.Function):
+    """out[i] = sigma[i] * bank[picks[i]] * inv_tau[i] in one kernel; differentiable in sigma (the layers' learnable
+    per-head scales), whose gradient is a small reduction done with tensor ops."""
+
+    @staticmethod
+    def forward(ctx, bank, picks, sigma, inv_tau):
+        out, bad = ops.gather_random_matrices(bank, picks, sigma, inv_tau)
+        ctx.save_for_backward(bank, picks, inv_tau)
+        ctx.bad = bad
+        return out
+
+    @staticmethod
+    def backward(ctx, g_out):
+        bank, picks, inv_tau = ctx.saved_tensors
+        g_sigma = None
+        if ctx.needs_input_grad[2]:
+            w = bank[picks.to(bank.device)].float()
+            if inv_tau is not None:
+                w = w * inv_tau.to(w.device).view(-1, 1, 1)
+            g_sigma = (g_out * w).sum(dim=1)
+        return None, None, g_sigma, None
+
+
+def sample_effective_matrices(*, num_layers: int, num_heads: int, random_matrices: Tensor, taus, sigmas=None,
+                              is_training: bool = True, generator: Optional[torch.Generator] = None) -> Tensor:
+    """Sampling and ``build_random_matrices`` for ALL layers of a step in one kernel launch on a device-resident bank:
+    returns ``[num_layers, num_heads, proj_dim, head_dim]`` fp32 with layer l holding ``sigma_l * W / tau_l`` -- what
+    each layer would otherwise compute itself from the list ``sample_random_matrices`` returns (upstream utils.py:62-97,
+    cross_attention.py:166-176).  ``taus``: one float per layer; ``sigmas``: per layer ``[num_heads, 1, head_dim]`` or
+    None.  Pass the result's slices to layers built with ``reparam_proj=False, tau=1``-style calls of ``random_project``."""
+    bank = random_matrices
+    if not bank.is_cuda:
+        raise RuntimeError("rfa_b200: sample_effective_matrices wants the bank on the device (there is no CPU path)")
+    n = num_layers * num_heads
+    if is_training:
+        picks = sample_matrix_indices(num_layers=num_layers, num_heads=num_heads, bank_size=bank.size(0), generator=generator)
+    else:
+        picks = torch.arange(num_heads, dtype=torch.int64).repeat(num_layers)
+    head_dim = bank.size(-1)
+    inv_tau = torch.tensor([1.0 / float(t) for t in taus], dtype=torch.float32).repeat_interleave(num_heads)
+    sigma = None
+    if sigmas is not None:
+        sigma = torch.stack([s.reshape(num_heads, head_dim) for s in sigmas]).reshape(n, head_dim)
+    out = _GatherMatrices.apply(bank, picks.to(bank.device), sigma, inv_tau.to(bank.device))
+    return out.view(num_layers, num_heads, bank.size(1), head_dim)
 
 
 def build_random_matrices(random_matrices: Tensor, tau: float, sigma: Optional[Tensor] = None,

@@ -257,6 +257,30 @@ def test_state_total_matches_single_cta_reduction(dev):
         assert_close(z1, z0.view(BH, 128).cpu(), "z vs single", rel=1e-5, mabs=1e-3)
 
 
+def test_effective_matrices_for_all_layers_in_one_launch(dev):
+    """Device-resident bank, deterministic picks, sigma / tau applied by the gather kernel: equals upstream's
+    sample_random_matrices + build_random_matrices per layer (restated by the oracle), with the gradient reaching sigma."""
+    from rfa_b200 import utils
+    L, H, D, d = 3, 4, 64, 64
+    bank = torch.from_numpy(O.draw_matrices("orf", 40, d, D, 5)).half()
+    taus = [0.9, 1.0, 1.3]
+    sigmas = [(torch.rand(H, 1, d) + 0.5).to(dev).requires_grad_(True) for _ in range(L)]
+    gen = lambda: torch.Generator().manual_seed(11)
+    eff = utils.sample_effective_matrices(num_layers=L, num_heads=H, random_matrices=bank.to(dev), taus=taus, sigmas=sigmas,
+                                          generator=gen())
+    layers = utils.sample_random_matrices(num_layers=L, num_heads=H, random_matrices=bank, generator=gen())
+    for l in range(L):
+        want = O.build_random_matrices(layers[l].float(), taus[l], sigmas[l].detach().cpu(), True)
+        assert_close(eff[l], want, f"layer {l}", rel=1e-6, mabs=1e-6)
+    up = torch.randn(L, H, D, d, device=dev)
+    (eff * up).sum().backward()
+    for l in range(L):
+        want = (up[l].cpu() * layers[l].float() / taus[l]).sum(dim=1, keepdim=True)
+        assert_close(sigmas[l].grad, want, f"grad sigma {l}", rel=1e-5, mabs=1e-4)
+    ev = utils.sample_effective_matrices(num_layers=2, num_heads=H, random_matrices=bank.to(dev), taus=[1.0, 2.0], is_training=False)
+    assert_close(ev[1], bank[:H].float() / 2.0, "evaluation: the first H matrices", rel=1e-6, mabs=1e-6)
+
+
 # ----------------------------------------------------------------------------- decode
 def test_decode_against_upstream_fixture(dev):
     from rfa_b200.causal_attention import incremental_rfa
@@ -271,6 +295,27 @@ def test_decode_against_upstream_fixture(dev):
         outs.append(a)
     assert_close(torch.cat(outs), g["attn_b"], "attn_b")
     assert_close(s, g["s_b"], "s_b", rel=1e-4); assert_close(z, g["z_b"], "z_b", rel=1e-4)
+
+
+def test_incremental_rfa_is_differentiable_and_reorderable(dev):
+    """With autograd recording, incremental_rfa differentiates through outputs AND the carried state (as upstream's plain
+    PyTorch loop does): two calls in a row against the oracle's gradients of the whole run; then the beam reorder."""
+    from rfa_b200.causal_attention import CausalAttention, incremental_rfa
+    T, B, H, cut = 40, 2, 3, 25
+    q, k, v, g = feats(T, B * H, seed=12)
+    leaves = [t.view(T, B, H, -1).half().to(dev).requires_grad_(True) for t in (q, k, v)]
+    pq, pk, pv = leaves
+    a1, s, z = incremental_rfa(phi_q=pq[:cut], phi_k=pk[:cut], v=pv[:cut])
+    a2, s2, z2 = incremental_rfa(phi_q=pq[cut:], phi_k=pk[cut:], v=pv[cut:], s=s, z=z)
+    attn = torch.cat([a1, a2])
+    assert_close(attn.view(T, B * H, 64), O.causal_forward(q, k, v), "attn")
+    (attn.view(T, B * H, 64).float() * g.to(dev)).sum().backward()
+    rq, rk, rv = O.causal_backward(q, k, v, g)
+    assert_close(pq.grad.view(T, B * H, 128), rq, "gq"); assert_close(pk.grad.view(T, B * H, 128), rk, "gk")
+    assert_close(pv.grad.view(T, B * H, 64), rv, "gv")
+    st = {"prev_s": s2.detach(), "prev_z": z2.detach()}
+    CausalAttention.reorder_incremental_state(st, torch.tensor([1, 1, 0]))
+    assert st["prev_s"].shape[0] == 3 and torch.equal(st["prev_s"][0], s2[1]) and torch.equal(st["prev_z"][2], z2[0])
 
 
 @pytest.mark.parametrize("state_dtype,in_dtype", [(torch.float32, torch.float16), (torch.float16, torch.float16), (torch.float32, torch.float32)])

@@ -1,4 +1,4 @@
-"""Sequence-sharded causal RFA on 2 GPUs over NCCL (skipped with fewer than two devices):
+"""Sequence-sharded causal RFA on 2 and 4 GPUs over NCCL (skipped with fewer devices):
 rfa_b200.sharded with the real kernels must equal the unsharded kernels and the oracle."""
 import os
 import socket
@@ -26,7 +26,7 @@ def _worker(rank, world, port, out_q):
         from oracle import rfa_oracle as O
         from rfa_b200 import sharded
         gen = torch.Generator().manual_seed(0)
-        T, BH = 1024, 3
+        T, BH = 1024 * world // 2, 3
         q = (torch.rand(T, BH, 128, generator=gen) * 0.2).half()
         k = (torch.rand(T, BH, 128, generator=gen) * 0.2).half()
         v = torch.randn(T, BH, 64, generator=gen).half()
@@ -47,16 +47,17 @@ def _worker(rank, world, port, out_q):
         dist.destroy_process_group()
 
 
-def test_two_gpu_sequence_sharding_matches_oracle():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_multi_gpu_sequence_sharding_matches_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out_q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out_q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [out_q.get(timeout=300) for _ in range(2)]
+    results = [out_q.get(timeout=300) for _ in range(world)]
     for p in procs:
         p.join(timeout=60)
     for rank, errs in results:

@@ -93,3 +93,19 @@ def test_cpu_list_parsing_for_numa_binding():
     assert _cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
     assert _cpulist("") == []
     assert gpu_numa_cpus(0, sysfs="/nonexistent") is None       # no GPU / no sysfs entry: nothing to bind to
+
+
+def test_matrix_sampling_with_a_generator_is_reproducible():
+    from rfa_b200.utils import sample_matrix_indices, sample_random_matrices
+    mk = lambda: torch.Generator().manual_seed(7)
+    a = sample_matrix_indices(num_layers=3, num_heads=4, bank_size=50, generator=mk())
+    b = sample_matrix_indices(num_layers=3, num_heads=4, bank_size=50, generator=mk())
+    assert torch.equal(a, b) and a.numel() == 12 and len(set(a.tolist())) == 12 and int(a.max()) < 50
+    bank = torch.arange(50.).view(50, 1, 1).expand(50, 2, 3).contiguous()
+    layers = sample_random_matrices(num_layers=3, num_heads=4, random_matrices=bank, generator=mk())
+    assert len(layers) == 3 and torch.equal(torch.cat(layers)[:, 0, 0].long(), a)
+    import numpy as np
+    np.random.seed(3)
+    x = sample_matrix_indices(num_layers=2, num_heads=2, bank_size=9)        # upstream's way: numpy's global RNG
+    np.random.seed(3)
+    assert x.tolist() == np.random.choice(9, size=4, replace=False).tolist()
