@@ -587,6 +587,30 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
+    # the host link's own ceiling, measured the same way on every rank at once: the step's uploads and downloads with no
+    # kernel between them (full duplex: uploads on one stream, downloads on another)
+    dev_in = pipe.slots[0]["in"]
+    dev_out = pipe.slots[0]["out"]
+
+    def copies_only():
+        with torch.cuda.stream(pipe.up):
+            for dst, h in zip(dev_in, (hq, hk, hv, hg)):
+                dst.copy_(h, non_blocking=True)
+        with torch.cuda.stream(pipe.down):
+            for h, src in zip(ho, dev_out):
+                h.copy_(src, non_blocking=True)
+    barrier()
+    e0.record(stream)
+    pipe.up.wait_stream(stream); pipe.down.wait_stream(stream)
+    for _ in range(e2e_steps):
+        copies_only()
+    pipe.join(stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    copy_ms = float(t.item())
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hg))
     d2h = sum(x.numel() * x.element_size() for x in ho)
 
@@ -618,6 +642,7 @@ def main():
             "e2e": {"value": world * TOKENS_PER_STEP / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "h2d_GBps_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_GBps_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
+                    "copies_only_ms_per_step": copy_ms, "frac_of_copy_ceiling": copy_ms / e2e_ms,
                     "numa_bound": affinity_before is not None,
                     "api": "rfa_b200.host_pipeline.HostPipelinedRFA.step (upload / compute / download streams), pinned host buffers"},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps,

@@ -17,9 +17,14 @@
  * the upstream interface (file:line) each entry point stands in for.
  *
  * Shapes: T tokens (time-major), BH = batch*heads, K = 2*D = width of phi,
- * d = head_dim.  The attention kernels support K == 128 and d == 64 (the only
- * geometry upstream's benchmarks and checks use); anything else is rejected
- * with RFA_EUNSUPPORTED.  fp16 arrays are IEEE binary16 ("half").
+ * d = head_dim.  The tensor-core attention kernels are built for K == 128 and
+ * d == 64 (the only geometry upstream's benchmarks and checks use).  Any other
+ * K % 8 == 0, d % 8 == 0 whose fp32 state [K][d+1] fits in shared memory (e.g.
+ * K <= 256 with d <= 128) runs on plain CUDA-core kernels that walk a sequence
+ * token by token, as upstream's do (cuda/forward.cu:112-125): correct, not fast.
+ * The packed-total / gathered-scan entry points of the sequence-sharded path and
+ * rfa_causal_bwd_noalloc exist for K == 128, d == 64 only.  Unsupported
+ * geometries are rejected with RFA_EUNSUPPORTED.  fp16 arrays are IEEE binary16.
  */
 #ifndef RFA_B200_H_
 #define RFA_B200_H_
@@ -85,6 +90,20 @@ int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w,
                         void* g_x, int gx_dtype, float* g_w,
                         int64_t rows, int H, int d, int D, float scale,
                         rfa_stream_t stream);
+
+/* The same two with a row mask: row_mask [rows] bytes (may be NULL), non-zero =
+ * the row's features are all zero and no gradient flows through it -- a padded
+ * key.  replaces the separate masked_fill pass over phi_k in cuda_causal_rfa
+ * (causal_attention.py:137-143) when the caller computes phi_k itself. */
+int rfa_feature_map_fwd_masked(const void* x, int x_dtype, const float* w,
+                               const uint8_t* row_mask, void* phi, int phi_dtype,
+                               int64_t rows, int H, int d, int D, float scale,
+                               rfa_stream_t stream);
+int rfa_feature_map_bwd_masked(const void* x, int x_dtype, const float* w,
+                               const uint8_t* row_mask, const void* g_phi, int g_dtype,
+                               void* g_x, int gx_dtype, float* g_w,
+                               int64_t rows, int H, int d, int D, float scale,
+                               rfa_stream_t stream);
 
 /* Effective random matrices for a whole step in one launch:
  *   out[i] = sigma[i] * bank[idx[i]] * inv_tau[i],  i < n_out

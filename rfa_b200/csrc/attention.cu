@@ -48,6 +48,25 @@ int launch_cross_query_bwd_tc(const __half* q, const float* s, const float* z, c
 int launch_cross_state_bwd_tc(const __half* k, const __half* v, const uint8_t* pad_mask, const float* d_s, const float* d_z,
                               __half* gk, __half* gv, int64_t T, int BH, int H, cudaStream_t st);
 
+// CUDA-core kernels for every other geometry (generic.cu)
+bool generic_geometry_ok(int K, int d, bool two_states);
+int launch_causal_generic_fwd(const __half* q, const __half* k, const __half* v, __half* out, const float* s_in, const float* z_in,
+                              float* s_out, float* z_out, float* den_out, int64_t T, int BH, int K, int d, cudaStream_t st);
+int launch_causal_generic_bwd_q(const __half* q, const __half* k, const __half* v, const __half* g, __half* gq, const float* s_in,
+                                const float* z_in, float* ws_den, float* ws_gz, float* ds_tot, float* dz_tot, int64_t T, int BH,
+                                int K, int d, cudaStream_t st);
+int launch_causal_generic_bwd_kv(const __half* q, const __half* k, const __half* v, const __half* g, __half* gk, __half* gv,
+                                 const float* ws_den, const float* ws_gz, const float* ds_in, const float* dz_in, int64_t T,
+                                 int BH, int K, int d, cudaStream_t st);
+int launch_state_generic_fwd(const __half* k, const __half* v, const uint8_t* pad_mask, float* s, float* z, int64_t T, int BH, int H,
+                             int nseg, int64_t tseg, int K, int d, cudaStream_t st);
+int launch_cross_generic_query_fwd(const __half* q, const float* s, const float* z, __half* out, int64_t T, int BH, int K, int d,
+                                   cudaStream_t st);
+int launch_cross_generic_query_bwd(const __half* q, const float* s, const float* z, const __half* g, __half* gq, float* d_s,
+                                   float* d_z, int64_t T, int BH, int K, int d, cudaStream_t st);
+int launch_state_generic_bwd(const __half* k, const __half* v, const uint8_t* pad_mask, const float* d_s, const float* d_z,
+                             __half* gk, __half* gv, int64_t T, int BH, int H, int K, int d, cudaStream_t st);
+
 static CausalPlan plan_causal(int64_t T, int BH) {
   CausalPlan p{1, ((T + kSegAlign - 1) / kSegAlign) * kSegAlign};
   if (BH >= 120 || T < 1024) return p;
@@ -147,10 +166,17 @@ __global__ void scan_gathered_kernel(const float* __restrict__ gathered, int wor
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-static int check_geometry(const char* what, int64_t T, int BH, int K, int d) {
+// Which kernels serve a geometry: the tensor-core ones (K = 128, d = 64) or the generic CUDA-core ones.
+static bool is_tc(int K, int d) { return K == kK && d == kD; }
+
+static int check_geometry(const char* what, int64_t T, int BH, int K, int d, bool generic_allowed = true, bool two_states = false) {
   RFA_REQUIRE(T >= 0 && BH > 0, RFA_EINVAL, "%s: T=%lld BH=%d", what, (long long)T, BH);
-  RFA_REQUIRE(K == kK && d == kD, RFA_EUNSUPPORTED, "%s: only K=%d, d=%d is built (got K=%d d=%d)", what, kK, kD, K, d);
   RFA_REQUIRE(BH <= 65535, RFA_EUNSUPPORTED, "%s: BH=%d exceeds 65535", what, BH);
+  if (is_tc(K, d)) return 0;
+  RFA_REQUIRE(generic_allowed, RFA_EUNSUPPORTED, "%s: this entry point is built for K=%d, d=%d only (got K=%d d=%d)", what, kK, kD, K, d);
+  RFA_REQUIRE(generic_geometry_ok(K, d, two_states), RFA_EUNSUPPORTED,
+              "%s: K=%d d=%d: K and d must be multiples of 8 and the fp32 state%s must fit in shared memory", what, K, d,
+              two_states ? "s (two of them for this call)" : "");
   return 0;
 }
 
@@ -187,7 +213,11 @@ static int check_ws(const char* what, void* workspace, size_t bytes, int64_t T, 
 using namespace rfa;
 
 extern "C" size_t rfa_causal_workspace_bytes(int64_t T, int BH, int K, int d) {
-  if (T < 0 || BH <= 0 || K != kK || d != kD) return 0;
+  if (T < 0 || BH <= 0) return 0;
+  if (!is_tc(K, d)) {                     // generic geometry: one run per sequence, only the two per-token scalars
+    if (!generic_geometry_ok(K, d, false)) return 0;
+    return carve_ws(nullptr, T, BH, CausalPlan{1, T}).bytes;
+  }
   const CausalPlan p = plan_causal(T, BH);
   return carve_ws(nullptr, T, BH, p).bytes;
 }
@@ -204,20 +234,27 @@ extern "C" int rfa_causal_fwd_staged(const void* q, const void* k, const void* v
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(s_in) && aligned16(z_in) &&
                   aligned16(s_out) && aligned16(z_out), RFA_EALIGN, "causal_fwd: 16-byte alignment required");
   RFA_REQUIRE((ws_has & ~RFA_WS_PARTIALS) == 0, RFA_EINVAL, "causal_fwd: ws_has may only name RFA_WS_PARTIALS (got %d)", ws_has);
-  const CausalPlan p = plan_causal(T, BH);
+  const CausalPlan p = is_tc(K, d) ? plan_causal(T, BH) : CausalPlan{1, T};
   cudaStream_t st = as_stream(stream);
   const float *s_seg = s_in, *z_seg = z_in;
   if (T == 0) {
     if (s_out) {
       if (s_in) {
-        cudaMemcpyAsync(s_out, s_in, (size_t)BH * kK * kD * sizeof(float), cudaMemcpyDeviceToDevice, st);
-        cudaMemcpyAsync(z_out, z_in, (size_t)BH * kK * sizeof(float), cudaMemcpyDeviceToDevice, st);
+        cudaMemcpyAsync(s_out, s_in, (size_t)BH * K * d * sizeof(float), cudaMemcpyDeviceToDevice, st);
+        cudaMemcpyAsync(z_out, z_in, (size_t)BH * K * sizeof(float), cudaMemcpyDeviceToDevice, st);
       } else {
-        cudaMemsetAsync(s_out, 0, (size_t)BH * kK * kD * sizeof(float), st);
-        cudaMemsetAsync(z_out, 0, (size_t)BH * kK * sizeof(float), st);
+        cudaMemsetAsync(s_out, 0, (size_t)BH * K * d * sizeof(float), st);
+        cudaMemsetAsync(z_out, 0, (size_t)BH * K * sizeof(float), st);
       }
     }
     return check_launch("causal_fwd(T=0)");
+  }
+  if (!is_tc(K, d)) {
+    CausalWs gws{};
+    if (save_den)
+      if (int e = check_ws("causal_fwd", workspace, workspace_bytes, T, BH, p, &gws)) return e;
+    return launch_causal_generic_fwd((const __half*)q, (const __half*)k, (const __half*)v, (__half*)out, s_in, z_in, s_out, z_out,
+                                     save_den ? gws.den : nullptr, T, BH, K, d, st);
   }
   CausalWs ws{};
   if (p.nseg > 1 || save_den)
@@ -245,7 +282,7 @@ extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void*
 // workspace for rfa_causal_fwd_staged(..., RFA_WS_PARTIALS, ...).
 extern "C" int rfa_causal_shard_total(const void* k, const void* v, float* total_packed, void* workspace, size_t workspace_bytes,
                                       int64_t T, int BH, int K, int d, rfa_stream_t stream) {
-  if (int e = check_geometry("causal_shard_total", T, BH, K, d)) return e;
+  if (int e = check_geometry("causal_shard_total", T, BH, K, d, false)) return e;
   RFA_REQUIRE(total_packed && (T == 0 || (k && v)), RFA_EINVAL, "causal_shard_total: null pointer");
   RFA_REQUIRE(aligned16(k) && aligned16(v) && aligned16(total_packed), RFA_EALIGN, "causal_shard_total: 16-byte alignment required");
   cudaStream_t st = as_stream(stream);
@@ -262,7 +299,7 @@ extern "C" int rfa_causal_shard_total(const void* k, const void* v, float* total
 
 extern "C" int rfa_exclusive_scan_gathered(const float* gathered, int world, int rank, int reverse, float* s_out, float* z_out,
                                            int BH, int K, int d, rfa_stream_t stream) {
-  if (int e = check_geometry("exclusive_scan_gathered", 0, BH, K, d)) return e;
+  if (int e = check_geometry("exclusive_scan_gathered", 0, BH, K, d, false)) return e;
   RFA_REQUIRE(gathered && s_out && z_out, RFA_EINVAL, "exclusive_scan_gathered: null pointer");
   RFA_REQUIRE(world > 0 && rank >= 0 && rank < world, RFA_EINVAL, "exclusive_scan_gathered: rank %d of %d", rank, world);
   scan_gathered_kernel<<<state_blocks(BH), 256, 0, as_stream(stream)>>>(gathered, world, rank, reverse ? 1 : 0, s_out, z_out, BH);
@@ -274,7 +311,7 @@ static int bwd_q_impl(const void* q, const void* k, const void* v, const void* g
                       const float* s_in, const float* z_in, float* ds_tot, float* dz_tot, float* dtotal_packed,
                       void* workspace, size_t workspace_bytes, int64_t T, int BH, int K, int d, int ws_has,
                       rfa_stream_t stream) {
-  if (int e = check_geometry("causal_bwd_q", T, BH, K, d)) return e;
+  if (int e = check_geometry("causal_bwd_q", T, BH, K, d, dtotal_packed == nullptr, ds_tot != nullptr)) return e;
   RFA_REQUIRE(T == 0 || (q && k && v && g && gq), RFA_EINVAL, "causal_bwd_q: null pointer");   // empty arrays have no address
   RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (ds_tot == nullptr) == (dz_tot == nullptr), RFA_EINVAL,
               "causal_bwd_q: s/z pointers must be given in pairs");
@@ -284,19 +321,22 @@ static int bwd_q_impl(const void* q, const void* k, const void* v, const void* g
   RFA_REQUIRE((ws_has & ~(RFA_WS_STATES | RFA_WS_DEN)) == 0, RFA_EINVAL,
               "causal_bwd_q: ws_has may only name RFA_WS_STATES and RFA_WS_DEN (got %d)", ws_has);
   RFA_REQUIRE(!(ws_has & RFA_WS_DEN) || out, RFA_EINVAL, "causal_bwd_q: RFA_WS_DEN needs the forward's output as well");
-  const CausalPlan p = plan_causal(T, BH);
+  const CausalPlan p = is_tc(K, d) ? plan_causal(T, BH) : CausalPlan{1, T};
   cudaStream_t st = as_stream(stream);
   const bool want_tot = ds_tot != nullptr || dtotal_packed != nullptr;
   if (T == 0) {
     if (ds_tot) {
-      cudaMemsetAsync(ds_tot, 0, (size_t)BH * kK * kD * sizeof(float), st);
-      cudaMemsetAsync(dz_tot, 0, (size_t)BH * kK * sizeof(float), st);
+      cudaMemsetAsync(ds_tot, 0, (size_t)BH * K * d * sizeof(float), st);
+      cudaMemsetAsync(dz_tot, 0, (size_t)BH * K * sizeof(float), st);
     }
     if (dtotal_packed) cudaMemsetAsync(dtotal_packed, 0, (size_t)BH * kStateN * sizeof(float), st);
     return check_launch("causal_bwd_q(T=0)");
   }
   CausalWs ws;
   if (int e = check_ws("causal_bwd_q", workspace, workspace_bytes, T, BH, p, &ws)) return e;
+  if (!is_tc(K, d))      // the generic sweep recomputes (it does not use a saved output) and writes the totals itself
+    return launch_causal_generic_bwd_q((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gq, s_in,
+                                       z_in, ws.den, ws.gz, ds_tot, dz_tot, T, BH, K, d, st);
   const float *s_seg = s_in, *z_seg = z_in;
   if (p.nseg > 1) {
     if (!(ws_has & RFA_WS_STATES)) {    // the states entering each segment: partial sums, then an exclusive scan
@@ -350,10 +390,13 @@ extern "C" int rfa_causal_bwd_kv(const void* q, const void* k, const void* v, co
   RFA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(g) && aligned16(gk) && aligned16(gv) &&
                   aligned16(ds_in) && aligned16(dz_in), RFA_EALIGN, "causal_bwd_kv: 16-byte alignment required");
   if (T == 0) return 0;
-  const CausalPlan p = plan_causal(T, BH);
+  const CausalPlan p = is_tc(K, d) ? plan_causal(T, BH) : CausalPlan{1, T};
   cudaStream_t st = as_stream(stream);
   CausalWs ws;
   if (int e = check_ws("causal_bwd_kv", workspace, workspace_bytes, T, BH, p, &ws)) return e;
+  if (!is_tc(K, d))
+    return launch_causal_generic_bwd_kv((const __half*)q, (const __half*)k, (const __half*)v, (const __half*)g, (__half*)gk,
+                                        (__half*)gv, ws.den, ws.gz, ds_in, dz_in, T, BH, K, d, st);
   const float *ds_seg = ds_in, *dz_seg = dz_in;
   if (p.nseg > 1) {   // segment totals left by the forward-direction sweep -> reverse exclusive scan seeded with the carry
     if (int e = scan_launch(ws.ds_seg, ws.dz_seg, ds_in, dz_in, BH, p.nseg, 1, st)) return e;
@@ -392,10 +435,12 @@ extern "C" int rfa_cross_state_fwd(const void* phi_k, const void* v, const uint8
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(s) && aligned16(z), RFA_EALIGN,
               "cross_state_fwd: 16-byte alignment required");
   if (T == 0) {
-    cudaMemsetAsync(s, 0, (size_t)BH * kK * kD * sizeof(float), as_stream(stream));
-    cudaMemsetAsync(z, 0, (size_t)BH * kK * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(s, 0, (size_t)BH * K * d * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(z, 0, (size_t)BH * K * sizeof(float), as_stream(stream));
     return check_launch("rfa_cross_state_fwd(T=0)");
   }
+  if (!is_tc(K, d))
+    return launch_state_generic_fwd((const __half*)phi_k, (const __half*)v, pad_mask, s, z, T, BH, H, 1, T, K, d, as_stream(stream));
   const int64_t tseg = ((T + kSegAlign - 1) / kSegAlign) * kSegAlign;
   return launch_cross_state_fwd_tc((const __half*)phi_k, (const __half*)v, pad_mask, s, z, T, BH, H, 1, tseg, as_stream(stream));
 }
@@ -414,10 +459,13 @@ extern "C" int rfa_state_partials(const void* phi_k, const void* v, float* s_par
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(s_part) && aligned16(z_part), RFA_EALIGN,
               "state_partials: 16-byte alignment required");
   if (T == 0) {
-    cudaMemsetAsync(s_part, 0, (size_t)BH * nseg * kK * kD * sizeof(float), as_stream(stream));
-    cudaMemsetAsync(z_part, 0, (size_t)BH * nseg * kK * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(s_part, 0, (size_t)BH * nseg * K * d * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(z_part, 0, (size_t)BH * nseg * K * sizeof(float), as_stream(stream));
     return check_launch("rfa_state_partials(T=0)");
   }
+  if (!is_tc(K, d))
+    return launch_state_generic_fwd((const __half*)phi_k, (const __half*)v, nullptr, s_part, z_part, T, BH, 1, nseg,
+                                    rfa_state_partials_run_length(T, nseg), K, d, as_stream(stream));
   return launch_cross_state_fwd_tc((const __half*)phi_k, (const __half*)v, nullptr, s_part, z_part, T, BH, 1, nseg,
                                    rfa_state_partials_run_length(T, nseg), as_stream(stream));
 }
@@ -432,6 +480,9 @@ extern "C" int rfa_cross_state_bwd(const void* phi_k, const void* v, const uint8
   RFA_REQUIRE(aligned16(phi_k) && aligned16(v) && aligned16(d_s) && aligned16(d_z) && aligned16(g_phi_k) && aligned16(g_v),
               RFA_EALIGN, "cross_state_bwd: 16-byte alignment required");
   if (T == 0) return 0;
+  if (!is_tc(K, d))
+    return launch_state_generic_bwd((const __half*)phi_k, (const __half*)v, pad_mask, d_s, d_z, (__half*)g_phi_k, (__half*)g_v, T, BH,
+                                    H, K, d, as_stream(stream));
   return launch_cross_state_bwd_tc((const __half*)phi_k, (const __half*)v, pad_mask, d_s, d_z, (__half*)g_phi_k, (__half*)g_v, T, BH,
                                    H, as_stream(stream));
 }
@@ -443,20 +494,25 @@ extern "C" int rfa_cross_query_fwd(const void* phi_q, const float* s, const floa
   RFA_REQUIRE(aligned16(phi_q) && aligned16(s) && aligned16(z) && aligned16(out), RFA_EALIGN,
               "cross_query_fwd: 16-byte alignment required");
   if (T == 0) return 0;
+  if (!is_tc(K, d))
+    return launch_cross_generic_query_fwd((const __half*)phi_q, s, z, (__half*)out, T, BH, K, d, as_stream(stream));
   return launch_cross_query_fwd_tc((const __half*)phi_q, s, z, (__half*)out, T, BH, as_stream(stream));
 }
 
 extern "C" int rfa_cross_query_bwd(const void* phi_q, const float* s, const float* z, const void* g,
                                    void* g_phi_q, float* d_s, float* d_z,
                                    int64_t T, int BH, int K, int d, rfa_stream_t stream) {
-  if (int e = check_geometry("cross_query_bwd", T, BH, K, d)) return e;
+  if (int e = check_geometry("cross_query_bwd", T, BH, K, d, true, true)) return e;
   RFA_REQUIRE(s && z && d_s && d_z && (T == 0 || (phi_q && g && g_phi_q)), RFA_EINVAL, "cross_query_bwd: null pointer");
   RFA_REQUIRE(aligned16(phi_q) && aligned16(s) && aligned16(z) && aligned16(g) && aligned16(g_phi_q) && aligned16(d_s) &&
                   aligned16(d_z), RFA_EALIGN, "cross_query_bwd: 16-byte alignment required");
   if (T == 0) {
-    cudaMemsetAsync(d_s, 0, (size_t)BH * kK * kD * sizeof(float), as_stream(stream));
-    cudaMemsetAsync(d_z, 0, (size_t)BH * kK * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(d_s, 0, (size_t)BH * K * d * sizeof(float), as_stream(stream));
+    cudaMemsetAsync(d_z, 0, (size_t)BH * K * sizeof(float), as_stream(stream));
     return check_launch("rfa_cross_query_bwd(T=0)");
   }
+  if (!is_tc(K, d))
+    return launch_cross_generic_query_bwd((const __half*)phi_q, s, z, (const __half*)g, (__half*)g_phi_q, d_s, d_z, T, BH, K, d,
+                                          as_stream(stream));
   return launch_cross_query_bwd_tc((const __half*)phi_q, s, z, (const __half*)g, (__half*)g_phi_q, d_s, d_z, T, BH, as_stream(stream));
 }

@@ -71,8 +71,8 @@ __device__ __forceinline__ void fm_load_rows(const FmSmem& s, const TX* __restri
 
 template <typename TX, typename TP>
 __global__ void __launch_bounds__(kFmThreads)
-feature_map_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TP* __restrict__ phi,
-                       int64_t rows, int H, int d, int D, float scale, int R) {
+feature_map_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, const uint8_t* __restrict__ row_mask,
+                       TP* __restrict__ phi, int64_t rows, int H, int d, int D, float scale, int R) {
   extern __shared__ __align__(16) float fm_smem[];
   const FmSmem s = fm_carve(fm_smem, R, D, d, false, false);
   const int LU = fm_ldu(D, d);
@@ -96,11 +96,12 @@ feature_map_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TP
       const int64_t row = row0 + r;
       if (row >= rows) continue;
       float sn[8], cs[8];
+      const float sc_row = (row_mask && row_mask[row]) ? 0.f : scale;     // a masked row gets all-zero features
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         sincosf(s.U[r * LU + j0 + e], &sn[e], &cs[e]);
-        sn[e] *= scale;
-        cs[e] *= scale;
+        sn[e] *= sc_row;
+        cs[e] *= sc_row;
       }
       TP* dst = phi + ((size_t)row * H + h) * 2 * D + j0;
       if constexpr (sizeof(TP) == 2) {
@@ -120,7 +121,7 @@ feature_map_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TP
 //   g_xh = W^T g_u;  g_x = g_xh / (n + eps) - xh * (xh . g_xh) / n;  g_W += g_u (x) xh
 template <typename TX, typename TG, typename TO>
 __global__ void __launch_bounds__(kFmThreads)
-feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w,
+feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, const uint8_t* __restrict__ row_mask,
                        const TG* __restrict__ g_phi, TO* __restrict__ g_x, float* __restrict__ g_w,
                        int64_t rows, int H, int d, int D, float scale, int R) {
   extern __shared__ __align__(16) float fm_smem[];
@@ -148,7 +149,7 @@ feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w,
       const int r = idx / D, j = idx % D;
       const int64_t row = row0 + r;
       float gu = 0.f;
-      if (row < rows) {
+      if (row < rows && !(row_mask && row_mask[row])) {     // a masked row's features are constants: no gradient
         float sn, cs;
         sincosf(s.U[r * LU + j], &sn, &cs);
         const TG* gp = g_phi + ((size_t)row * H + h) * 2 * D;
@@ -191,9 +192,10 @@ feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w,
 }
 
 // tensor-core forward for fp16 rows with head_dim = proj_dim = 64 (feature_map_tc.cu)
-int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int64_t rows, int H, float scale, int sms, cudaStream_t st);
-int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_phi, __half* g_x, float* g_w, int64_t rows, int H,
-                              float scale, int sms, cudaStream_t st);
+int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* row_mask, __half* phi, int64_t rows, int H, float scale,
+                              int sms, cudaStream_t st);
+int launch_feature_map_bwd_tc(const __half* x, const float* w, const uint8_t* row_mask, const __half* g_phi, __half* g_x, float* g_w,
+                              int64_t rows, int H, float scale, int sms, cudaStream_t st);
 
 static int fm_check(const void* x, const float* w, int64_t rows, int H, int d, int D) {
   RFA_REQUIRE(x && w, RFA_EINVAL, "feature_map: null pointer");
@@ -226,8 +228,8 @@ static int fm_grid_x(int64_t ntiles, int H) {
 
 using namespace rfa;
 
-extern "C" int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w, void* phi, int phi_dtype,
-                                   int64_t rows, int H, int d, int D, float scale, rfa_stream_t stream) {
+extern "C" int rfa_feature_map_fwd_masked(const void* x, int x_dtype, const float* w, const uint8_t* row_mask, void* phi,
+                                          int phi_dtype, int64_t rows, int H, int d, int D, float scale, rfa_stream_t stream) {
   if (int e = fm_check(x, w, rows, H, d, D)) return e;
   RFA_REQUIRE(phi, RFA_EINVAL, "feature_map_fwd: null output");
   RFA_REQUIRE(aligned16(x) && aligned16(w) && aligned16(phi), RFA_EALIGN, "feature_map_fwd: 16-byte alignment required");
@@ -236,7 +238,7 @@ extern "C" int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w, v
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return launch_feature_map_fwd_tc((const __half*)x, w, (__half*)phi, rows, H, scale, sms, as_stream(stream));
+    return launch_feature_map_fwd_tc((const __half*)x, w, row_mask, (__half*)phi, rows, H, scale, sms, as_stream(stream));
   }
   size_t smem = 0;
   const int R = fm_pick_rows(D, d, false, false, &smem);
@@ -246,7 +248,7 @@ extern "C" int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w, v
 #define RFA_LAUNCH(TX, TP)                                                                         \
   do {                                                                                             \
     cudaFuncSetAttribute(feature_map_fwd_kernel<TX, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    feature_map_fwd_kernel<TX, TP><<<grid, kFmThreads, smem, st>>>((const TX*)x, w, (TP*)phi, rows, H, d, D, scale, R); \
+    feature_map_fwd_kernel<TX, TP><<<grid, kFmThreads, smem, st>>>((const TX*)x, w, row_mask, (TP*)phi, rows, H, d, D, scale, R); \
   } while (0)
   if (x_dtype == RFA_F16 && phi_dtype == RFA_F16) RFA_LAUNCH(__half, __half);
   else if (x_dtype == RFA_F32 && phi_dtype == RFA_F32) RFA_LAUNCH(float, float);
@@ -257,9 +259,14 @@ extern "C" int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w, v
   return check_launch("rfa_feature_map_fwd");
 }
 
-extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, const void* g_phi, int g_dtype,
-                                   void* g_x, int gx_dtype, float* g_w, int64_t rows, int H, int d, int D,
-                                   float scale, rfa_stream_t stream) {
+extern "C" int rfa_feature_map_fwd(const void* x, int x_dtype, const float* w, void* phi, int phi_dtype,
+                                   int64_t rows, int H, int d, int D, float scale, rfa_stream_t stream) {
+  return rfa_feature_map_fwd_masked(x, x_dtype, w, nullptr, phi, phi_dtype, rows, H, d, D, scale, stream);
+}
+
+extern "C" int rfa_feature_map_bwd_masked(const void* x, int x_dtype, const float* w, const uint8_t* row_mask, const void* g_phi,
+                                          int g_dtype, void* g_x, int gx_dtype, float* g_w, int64_t rows, int H, int d, int D,
+                                          float scale, rfa_stream_t stream) {
   if (int e = fm_check(x, w, rows, H, d, D)) return e;
   RFA_REQUIRE(g_phi && g_x, RFA_EINVAL, "feature_map_bwd: null pointer");
   RFA_REQUIRE(aligned16(x) && aligned16(w) && aligned16(g_phi) && aligned16(g_x) && aligned16(g_w), RFA_EALIGN,
@@ -271,7 +278,8 @@ extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, c
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return launch_feature_map_bwd_tc((const __half*)x, w, (const __half*)g_phi, (__half*)g_x, g_w, rows, H, scale, sms, as_stream(stream));
+    return launch_feature_map_bwd_tc((const __half*)x, w, row_mask, (const __half*)g_phi, (__half*)g_x, g_w, rows, H, scale, sms,
+                                     as_stream(stream));
   }
   size_t smem = 0;
   const int R = fm_pick_rows(D, d, true, g_w != nullptr, &smem);
@@ -281,7 +289,7 @@ extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, c
 #define RFA_LAUNCH(T)                                                                              \
   do {                                                                                             \
     cudaFuncSetAttribute(feature_map_bwd_kernel<T, T, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    feature_map_bwd_kernel<T, T, T><<<grid, kFmThreads, smem, st>>>((const T*)x, w, (const T*)g_phi, (T*)g_x, g_w, \
+    feature_map_bwd_kernel<T, T, T><<<grid, kFmThreads, smem, st>>>((const T*)x, w, row_mask, (const T*)g_phi, (T*)g_x, g_w, \
                                                                     rows, H, d, D, scale, R);      \
   } while (0)
   if (x_dtype == RFA_F16) RFA_LAUNCH(__half);
@@ -289,6 +297,12 @@ extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, c
   else return fail(RFA_EUNSUPPORTED, "feature_map_bwd: bad dtype %d", x_dtype);
 #undef RFA_LAUNCH
   return check_launch("rfa_feature_map_bwd");
+}
+
+extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, const void* g_phi, int g_dtype,
+                                   void* g_x, int gx_dtype, float* g_w, int64_t rows, int H, int d, int D,
+                                   float scale, rfa_stream_t stream) {
+  return rfa_feature_map_bwd_masked(x, x_dtype, w, nullptr, g_phi, g_dtype, g_x, gx_dtype, g_w, rows, H, d, D, scale, stream);
 }
 
 // ---------------------------------------------------------------------------

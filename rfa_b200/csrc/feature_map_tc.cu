@@ -17,7 +17,7 @@ enum { bFull = 0, bEmpty = 2, bU = 4, bUFree = 6, bEpi = 8, bNum = 9 };
 
 __global__ void __launch_bounds__(fm::kThreads_, 2)
 feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_phi,
-                          const float* __restrict__ w, int64_t rows, int H, float scale) {
+                          const float* __restrict__ w, const uint8_t* __restrict__ row_mask, int64_t rows, int H, float scale) {
   using namespace fm;
   extern __shared__ unsigned char fm_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fm_raw) + 1023) & ~uintptr_t(1023));
@@ -108,14 +108,16 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
         if (etid == 0) tma_store_wait_read<0>();
         if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(6); ok = false; break; }
       }
+      // a masked row (a padded key) gets all-zero features
+      const float sc_row = (row_mask && (int64_t)row0 + row < rows && row_mask[(int64_t)row0 + row]) ? 0.f : scale;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         float sn[8], cs[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           __sincosf(__uint_as_float(u[ch * 8 + e]) * inv, &sn[e], &cs[e]);
-          sn[e] *= scale;
-          cs[e] *= scale;
+          sn[e] *= sc_row;
+          cs[e] *= sc_row;
         }
         uint4 a, b;
         a.x = pack_half2(sn[0], sn[1]); a.y = pack_half2(sn[2], sn[3]); a.z = pack_half2(sn[4], sn[5]); a.w = pack_half2(sn[6], sn[7]);
@@ -139,7 +141,8 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
 }
 
 // x [rows][H][64] fp16, w [H][64][64] fp32, phi [rows][H][128] fp16
-int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int64_t rows, int H, float scale, int sms, cudaStream_t st) {
+int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* row_mask, __half* phi, int64_t rows, int H, float scale,
+                              int sms, cudaStream_t st) {
   CUtensorMap tx, tp;
   if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tp, phi, rows, H, 128, kTC))
     return fail(RFA_EDEVICE, "feature_map_fwd: cuTensorMapEncodeTiled failed or is unavailable");
@@ -149,7 +152,7 @@ int launch_feature_map_fwd_tc(const __half* x, const float* w, __half* phi, int6
   int64_t gx = 2LL * sms / H;                    // two CTAs per SM, and never more CTAs than fit at once
   if (gx > ntile) gx = ntile;
   if (gx < 1) gx = 1;
-  feature_map_fwd_tc_kernel<<<dim3((unsigned)gx, H), fm::kThreads_, fm::kSmem, st>>>(tx, tp, w, rows, H, scale);
+  feature_map_fwd_tc_kernel<<<dim3((unsigned)gx, H), fm::kThreads_, fm::kSmem, st>>>(tx, tp, w, row_mask, rows, H, scale);
   return check_launch("rfa_feature_map_fwd");
 }
 
@@ -182,7 +185,7 @@ enum { bFull = 0, bEmpty = 2, bU = 4, bUFree = 6, bGH = 8, bGHFree = 10, bGX = 1
 __global__ void __launch_bounds__(fmb::kThreads_, 1)
 feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gp,
                           const __grid_constant__ CUtensorMap tm_gx, const float* __restrict__ w, float* __restrict__ g_w,
-                          int64_t rows, int H, float scale) {
+                          const uint8_t* __restrict__ row_mask, int64_t rows, int H, float scale) {
   using namespace fmb;
   extern __shared__ unsigned char fmb_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fmb_raw) + 1023) & ~uintptr_t(1023));
@@ -284,6 +287,9 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
     for (int i = 0; i < ntile; ++i) {
       const int st = i & 1;
       unsigned char* base = sm + st * kStage;
+      const int64_t grow = (int64_t)(blockIdx.x + i * gridDim.x) * kTC + row;
+      // a masked row's features are constant zeros: no gradient flows through it
+      const float scale_row = (row_mask && grow < rows && row_mask[grow]) ? 0.f : scale;
       if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(16); break; }
       float ss = 0.f;                                  // |x|^2 of this thread's row
 #pragma unroll
@@ -307,7 +313,7 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       // the gh tile of this parity was last read by the products of tile i - 2
       if (i >= 2 && !mbar_wait(&bars[bGHFree + st], ((i >> 1) + 1) & 1)) { tc_fail(18); break; }
       rn[st * 128 + row] = make_float2(inv, n > 0.f ? inv / n : 0.f);
-      const float sc = scale * inv;
+      const float sc = scale_row * inv;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         const uint4 gs = *reinterpret_cast<const uint4*>(base + kGP + row_chunk1(row, ch));          // g_sin, columns 8 ch ..
@@ -409,8 +415,8 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
 }
 
 // x, g_x [rows][H][64] fp16, g_phi [rows][H][128] fp16, w [H][64][64] fp32, g_w [H][64][64] fp32 accumulated into (may be null)
-int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_phi, __half* g_x, float* g_w, int64_t rows, int H,
-                              float scale, int sms, cudaStream_t st) {
+int launch_feature_map_bwd_tc(const __half* x, const float* w, const uint8_t* row_mask, const __half* g_phi, __half* g_x, float* g_w,
+                              int64_t rows, int H, float scale, int sms, cudaStream_t st) {
   CUtensorMap tx, tg, to;
   if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tg, g_phi, rows, H, 128, kTC) || make_tmap_rows(&to, g_x, rows, H, 64, kTC))
     return fail(RFA_EDEVICE, "feature_map_bwd: cuTensorMapEncodeTiled failed or is unavailable");
@@ -420,7 +426,7 @@ int launch_feature_map_bwd_tc(const __half* x, const float* w, const __half* g_p
   int64_t gx = sms / H;                          // one CTA per SM (shared memory): never more CTAs than SMs, or a second wave runs
   if (gx > ntile) gx = ntile;
   if (gx < 1) gx = 1;
-  feature_map_bwd_tc_kernel<<<dim3((unsigned)gx, H), fmb::kThreads_, fmb::kSmem, st>>>(tx, tg, to, w, g_w, rows, H, scale);
+  feature_map_bwd_tc_kernel<<<dim3((unsigned)gx, H), fmb::kThreads_, fmb::kSmem, st>>>(tx, tg, to, w, g_w, row_mask, rows, H, scale);
   return check_launch("rfa_feature_map_bwd");
 }
 

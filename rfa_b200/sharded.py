@@ -89,7 +89,7 @@ def _group_size(group) -> int:
 def _carry(kern, packed: Tensor, group, reverse: bool, K: int, d: int):
     """The exchange step: every shard's packed total [BH, K*d + K] -> this shard's carry (s [BH,K,d], z [BH,K]).
     With a real process group the gathered totals are reduced by one kernel when the kernel set has one."""
-    if not isinstance(group, InProcessShards) and hasattr(kern, "scan_gathered"):
+    if not isinstance(group, InProcessShards) and hasattr(kern, "scan_gathered") and kern.packed_kernels(K, d):
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         return kern.scan_gathered(_all_gather(packed, group, world), rank, reverse)
     total = exclusive_scan_over_ranks(packed, group, reverse)
@@ -104,8 +104,18 @@ class _CudaKernels:
     value; the autograd function stores the tensors with ``save_for_backward``."""
 
     @staticmethod
+    def packed_kernels(K: int, d: int) -> bool:
+        """The packed-total / kept-workspace entry points exist for the tensor-core geometry only; other geometries take
+        the plain entry points (same results, a few more launches)."""
+        from . import ops
+        return (K, d) == (ops.K_BUILT, ops.D_BUILT)
+
+    @staticmethod
     def local_total(k: Tensor, v: Tensor):
         from . import ops
+        if not _CudaKernels.packed_kernels(k.shape[-1], v.shape[-1]):
+            s, z = ops.state_total(k, v)
+            return torch.cat([s.reshape(s.shape[0], -1), z], dim=1), None
         return ops.shard_total(k, v)
 
     @staticmethod
@@ -116,12 +126,17 @@ class _CudaKernels:
     @staticmethod
     def forward(q, k, v, s_in, z_in, ws):
         from . import _lib, ops
+        if not _CudaKernels.packed_kernels(q.shape[-1], v.shape[-1]):
+            return ops.causal_fwd(q, k, v, s_in, z_in), (), None
         out, ws, has = ops.causal_fwd_saved(q, k, v, s_in, z_in, ws, _lib.WS_PARTIALS if ws is not None else 0)
         return out, (out, ws), has
 
     @staticmethod
     def backward_q(q, k, v, g, s_in, z_in, kept, has):
         from . import ops
+        if not kept:
+            gq, ds, dz, ws = ops.causal_bwd_q(q, k, v, g, s_in, z_in, True)
+            return gq, torch.cat([ds.reshape(ds.shape[0], -1), dz], dim=1), ws
         out, ws = kept
         gq, dpacked = ops.causal_bwd_q_staged(q, k, v, g, out, s_in, z_in, ws, has)
         return gq, dpacked, ws

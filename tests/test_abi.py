@@ -30,8 +30,8 @@ def test_host_side_argument_checks_need_no_gpu():
     from rfa_b200 import _lib
     lib = _lib.load()
     # wrong geometry: rejected before any CUDA call
-    assert lib.rfa_causal_fwd(16, 16, 16, 16, None, None, None, None, None, 0, 8, 2, 96, 64, None) == -3
-    assert b"K=128" in lib.rfa_last_error()
+    assert lib.rfa_causal_fwd(16, 16, 16, 16, None, None, None, None, None, 0, 8, 2, 100, 64, None) == -3   # K not a multiple of 8
+    assert b"multiples of 8" in lib.rfa_last_error()
     assert lib.rfa_causal_fwd(None, None, None, None, None, None, None, None, None, 0, 8, 2, 128, 64, None) == -1
     assert lib.rfa_causal_fwd(8, 16, 16, 16, None, None, None, None, None, 0, 8, 2, 128, 64, None) == -2   # misaligned q
     assert lib.rfa_decode_step(16, 16, 16, 0, 16, 16, 1, 16, 4, 128, 63, None) == -3
@@ -46,7 +46,8 @@ def test_workspace_query_is_a_pure_function_of_the_geometry():
     lib = _lib.load()
     a = lib.rfa_causal_workspace_bytes(2048, 128, 128, 64)
     assert a == lib.rfa_causal_workspace_bytes(2048, 128, 128, 64) and a >= 2 * 2048 * 128 * 4
-    assert lib.rfa_causal_workspace_bytes(2048, 128, 96, 64) == 0
+    assert lib.rfa_causal_workspace_bytes(2048, 128, 100, 64) == 0          # no kernel for K % 8 != 0
+    assert lib.rfa_causal_workspace_bytes(2048, 128, 96, 64) >= 2 * 2048 * 128 * 4   # generic kernels: the per-token scalars
     # few heads + long sequence -> segmented plan needs room for boundary states
     assert lib.rfa_causal_workspace_bytes(131072, 32, 128, 64) > 2 * 131072 * 32 * 4 + 32 * 2 * 128 * 65 * 4
 

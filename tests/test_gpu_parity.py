@@ -109,6 +109,74 @@ def test_causal_saved_output_backward_with_carries(dev):
     assert_close(torch.cat([gv1, gv2]), rv, "gv")
 
 
+def generic_feats(T, BH, K, d, seed):
+    gen = torch.Generator().manual_seed(seed)
+    q = h16(torch.rand(T, BH, K, generator=gen) * 0.3 - 0.1)
+    k = h16(torch.rand(T, BH, K, generator=gen) * 0.3 - 0.1)
+    return q, k, h16(torch.randn(T, BH, d, generator=gen)), h16(torch.randn(T, BH, d, generator=gen))
+
+
+@pytest.mark.parametrize("K,d", [(64, 32), (256, 128), (96, 40), (128, 128)])
+def test_other_geometries_run_on_the_generic_kernels(dev, K, d):
+    """Feature widths / head dims other than 128 / 64 (upstream accepts any K % 16 == 0, d % 8 == 0): causal forward,
+    both backward forms (recomputing and RFA.apply's), state carries and the reverse-state total, against the oracle."""
+    from rfa_b200 import ops
+    from rfa_b200.rfa import RFA
+    T, BH, cut = 150, 3, 90
+    q, k, v, g = generic_feats(T, BH, K, d, seed=K + d)
+    c = lambda t: t.half().to(dev)
+    ro = O.causal_forward(q, k, v); rq, rk, rv = O.causal_backward(q, k, v, g)
+    out = ops.causal_fwd(c(q), c(k), c(v)); gq, gk, gv = ops.causal_bwd(c(q), c(k), c(v), c(g))
+    assert_close(out, ro, "out"); assert_close(gq, rq, "gq"); assert_close(gk, rk, "gk"); assert_close(gv, rv, "gv")
+    leaves = [c(t).requires_grad_(True) for t in (q, k, v)]
+    RFA.apply(*leaves).backward(c(g))
+    for name, leaf, ref in zip(("gq", "gk", "gv"), leaves, (rq, rk, rv)):
+        assert_close(leaf.grad, ref, f"RFA.apply {name}")
+    # split run: state carried in and out, reverse-state total handed back
+    o1, s, z = ops.causal_fwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), return_state=True)
+    o2, s2, z2 = ops.causal_fwd(c(q[cut:]), c(k[cut:]), c(v[cut:]), s, z, return_state=True)
+    assert_close(torch.cat([o1, o2]), ro, "out (split)")
+    rs, rz = O.segment_state(k, v)
+    assert_close(s2, rs, "S", rel=1e-4); assert_close(z2, rz, "z", rel=1e-4)
+    gq2, ds, dz, ws2 = ops.causal_bwd_q(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), s, z, True)
+    gk2, gv2 = ops.causal_bwd_kv(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), None, None, ws2)
+    gq1, gk1, gv1 = ops.causal_bwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), c(g[:cut]), None, None, ds, dz)
+    assert_close(torch.cat([gq1, gq2]), rq, "gq (split)"); assert_close(torch.cat([gk1, gk2]), rk, "gk (split)")
+    assert_close(torch.cat([gv1, gv2]), rv, "gv (split)")
+
+
+def test_cross_attention_other_geometry(dev):
+    Tq, Ts, B, H, K, d = 70, 45, 2, 3, 64, 32
+    q, _, _, _ = generic_feats(Tq, B * H, K, d, seed=1)
+    _, k, v, _ = generic_feats(Ts, B * H, K, d, seed=2)
+    pq, pk, v = q.view(Tq, B, H, K), k.view(Ts, B, H, K), v.view(Ts, B, H, d)
+    g = h16(torch.randn(Tq, B, H, d, generator=torch.Generator().manual_seed(3)))
+    pad = torch.arange(Ts)[None] >= torch.tensor([Ts, 20])[:, None]
+    attn, s, z, gq, gk, gv = run_cross(dev, pq, pk, v, g, pad)
+    rs, rz = O.cross_state(pk, v, pad)
+    assert_close(s, rs, "s", rel=1e-4); assert_close(z, rz, "z", rel=1e-4)
+    assert_close(attn, O.cross_query(pq, rs, rz), "attn")
+    rq, rk, rv = O.cross_backward(pq, pk, v, g, pad)
+    assert_close(gq, rq, "g_phi_q"); assert_close(gk, rk, "g_phi_k"); assert_close(gv, rv, "g_v")
+    assert (gk.cpu()[pad.T] == 0).all() and (gv.cpu()[pad.T] == 0).all()
+
+
+def test_module_with_another_head_dim(dev):
+    """CausalAttention(head_dim=32, proj_dim=32) end to end (feature map, causal kernel, decode) against its own
+    incremental form."""
+    from rfa_b200 import CausalAttention
+    torch.manual_seed(0)
+    mod = CausalAttention(embed_dim=64, num_heads=2, head_dim=32, proj_dim=32, tau=1.0).to(dev)
+    w = torch.from_numpy(O.draw_matrices("orf", 2, 32, 32, 9)).float().to(dev)
+    x = torch.randn(6, 2, 64, device=dev)
+    y = mod(x, w)
+    st = {}
+    ys = torch.cat([mod(x[i:i + 1], w, saved_state=st) for i in range(6)])
+    assert_close(ys, y.detach().float().cpu(), "incremental vs full", rel=4e-3)
+    y.sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in mod.parameters())
+
+
 def test_causal_unclamped_large_denominators(dev):
     """Positive features so that q.z >> 1 everywhere except the first tokens."""
     gen = torch.Generator().manual_seed(4)
@@ -412,9 +480,9 @@ def test_modules_against_upstream_fixture(dev):
 # ----------------------------------------------------------------------------- argument checking
 def test_bad_arguments_are_rejected_without_launching(dev):
     from rfa_b200 import ops
-    q = torch.zeros(8, 2, 96, dtype=torch.half, device=dev)
+    q = torch.zeros(8, 2, 100, dtype=torch.half, device=dev)
     v = torch.zeros(8, 2, 64, dtype=torch.half, device=dev)
-    with pytest.raises(ValueError, match="only K=128"):
+    with pytest.raises(ValueError, match="multiples of 8"):
         ops.causal_fwd(q, q, v)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         ops.causal_fwd(q.cpu(), q.cpu(), v.cpu())
