@@ -190,8 +190,10 @@ class CausalAttention(nn.Module):
         w = build_random_matrices(random_matrices=random_matrices, tau=self.tau,
                                   sigma=self.sigma if self.reparam_proj else None,
                                   reparam_proj=self.reparam_proj)
+        # the padding mask of the kernel path is applied inside the feature map of k (no separate pass over phi_k)
+        fused_mask = key_padding_mask if (saved_state is None and self.cuda_causal_rfa) else None
         phi_q = random_project(x=q, random_matrices=w)
-        phi_k = random_project(x=k, random_matrices=w)
+        phi_k = random_project(x=k, random_matrices=w, key_padding_mask=fused_mask)
         if saved_state is not None:
             assert tgt_len == 1
             prev_s, prev_z = saved_state.get("prev_s"), saved_state.get("prev_z")
@@ -199,7 +201,7 @@ class CausalAttention(nn.Module):
             attn, s, z = incremental_rfa(phi_q=phi_q, phi_k=phi_k, v=v, s=prev_s, z=prev_z)
             saved_state["prev_s"], saved_state["prev_z"] = s, z
         elif self.cuda_causal_rfa:
-            attn = cuda_causal_rfa(phi_q=phi_q, phi_k=phi_k, v=v, key_padding_mask=key_padding_mask)
+            attn = cuda_causal_rfa(phi_q=phi_q, phi_k=phi_k, v=v, key_padding_mask=None)
         else:
             attn = masked_rfa(phi_q=phi_q, phi_k=phi_k, v=v, attn_mask=attn_mask,
                               key_padding_mask=key_padding_mask)

@@ -44,21 +44,33 @@ def _workspace(T: int, BH: int, K: int, d: int, like: Tensor) -> Tuple[Tensor, i
 
 
 # --------------------------------------------------------------------------- feature map
-def feature_map_fwd(x: Tensor, w: Tensor, scale: float, out_dtype: Optional[torch.dtype] = None) -> Tensor:
-    """x [..., H, d], w [H, D, d] fp32 -> phi [..., H, 2D]."""
+def _row_mask(row_mask: Optional[Tensor], rows: int, dev) -> Optional[Tensor]:
+    if row_mask is None:
+        return None
+    m = (row_mask.to(device=dev).reshape(-1) != 0).to(torch.uint8).contiguous()
+    assert m.numel() == rows, (m.numel(), rows)
+    return m
+
+
+def feature_map_fwd(x: Tensor, w: Tensor, scale: float, out_dtype: Optional[torch.dtype] = None,
+                    row_mask: Optional[Tensor] = None) -> Tensor:
+    """x [..., H, d], w [H, D, d] fp32 -> phi [..., H, 2D].  row_mask (one entry per leading index, non-zero = masked):
+    those rows get all-zero features."""
     H, D, d = w.shape
     assert x.shape[-2] == H and x.shape[-1] == d, (x.shape, w.shape)
     x = x.contiguous()
     w = w.contiguous().float()
     phi = torch.empty(*x.shape[:-1], 2 * D, dtype=out_dtype or x.dtype, device=x.device)
     rows = x.numel() // (H * d)
+    m = _row_mask(row_mask, rows, x.device)
     with _guard(x):
-        check(_lib.load().rfa_feature_map_fwd(ptr(x), dtype_code(x), ptr(w), ptr(phi), dtype_code(phi),
-                                              rows, H, d, D, float(scale), stream_of(x)), "rfa_feature_map_fwd")
+        check(_lib.load().rfa_feature_map_fwd_masked(ptr(x), dtype_code(x), ptr(w), ptr(m), ptr(phi), dtype_code(phi),
+                                                     rows, H, d, D, float(scale), stream_of(x)), "rfa_feature_map_fwd")
     return phi
 
 
-def feature_map_bwd(x: Tensor, w: Tensor, g_phi: Tensor, scale: float, need_gw: bool) -> Tuple[Tensor, Optional[Tensor]]:
+def feature_map_bwd(x: Tensor, w: Tensor, g_phi: Tensor, scale: float, need_gw: bool,
+                    row_mask: Optional[Tensor] = None) -> Tuple[Tensor, Optional[Tensor]]:
     H, D, d = w.shape
     x = x.contiguous()
     w = w.contiguous().float()
@@ -66,10 +78,11 @@ def feature_map_bwd(x: Tensor, w: Tensor, g_phi: Tensor, scale: float, need_gw: 
     g_x = torch.empty_like(x)
     g_w = torch.zeros(H, D, d, dtype=torch.float32, device=x.device) if need_gw else None
     rows = x.numel() // (H * d)
+    m = _row_mask(row_mask, rows, x.device)
     with _guard(x):
-        check(_lib.load().rfa_feature_map_bwd(ptr(x), dtype_code(x), ptr(w), ptr(g_phi), dtype_code(g_phi),
-                                              ptr(g_x), dtype_code(g_x), ptr(g_w), rows, H, d, D, float(scale),
-                                              stream_of(x)), "rfa_feature_map_bwd")
+        check(_lib.load().rfa_feature_map_bwd_masked(ptr(x), dtype_code(x), ptr(w), ptr(m), ptr(g_phi), dtype_code(g_phi),
+                                                     ptr(g_x), dtype_code(g_x), ptr(g_w), rows, H, d, D, float(scale),
+                                                     stream_of(x)), "rfa_feature_map_bwd")
     return g_x, g_w
 
 

@@ -151,24 +151,33 @@ class _FeatureMap(torch.autograd.Function):
     """phi(x) = SCALE * [sin(W xhat) | cos(W xhat)] with xhat = x / (|x| + 1e-3)."""
 
     @staticmethod
-    def forward(ctx, x, w, scale):
+    def forward(ctx, x, w, scale, row_mask):
         ctx.save_for_backward(x, w)
-        ctx.scale = scale
-        return ops.feature_map_fwd(x, w, scale)
+        ctx.scale, ctx.row_mask = scale, row_mask
+        return ops.feature_map_fwd(x, w, scale, row_mask=row_mask)
 
     @staticmethod
     def backward(ctx, g_phi):
         x, w = ctx.saved_tensors
         need_w = ctx.needs_input_grad[1]
-        g_x, g_w = ops.feature_map_bwd(x, w, g_phi, ctx.scale, need_w)
-        return g_x, (g_w.to(w.dtype) if need_w else None), None
+        g_x, g_w = ops.feature_map_bwd(x, w, g_phi, ctx.scale, need_w, row_mask=ctx.row_mask)
+        return g_x, (g_w.to(w.dtype) if need_w else None), None, None
 
 
-def random_project(*, x: Tensor, random_matrices: Tensor, scale: float = SCALE) -> Tensor:
+def random_project(*, x: Tensor, random_matrices: Tensor, scale: float = SCALE,
+                   key_padding_mask: Optional[Tensor] = None) -> Tensor:
     """x ``[seq_len, bsz, num_heads, head_dim]``, random_matrices ``[num_heads, proj_dim,
     head_dim]`` -> phi ``[seq_len, bsz, num_heads, 2 * proj_dim]`` in x's dtype
-    (upstream utils.py:105-120; ``scale`` defaults to upstream's constant 0.1)."""
-    return _FeatureMap.apply(x, random_matrices, scale)
+    (upstream utils.py:105-120; ``scale`` defaults to upstream's constant 0.1).
+
+    ``key_padding_mask`` ``[bsz, seq_len]`` (1 = padding; an addition): the features of padded positions come out as
+    zeros, inside the kernel -- what upstream's ``cuda_causal_rfa`` does to phi_k with a separate ``masked_fill`` pass
+    (causal_attention.py:137-143)."""
+    row_mask = None
+    if key_padding_mask is not None and key_padding_mask.dim() > 0:
+        assert key_padding_mask.shape == (x.size(1), x.size(0)), (key_padding_mask.shape, x.shape)
+        row_mask = key_padding_mask.to(torch.bool).t().contiguous()          # [seq_len, bsz]: one entry per row of x
+    return _FeatureMap.apply(x, random_matrices, scale, row_mask)
 
 
 def normalize_attn_weights(x: Tensor, dim: int = -1, dtype: torch.dtype = torch.float32) -> Tensor:

@@ -138,6 +138,10 @@ def test_other_geometries_run_on_the_generic_kernels(dev, K, d):
     assert_close(torch.cat([o1, o2]), ro, "out (split)")
     rs, rz = O.segment_state(k, v)
     assert_close(s2, rs, "S", rel=1e-4); assert_close(z2, rz, "z", rel=1e-4)
+    if (K, d) == (256, 128):      # the reverse-state total needs a second state in shared memory, which does not fit here
+        with pytest.raises(ValueError, match="two of them"):
+            ops.causal_bwd_q(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), s, z, True)
+        return
     gq2, ds, dz, ws2 = ops.causal_bwd_q(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), s, z, True)
     gk2, gv2 = ops.causal_bwd_kv(c(q[cut:]), c(k[cut:]), c(v[cut:]), c(g[cut:]), None, None, ws2)
     gq1, gk1, gv1 = ops.causal_bwd(c(q[:cut]), c(k[:cut]), c(v[:cut]), c(g[:cut]), None, None, ds, dz)
@@ -274,6 +278,30 @@ def test_feature_map_against_upstream_fixture(dev):
     assert_close(x.grad, g["g_x"], "g_x"); assert_close(w.grad, g["g_w"], "g_w", rel=2e-3, mabs=5e-2)
     x32 = g["x"].to(dev)
     assert_close(utils.random_project(x=x32, random_matrices=g["w"].to(dev)), g["phi_plain"], "phi fp32", rel=1e-5, mabs=1e-6)
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.half, 64), (torch.float32, 64), (torch.half, 32)])
+def test_feature_map_with_padding_mask(dev, dtype, d):
+    """random_project(key_padding_mask=...) == random_project followed by upstream's masked_fill (forward and gradients),
+    on the tensor-core kernel (fp16, 64) and the generic ones."""
+    from rfa_b200 import utils
+    gen = torch.Generator().manual_seed(d)
+    T, B, H = 150, 3, 2
+    x = h16(torch.randn(T, B, H, d, generator=gen))
+    w = torch.randn(H, d, d, generator=gen)
+    gp = h16(torch.randn(T, B, H, 2 * d, generator=gen))
+    pad = torch.arange(T)[None] >= torch.tensor([T, 100, 1])[:, None]              # [B, T]
+    xd = x.to(dev, dtype).requires_grad_(True); wd = w.to(dev).requires_grad_(True)
+    phi = utils.random_project(x=xd, random_matrices=wd, key_padding_mask=pad.to(dev))
+    (phi.float() * gp.to(dev)).sum().backward()
+    xr = x.clone().requires_grad_(True); wr = w.clone().requires_grad_(True)
+    ref = O.random_project(xr, wr).masked_fill(pad.t()[:, :, None, None], 0.0)
+    (ref * gp).sum().backward()
+    tol = dict(rel=2e-3, mabs=2e-4) if dtype == torch.half else dict(rel=1e-5, mabs=1e-6)
+    assert_close(phi, ref.detach(), "phi", **tol)
+    assert (phi.float().cpu()[pad.t()] == 0).all() and (xd.grad.float().cpu()[pad.t()] == 0).all()
+    assert_close(xd.grad, xr.grad, "g_x", rel=2e-3 if dtype == torch.half else 1e-4, mabs=1e-2)
+    assert_close(wd.grad, wr.grad, "g_w", rel=2e-3 if dtype == torch.half else 1e-4, mabs=5e-2)
 
 
 @pytest.mark.parametrize("rows,H,d,D", [(1, 1, 64, 64), (77, 3, 64, 64), (130, 2, 32, 48), (65, 2, 128, 128), (9, 5, 16, 8)])
