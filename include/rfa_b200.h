@@ -302,6 +302,16 @@ int rfa_decode_step_fused(const void* q, const void* k, const void* v, int in_dt
                           void* s, void* z, int state_dtype, void* out,
                           int BH, int H, int D, int d, rfa_stream_t stream);
 
+/* One decoding step of cross attention for all L layers in one launch:
+ *   out[l] = phi_q[l] . s_l / max(|phi_q[l] . z_l|, 1)
+ * phi_q [L,BH,K], out [L,BH,d] of in_dtype; s_ptrs / z_ptrs: DEVICE arrays of L
+ * pointers to the layers' fp32 states [BH,K,d] / [BH,K] (16-byte aligned; they do
+ * not change while a sequence is decoded, so the arrays are built once).
+ * replaces L calls of CrossAttention.rfa with tgt_len 1 (cross_attention.py:266-269). */
+int rfa_cross_decode_step(const void* phi_q, int in_dtype,
+                          const float* const* s_ptrs, const float* const* z_ptrs,
+                          void* out, int L, int BH, int K, int d, rfa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -201,6 +201,62 @@ decode_step_fused_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
   decode_body<TIn, TState>(pq, pk, vs, S + bh * (size_t)K * d, z + bh * K, out + bh * d, red, den_s, K, d, buf);
 }
 
+// One decoding step of cross attention for ALL layers in one launch: the states do not change while a sequence is
+// decoded, so a step only streams them:  out[l] = phi_q[l] . s_l / max(|phi_q[l] . z_l|, 1)  (upstream
+// cross_attention.py:266-269, called once per layer).  grid (BH, L); the layers' states are separate arrays, reached
+// through device arrays of pointers.
+template <typename TIn>
+__global__ void __launch_bounds__(kDecodeThreads, 7)
+cross_decode_kernel(const TIn* __restrict__ phi_q, const float* const* __restrict__ s_ptrs, const float* const* __restrict__ z_ptrs,
+                    TIn* __restrict__ out, int BH, int K, int d) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float4* red = reinterpret_cast<float4*>(smem_raw);                 // kDecodeThreads float4
+  float* pq = reinterpret_cast<float*>(red + kDecodeThreads);        // K
+  float* den_s = pq + K;
+  const size_t bh = blockIdx.x, l = blockIdx.y;
+  const float* S = s_ptrs[l] + bh * (size_t)K * d;
+  const float* z = z_ptrs[l] + bh * (size_t)K;
+  const int tid = threadIdx.x;
+  float4 buf[kDecodePrefetch];
+  decode_prefetch(S, K, d, buf);
+  for (int i = tid; i < K; i += kDecodeThreads) pq[i] = to_f(phi_q[(l * BH + bh) * K + i]);
+  __syncthreads();
+  if (tid < 32) {
+    float part = 0.f;
+    for (int k = tid; k < K; k += 32) part = fmaf(pq[k], z[k], part);
+    part = warp_sum(part);
+    if (tid == 0) *den_s = fmaxf(fabsf(part), kEps);
+  }
+  const int d4 = d >> 2, rows = kDecodeThreads / d4;
+  const int c = tid % d4, r0 = tid / d4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int u = 0; u < kDecodePrefetch; ++u) {
+    const int kk = r0 + u * rows;
+    if (kk < K) {
+      const float b = pq[kk];
+      acc.x = fmaf(b, buf[u].x, acc.x); acc.y = fmaf(b, buf[u].y, acc.y); acc.z = fmaf(b, buf[u].z, acc.z); acc.w = fmaf(b, buf[u].w, acc.w);
+    }
+  }
+  for (int k = r0 + kDecodePrefetch * rows; k < K; k += rows) {
+    const float4 t = load4(S + (size_t)k * d + 4 * c);
+    const float b = pq[k];
+    acc.x = fmaf(b, t.x, acc.x); acc.y = fmaf(b, t.y, acc.y); acc.z = fmaf(b, t.z, acc.z); acc.w = fmaf(b, t.w, acc.w);
+  }
+  red[tid] = acc;
+  __syncthreads();
+  if (tid < d4) {
+    float4 t = red[tid];
+    for (int r = 1; r < rows; ++r) {
+      const float4 u = red[r * d4 + tid];
+      t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+    }
+    const float inv = 1.f / *den_s;
+    t.x *= inv; t.y *= inv; t.z *= inv; t.w *= inv;
+    store4(out + (l * BH + bh) * d + 4 * tid, t);
+  }
+}
+
 static int check_decode_dtypes(const char* what, int in_dtype, int state_dtype) {
   const bool ok = (in_dtype == RFA_F16 && (state_dtype == RFA_F32 || state_dtype == RFA_F16)) ||
                   (in_dtype == RFA_F32 && state_dtype == RFA_F32);
@@ -266,4 +322,20 @@ extern "C" int rfa_decode_step_fused(const void* q, const void* k, const void* v
   else return fail(RFA_EUNSUPPORTED, "decode_fused: unsupported dtype pair in=%d state=%d", in_dtype, state_dtype);
 #undef RFA_LAUNCH
   return check_launch("rfa_decode_step_fused");
+}
+
+extern "C" int rfa_cross_decode_step(const void* phi_q, int in_dtype, const float* const* s_ptrs, const float* const* z_ptrs,
+                                     void* out, int L, int BH, int K, int d, rfa_stream_t stream) {
+  RFA_REQUIRE(phi_q && s_ptrs && z_ptrs && out, RFA_EINVAL, "cross_decode: null pointer");
+  RFA_REQUIRE(L > 0 && L <= 65535, RFA_EINVAL, "cross_decode: L=%d", L);
+  if (int e = check_decode_geometry(BH, K, d)) return e;
+  RFA_REQUIRE(in_dtype == RFA_F16 || in_dtype == RFA_F32, RFA_EUNSUPPORTED, "cross_decode: dtype %d", in_dtype);
+  RFA_REQUIRE(aligned16(phi_q) && aligned16(out), RFA_EALIGN, "cross_decode: pointers must be 16-byte aligned");
+  const size_t smem = kDecodeThreads * sizeof(float4) + (K + 4) * sizeof(float);
+  const dim3 grid(BH, L);
+  if (in_dtype == RFA_F16)
+    cross_decode_kernel<__half><<<grid, kDecodeThreads, smem, as_stream(stream)>>>((const __half*)phi_q, s_ptrs, z_ptrs, (__half*)out, BH, K, d);
+  else
+    cross_decode_kernel<float><<<grid, kDecodeThreads, smem, as_stream(stream)>>>((const float*)phi_q, s_ptrs, z_ptrs, (float*)out, BH, K, d);
+  return check_launch("rfa_cross_decode_step");
 }

@@ -404,3 +404,35 @@ def decode_step_fused(q: Tensor, k: Tensor, v: Tensor, w: Tensor, scale: float, 
                                                 ptr(z), dtype_code(s), ptr(out), B * H, H, D, d, stream_of(v)),
               "rfa_decode_step_fused")
     return out
+
+
+class CrossDecodeStates:
+    """The cross-attention states of all layers of a decoder, gathered once per sequence for ``cross_decode_step``:
+    device arrays of pointers to each layer's ``s [B,H,K,d]`` and ``z [B,H,K]`` (fp32, contiguous).  The states are
+    referenced, not copied; keep them alive and unchanged while this object is used."""
+
+    def __init__(self, states):
+        self.s = [st[0].contiguous() for st in states]
+        self.z = [st[1].contiguous() for st in states]
+        for t in self.s + self.z:
+            if not t.is_cuda or t.dtype != torch.float32:
+                raise TypeError("rfa_b200: cross-attention states must be fp32 CUDA tensors")
+        self.L = len(self.s)
+        B, H, self.K, self.d = self.s[0].shape
+        self.BH = B * H
+        dev = self.s[0].device
+        self.s_ptrs = torch.tensor([t.data_ptr() for t in self.s], dtype=torch.int64, device=dev)
+        self.z_ptrs = torch.tensor([t.data_ptr() for t in self.z], dtype=torch.int64, device=dev)
+
+
+def cross_decode_step(phi_q: Tensor, states: CrossDecodeStates, out: Optional[Tensor] = None) -> Tensor:
+    """phi_q [L, B, H, K] (one token's query features for every layer) -> out [L, B, H, d], one launch for all layers."""
+    L, B, H, K = phi_q.shape
+    assert (L, B * H, K) == (states.L, states.BH, states.K), (phi_q.shape, states.L, states.BH, states.K)
+    phi_q = phi_q.contiguous()
+    if out is None:
+        out = torch.empty(L, B, H, states.d, dtype=phi_q.dtype, device=phi_q.device)
+    with _guard(phi_q):
+        check(_lib.load().rfa_cross_decode_step(ptr(phi_q), dtype_code(phi_q), ptr(states.s_ptrs), ptr(states.z_ptrs), ptr(out),
+                                                L, B * H, K, states.d, stream_of(phi_q)), "rfa_cross_decode_step")
+    return out

@@ -477,6 +477,21 @@ def test_cross_vs_oracle_ragged(dev, Tq, Ts, B, H):
     assert_close(gq, rq, "g_phi_q"); assert_close(gk, rk, "g_phi_k"); assert_close(gv, rv, "g_v")
 
 
+def test_cross_decode_step_all_layers_in_one_launch(dev):
+    from rfa_b200 import ops
+    L, B, H, K, d = 3, 2, 4, 128, 64
+    gen = torch.Generator().manual_seed(8)
+    states, refs = [], []
+    pq = h16(torch.rand(L, B, H, K, generator=gen) * 0.3 - 0.1)
+    for l in range(L):
+        s = torch.randn(B, H, K, d, generator=gen) * (1.0 if l else 40.0)          # layer 0: denominators beyond the clamp
+        z = torch.randn(B, H, K, generator=gen) * (1.0 if l else 40.0)
+        states.append((s.to(dev), z.to(dev)))
+        refs.append(O.cross_query(pq[l][None], s, z))
+    out = ops.cross_decode_step(pq.half().to(dev), ops.CrossDecodeStates(states))
+    assert_close(out.view(L, 1, B, H * d), torch.stack(refs).view(L, 1, B, H * d), "cross decode step")
+
+
 # ----------------------------------------------------------------------------- modules
 def test_modules_against_upstream_fixture(dev):
     from rfa_b200 import CausalAttention, CrossAttention
