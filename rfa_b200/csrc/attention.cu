@@ -8,6 +8,7 @@
 // the states at their boundaries come from a reduction pre-pass plus an exclusive scan, the
 // same primitive a multi-device split of the sequence uses.
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace rfa {
 
@@ -118,6 +119,8 @@ __device__ __forceinline__ float* state_elem(float* s_seg, float* z_seg, size_t 
 // order), seeded with carry_s [BH][K*d] / carry_z [BH][K] (may be null).
 __global__ void scan_states_kernel(float* __restrict__ s_seg, float* __restrict__ z_seg, const float* __restrict__ carry_s,
                                    const float* __restrict__ carry_z, int BH, int nseg, int reverse) {
+  sm100::pdl_wait();
+  sm100::pdl_launch_dependents();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)BH * kStateN) return;
   const size_t bh = i / kStateN;
@@ -135,6 +138,8 @@ __global__ void scan_states_kernel(float* __restrict__ s_seg, float* __restrict_
 // Sum over the segment axis -> packed [BH][K*d + K] and / or the two plain arrays tot_s [BH][K*d], tot_z [BH][K].
 __global__ void total_states_kernel(const float* __restrict__ s_seg, const float* __restrict__ z_seg, float* __restrict__ packed,
                                     float* __restrict__ tot_s, float* __restrict__ tot_z, int BH, int nseg) {
+  sm100::pdl_wait();
+  sm100::pdl_launch_dependents();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)BH * kStateN) return;
   const size_t bh = i / kStateN;
@@ -152,6 +157,8 @@ __global__ void total_states_kernel(const float* __restrict__ s_seg, const float
 // shard `rank`, written as the two plain arrays a kernel takes as its carry.
 __global__ void scan_gathered_kernel(const float* __restrict__ gathered, int world, int rank, int reverse,
                                      float* __restrict__ out_s, float* __restrict__ out_z, int BH) {
+  sm100::pdl_wait();
+  sm100::pdl_launch_dependents();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t n = (size_t)BH * kStateN;
   if (i >= n) return;
@@ -184,13 +191,13 @@ static unsigned state_blocks(int BH) { return (unsigned)(((size_t)BH * kStateN +
 
 static int scan_launch(float* s_seg, float* z_seg, const float* carry_s, const float* carry_z, int BH, int nseg, int reverse,
                        cudaStream_t st) {
-  scan_states_kernel<<<state_blocks(BH), 256, 0, st>>>(s_seg, z_seg, carry_s, carry_z, BH, nseg, reverse);
+  sm100::launch_pdl(scan_states_kernel, dim3(state_blocks(BH)), dim3(256), 0, st, s_seg, z_seg, carry_s, carry_z, BH, nseg, reverse);
   return check_launch("scan_states");
 }
 
 static int total_launch(const float* s_seg, const float* z_seg, float* packed, float* tot_s, float* tot_z, int BH, int nseg,
                         cudaStream_t st) {
-  total_states_kernel<<<state_blocks(BH), 256, 0, st>>>(s_seg, z_seg, packed, tot_s, tot_z, BH, nseg);
+  sm100::launch_pdl(total_states_kernel, dim3(state_blocks(BH)), dim3(256), 0, st, s_seg, z_seg, packed, tot_s, tot_z, BH, nseg);
   return check_launch("total_states");
 }
 
@@ -302,7 +309,7 @@ extern "C" int rfa_exclusive_scan_gathered(const float* gathered, int world, int
   if (int e = check_geometry("exclusive_scan_gathered", 0, BH, K, d, false)) return e;
   RFA_REQUIRE(gathered && s_out && z_out, RFA_EINVAL, "exclusive_scan_gathered: null pointer");
   RFA_REQUIRE(world > 0 && rank >= 0 && rank < world, RFA_EINVAL, "exclusive_scan_gathered: rank %d of %d", rank, world);
-  scan_gathered_kernel<<<state_blocks(BH), 256, 0, as_stream(stream)>>>(gathered, world, rank, reverse ? 1 : 0, s_out, z_out, BH);
+  sm100::launch_pdl(scan_gathered_kernel, dim3(state_blocks(BH)), dim3(256), 0, as_stream(stream), gathered, world, rank, reverse ? 1 : 0, s_out, z_out, BH);
   return check_launch("rfa_exclusive_scan_gathered");
 }
 

@@ -86,6 +86,8 @@ causal_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                   // everything above may overlap the tail of the previous kernel in the stream
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (chunks in reverse time order)
@@ -445,7 +447,7 @@ int launch_causal_bwd_kv_tc(const __half* q, const __half* k, const __half* v, c
     return fail(RFA_EDEVICE, "causal_bwd_kv: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(causal_bwd_kv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kvSmem);
   if (e != cudaSuccess) return fail((int)e, "causal_bwd_kv: cannot reserve %u bytes of shared memory: %s", kvSmem, cudaGetErrorString(e));
-  causal_bwd_kv_tc_kernel<<<dim3(BH, nseg), kKvThreads, kvSmem, st>>>(tq, tk, tv, tg, gk, gv, ws_den, ws_gz, ds_seg, dz_seg,
+  launch_pdl(causal_bwd_kv_tc_kernel, dim3(BH, nseg), dim3(kKvThreads), kvSmem, st, tq, tk, tv, tg, gk, gv, ws_den, ws_gz, ds_seg, dz_seg,
                                                                      T, BH, nseg, tseg);
   return check_launch("rfa_causal_bwd_kv");
 }

@@ -99,6 +99,8 @@ causal_bwd_q_saved_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                   // everything above may overlap the tail of the previous kernel in the stream
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -449,14 +451,14 @@ int launch_causal_bwd_q_saved_tc(const __half* q, const __half* k, const __half*
     constexpr uint32_t smem = BsLayout<true>::Smem;
     e = cudaFuncSetAttribute(causal_bwd_q_saved_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail((int)e, "causal_bwd_q_saved: cannot reserve %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    causal_bwd_q_saved_tc_kernel<true><<<dim3(BH, nseg), kBsThreads, smem, st>>>(tq, tk, tv, tg, tgq, out, den_raw, gq, s_seg, z_seg,
-                                                                               ws_gz, ds_seg, dz_seg, T, BH, nseg, tseg);
+    launch_pdl(causal_bwd_q_saved_tc_kernel<true>, dim3(BH, nseg), dim3(kBsThreads), smem, st, tq, tk, tv, tg, tgq, out, den_raw, gq, s_seg, z_seg,
+               ws_gz, ds_seg, dz_seg, T, BH, nseg, tseg);
   } else {
     constexpr uint32_t smem = BsLayout<false>::Smem;
     e = cudaFuncSetAttribute(causal_bwd_q_saved_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail((int)e, "causal_bwd_q_saved: cannot reserve %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    causal_bwd_q_saved_tc_kernel<false><<<dim3(BH, nseg), kBsThreads, smem, st>>>(tq, tk, tv, tg, tgq, out, den_raw, gq, s_seg, z_seg,
-                                                                                ws_gz, ds_seg, dz_seg, T, BH, nseg, tseg);
+    launch_pdl(causal_bwd_q_saved_tc_kernel<false>, dim3(BH, nseg), dim3(kBsThreads), smem, st, tq, tk, tv, tg, tgq, out, den_raw, gq, s_seg, z_seg,
+               ws_gz, ds_seg, dz_seg, T, BH, nseg, tseg);
   }
   return check_launch("rfa_causal_bwd_q_saved");
 }

@@ -100,6 +100,8 @@ causal_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                   // everything above may overlap the tail of the previous kernel in the stream
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -469,7 +471,7 @@ int launch_causal_bwd_q_tc(const __half* q, const __half* k, const __half* v, co
     return fail(RFA_EDEVICE, "causal_bwd_q: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(causal_bwd_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bqSmem);
   if (e != cudaSuccess) return fail((int)e, "causal_bwd_q: cannot reserve %u bytes of shared memory: %s", bqSmem, cudaGetErrorString(e));
-  causal_bwd_q_tc_kernel<<<dim3(BH, nseg), kBqThreads, bqSmem, st>>>(tq, tk, tv, tg, gq, s_seg, z_seg, ws_den, ws_gz, ds_seg,
+  launch_pdl(causal_bwd_q_tc_kernel, dim3(BH, nseg), dim3(kBqThreads), bqSmem, st, tq, tk, tv, tg, gq, s_seg, z_seg, ws_den, ws_gz, ds_seg,
                                                                     dz_seg, T, BH, nseg, tseg);
   return check_launch("rfa_causal_bwd_q");
 }

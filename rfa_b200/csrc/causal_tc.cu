@@ -101,6 +101,8 @@ causal_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                   // everything above may overlap the tail of the previous kernel in the stream
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -364,7 +366,7 @@ int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __ha
     return fail(RFA_EDEVICE, "causal_fwd: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(causal_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwSmem);
   if (e != cudaSuccess) return fail((int)e, "causal_fwd: cannot reserve %u bytes of shared memory: %s", kFwSmem, cudaGetErrorString(e));
-  causal_fwd_tc_kernel<<<dim3(BH, nseg), kFwThreads, kFwSmem, st>>>(tq, tk, tv, to, s_seg, z_seg, s_out, z_out, den_out, T, BH, nseg, tseg);
+  launch_pdl(causal_fwd_tc_kernel, dim3(BH, nseg), dim3(kFwThreads), kFwSmem, st, tq, tk, tv, to, s_seg, z_seg, s_out, z_out, den_out, T, BH, nseg, tseg);
   return check_launch("rfa_causal_fwd");
 }
 

@@ -30,6 +30,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched with launch_pdl() may start while the previous kernel in the stream is still draining: its CTAs are
+// placed as soon as an SM has room, run their prologue (barrier init, TMEM allocation, descriptor prefetch) and then
+// stop in pdl_wait() until the previous kernel has completed and its writes are visible.  Nothing that reads or writes
+// global memory may come before pdl_wait().  pdl_launch_dependents() lets the NEXT kernel do the same with this one.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -268,6 +276,22 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t col) {
 }
 
 #endif  // __CUDACC__
+
+// ---- host: launch with programmatic stream serialization (see pdl_wait) ----------
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---- host: tensor map creation without linking libcuda -------------------------
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
