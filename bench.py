@@ -261,10 +261,34 @@ def upstream_cuda_leg(q, k, v, up, stream, ours_ms):
         return {"error": repr(e)}
 
 
+def tile_stream_ceiling(device, stream, hbm):
+    """What the memory system gives for the causal kernels' own access pattern with no arithmetic (rfa_stream_probe): the
+    headline geometry (128 CTAs walking T in chunks of 128 rows of 128 bytes, two stages), reading 64 KB per chunk, alone
+    and with a 32 KB tile written back per chunk -- the read : write mix of the backward's first sweep."""
+    from rfa_b200 import ops
+    lib = ops._lib.load()
+    Tp, nb = 8 * T, 4                               # 1.07 GB read per launch: far beyond L2
+    src = torch.zeros(Tp, BH, 64 * nb, dtype=torch.half, device=device)
+    dst = torch.empty(Tp, BH, 128, dtype=torch.half, device=device)
+    res = {"workload": f"{BH} CTAs x {Tp // 128} chunks, {16 * nb} KB read (+32 KB written) per chunk, two stages"}
+    for name, store in (("read_only", 0), ("read_and_write_2_to_1", 1)):
+        fn = lambda: ops.check(lib.rfa_stream_probe(ops.ptr(src), ops.ptr(dst), Tp, BH, nb, store, stream.cuda_stream), "probe")
+        for _ in range(2):
+            fn()
+        ms = timed(fn, 5, stream)
+        nbytes = Tp * BH * (128 * nb + (256 if store else 0))
+        res[name] = {"ms": ms, "GBps": nbytes / (ms * 1e-3) / 1e9, "frac_of_copy_peak": nbytes / (ms * 1e-3) / 1e9 / hbm}
+    return res
+
+
 def extras(device, stream, hbm):
     """Secondary measurements: decode (config 4), cross attention (config 3), feature map."""
     from rfa_b200 import ops
     out = {}
+    try:
+        out["tile_stream_ceiling"] = tile_stream_ceiling(device, stream, hbm)
+    except Exception as e:  # noqa: BLE001
+        out["tile_stream_ceiling"] = {"error": repr(e)}
     # ---- incremental decoding: B64 H16, fp32 state, prefill 512 tokens, 4096 fused steps
     try:
         Bd, Hd, steps, chunk = 64, 16, 4096, 128

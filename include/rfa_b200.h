@@ -312,6 +312,15 @@ int rfa_cross_decode_step(const void* phi_q, int in_dtype,
                           const float* const* s_ptrs, const float* const* z_ptrs,
                           void* out, int L, int BH, int K, int d, rfa_stream_t stream);
 
+/* Measurement aid, no upstream counterpart: streams in [T, BH, 64*nb] fp16 through
+ * shared memory with the tile pattern of the causal kernels (one CTA per (batch,
+ * head), chunks of 128 tokens, nb boxes of 128 rows x 128 bytes per chunk, two
+ * stages) and, with_store != 0, writes one [128][128] fp16 tile per chunk to out
+ * [T, BH, 128].  No arithmetic: its time is the memory system's own for this
+ * pattern; bench.py reports it beside the copy bandwidth. */
+int rfa_stream_probe(const void* in, void* out, int64_t T, int BH, int nb, int with_store,
+                     rfa_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

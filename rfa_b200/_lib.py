@@ -52,6 +52,7 @@ SIGNATURES = {
     "rfa_cross_query_fwd": (_int, [_vp] * 4 + [_i64, _int, _int, _int, _vp]),
     "rfa_cross_query_bwd": (_int, [_vp] * 7 + [_i64, _int, _int, _int, _vp]),
     "rfa_decode_step": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _int, _vp, _int, _int, _int, _vp]),
+    "rfa_stream_probe": (_int, [_vp, _vp, _i64, _int, _int, _int, _vp]),
     "rfa_cross_decode_step": (_int, [_vp, _int, _vp, _vp, _vp, _int, _int, _int, _int, _vp]),
     "rfa_decode_step_fused": (_int, [_vp, _vp, _vp, _int, _vp, _f32, _vp, _vp, _int, _vp, _int, _int, _int, _int, _vp]),
 }

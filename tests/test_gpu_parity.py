@@ -533,6 +533,20 @@ def test_bad_arguments_are_rejected_without_launching(dev):
     assert ops.causal_fwd(q, q, torch.zeros(0, 2, 64, dtype=torch.half, device=dev)).shape == (0, 2, 64)
 
 
+def test_stream_probe_runs_and_checks_its_arguments(dev):
+    """The measurement aid behind bench.py's tile-stream ceiling: streams tiles with no arithmetic."""
+    from rfa_b200 import _lib
+    lib = _lib.load()
+    src = torch.zeros(300, 3, 64 * 4, dtype=torch.half, device=dev)
+    dst = torch.zeros(300, 3, 128, dtype=torch.half, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.rfa_stream_probe(src.data_ptr(), dst.data_ptr(), 300, 3, 4, 1, st) == 0
+    assert lib.rfa_stream_probe(src.data_ptr(), None, 300, 3, 4, 0, st) == 0
+    torch.cuda.synchronize()
+    assert lib.rfa_stream_probe(src.data_ptr(), None, 300, 3, 4, 1, st) == -1       # a store needs somewhere to go
+    assert lib.rfa_stream_probe(src.data_ptr(), dst.data_ptr(), 300, 3, 7, 0, st) == -1
+
+
 def test_causal_long_sequence_late_tokens(dev):
     """T = 32768 on real features: denominators reach ~7500, g/den ~1e-4 (fp16 subnormal range).  The
     late tokens are where rounding would show first; they are held to the same gate."""
