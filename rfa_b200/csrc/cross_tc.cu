@@ -28,6 +28,20 @@ constexpr int kXThreads = 192;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;                                                 \
   (void)sbase; (void)lane;
 
+// same, for kernels that use every byte two CTAs per SM may have: no slack to align the base, which is checked instead
+#define RFA_X_PROLOGUE_ALIGNED(NBARS)                                                                            \
+  extern __shared__ __align__(1024) unsigned char x_raw[];                                                       \
+  unsigned char* sm = x_raw;                                                                                     \
+  if (smem_u32(sm) & 1023u) {                                                                                    \
+    if (threadIdx.x == 0) tc_fail(99);                                                                           \
+    return;                                                                                                      \
+  }                                                                                                              \
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBarOff);                                                    \
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + (NBARS));                                             \
+  const uint32_t sbase = smem_u32(sm);                                                                           \
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;                                                 \
+  (void)sbase; (void)lane;
+
 #define RFA_X_START(TMEM_COLS)                                            \
   if (warp == 1) { tmem_alloc(tmem_slot, (TMEM_COLS)); tmem_relinquish(); } \
   tc_fence_before_sync();                                                 \
@@ -256,19 +270,21 @@ cross_query_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 // query backward.  grid (BH)
 // ===========================================================================
 namespace xb {
-constexpr uint32_t kQ_ = 0, kG_ = 2 * kBox, kStage = 3 * kBox, kS_ = 2 * kStage, kZ_ = kS_ + 2 * kBox, kGr_ = kZ_ + 512,
-                   kBarOff = kGr_ + 512, kSmem = kBarOff + 128 + 1024;
-constexpr uint32_t cN = 0, cDQ = 128, cDS = 256;
+// 113 KB and 256 TMEM columns exactly, so that two CTAs share an SM: the state tile is one box (q . z is formed on CUDA
+// cores in fp32 instead of as a 65th column of the numerator product) and z itself is read through the L1 cache
+constexpr uint32_t kQ_ = 0, kG_ = 2 * kBox, kStage = 3 * kBox, kS_ = 2 * kStage, kGr_ = kS_ + kBox,
+                   kBarOff = kGr_ + 512, kSmem = 113 * 1024;
+static_assert(kBarOff + 128 <= kSmem, "cross_query_bwd: shared memory map exceeds half an SM");
+constexpr uint32_t cN = 0, cDQ = 64, cDS = 192;
 enum { bFull = 0, bEmpty = 2, bN = 4, bG = 5, bDQ = 6, bDQFree = 7, bSt = 8, bEpi = 9, bNum = 10 };
 }
 
-__global__ void __launch_bounds__(kXThreads, 1)
+__global__ void __launch_bounds__(kXThreads, 2)
 cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_g,
                           const __grid_constant__ CUtensorMap tm_gq, const float* __restrict__ s, const float* __restrict__ z,
                           float* __restrict__ d_s, float* __restrict__ d_z, int64_t T, int BH) {
   using namespace xb;
-  RFA_X_PROLOGUE(bNum, 512)
-  float* zs = reinterpret_cast<float*>(sm + kZ_);
+  RFA_X_PROLOGUE_ALIGNED(bNum)
   float* grs = reinterpret_cast<float*>(sm + kGr_);
   const int bh = blockIdx.x;
   const int nchunk = (int)((T + kTC - 1) / kTC);
@@ -279,7 +295,7 @@ cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     mbar_fence_init();
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_g); tma_prefetch_desc(&tm_gq);
   }
-  RFA_X_START(512)
+  RFA_X_START(256)
   if (warp == 0) {
     if (lane == 0)
       for (int c = 0; c < nchunk; ++c) {
@@ -293,7 +309,7 @@ cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idQS = umma_idesc_f16(128, 80, false, true);     // Q [S|z]
+      constexpr uint32_t idQS = umma_idesc_f16(128, 64, false, true);     // Q S
       constexpr uint32_t idKK = umma_idesc_f16(128, 128, false, false);   // gs S^T
       constexpr uint32_t idMM = umma_idesc_f16(128, 64, true, true);      // Q^T gs
       const uint64_t dQk = umma_smem_desc(sbase + kQ_, 0, 1024, kSwizzle128B), dQm = umma_smem_desc(sbase + kQ_, kBox, 1024, kSwizzle128B);
@@ -323,9 +339,17 @@ cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
   } else {
     const int quarter = warp & 3, row = quarter * 32 + lane, etid = tid - 64;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const float zrow = z[(size_t)bh * kK + row];
-    build_state_tile(sm + kS_, row, s + ((size_t)bh * kK + row) * kD, zrow);
-    zs[row] = zrow;
+    const float* zs = z + (size_t)bh * kK;         // 512 bytes every thread reads whole, every chunk: served by L1
+    {
+      uint32_t r[64];
+      const float* src = s + ((size_t)bh * kK + row) * kD;
+#pragma unroll
+      for (int n = 0; n < 64; n += 4) {
+        const float4 f = *reinterpret_cast<const float4*>(src + n);
+        r[n] = __float_as_uint(f.x); r[n + 1] = __float_as_uint(f.y); r[n + 2] = __float_as_uint(f.z); r[n + 3] = __float_as_uint(f.w);
+      }
+      store_state_row(sm + kS_, row, r);
+    }
     fence_async_smem();
     mbar_arrive(&bars[bSt]);
     uint32_t epi_phase = 0;
@@ -335,17 +359,29 @@ cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       const int st = c & 1;
       const uint32_t ph = c & 1;
       unsigned char* stage = sm + st * kStage;
-      // ---- den, gs, gr from N = phi_q [S|z]
+      // ---- q . z in fp32 from this thread's own row of the staged Q tile while the tensor pipe forms N = phi_q S
+      if (!mbar_wait(&bars[bFull + st], (c >> 1) & 1)) { tc_fail(32); ok = false; break; }
+      float qz0 = 0.f, qz1 = 0.f, qz2 = 0.f, qz3 = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint4 u = *reinterpret_cast<const uint4*>(stage + kQ_ + row_chunk2(row, ch));
+        const float4 z0 = __ldg(reinterpret_cast<const float4*>(zs + ch * 8)), z1 = __ldg(reinterpret_cast<const float4*>(zs + ch * 8 + 4));
+        float2 f;
+        f = unpack_half2(u.x); qz0 = fmaf(f.x, z0.x, qz0); qz1 = fmaf(f.y, z0.y, qz1);
+        f = unpack_half2(u.y); qz2 = fmaf(f.x, z0.z, qz2); qz3 = fmaf(f.y, z0.w, qz3);
+        f = unpack_half2(u.z); qz0 = fmaf(f.x, z1.x, qz0); qz1 = fmaf(f.y, z1.y, qz1);
+        f = unpack_half2(u.w); qz2 = fmaf(f.x, z1.z, qz2); qz3 = fmaf(f.y, z1.w, qz3);
+      }
+      // ---- den, gs, gr
       if (!mbar_wait(&bars[bN], ph)) { tc_fail(27); ok = false; break; }
       tc_fence_after_sync();
       float gr;
       {
-        uint32_t nn[64], nz[16];
+        uint32_t nn[64];
         tmem_ld32(tmem + lane_addr + cN, nn);
         tmem_ld32(tmem + lane_addr + cN + 32, nn + 32);
-        tmem_ld16(tmem + lane_addr + cN + 64, nz);
         tmem_ld_wait();
-        const float raw = __uint_as_float(nz[0]);
+        const float raw = (qz0 + qz1) + (qz2 + qz3);
         const float dn = fmaxf(fabsf(raw), kEps), inv = 1.f / dn;
         float go = 0.f;
         unsigned char* grow = stage + kG_;
@@ -384,7 +420,7 @@ cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int k0 = piece * 32 + j * 8;
-          const float4 z0 = *reinterpret_cast<const float4*>(zs + k0), z1 = *reinterpret_cast<const float4*>(zs + k0 + 4);
+          const float4 z0 = __ldg(reinterpret_cast<const float4*>(zs + k0)), z1 = __ldg(reinterpret_cast<const float4*>(zs + k0 + 4));
           uint4 u;
           u.x = pack_half2(fmaf(gr, z0.x, __uint_as_float(a[j * 8 + 0])), fmaf(gr, z0.y, __uint_as_float(a[j * 8 + 1])));
           u.y = pack_half2(fmaf(gr, z0.z, __uint_as_float(a[j * 8 + 2])), fmaf(gr, z0.w, __uint_as_float(a[j * 8 + 3])));
@@ -418,26 +454,29 @@ cross_query_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     }
     if (etid == 0) tma_store_wait<0>();
   }
-  RFA_X_FINISH(512)
+  RFA_X_FINISH(256)
 }
 
 // ===========================================================================
 // state backward.  grid (BH)
 // ===========================================================================
 namespace xk {
+// 113 KB exactly: two CTAs share an SM (256 sequences are then one wave instead of 148 + 108, and one CTA's ramp and
+// drain hide behind the other's chunks)
 constexpr uint32_t kK_ = 0, kV_ = 2 * kBox, kStage = 3 * kBox, kS_ = 2 * kStage, kDz_ = kS_ + kBox, kBarOff = kDz_ + 512,
-                   kSmem = kBarOff + 128 + 1024;
+                   kSmem = 113 * 1024;
+static_assert(kBarOff + 128 <= kSmem, "cross_state_bwd: shared memory map exceeds half an SM");
 constexpr uint32_t cDK = 0, cDV = 128;
 enum { bFull = 0, bEmpty = 2, bReady = 4, bOut = 6, bFree = 7, bSt = 8, bEpi = 9, bNum = 10 };
 }
 
-__global__ void __launch_bounds__(kXThreads, 1)
+__global__ void __launch_bounds__(kXThreads, 2)
 cross_state_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                           const __grid_constant__ CUtensorMap tm_gk, const __grid_constant__ CUtensorMap tm_gv,
                           const uint8_t* __restrict__ pad_mask, const float* __restrict__ d_s, const float* __restrict__ d_z,
                           int64_t T, int BH, int H) {
   using namespace xk;
-  RFA_X_PROLOGUE(bNum, 256)
+  RFA_X_PROLOGUE_ALIGNED(bNum)
   float* dzs = reinterpret_cast<float*>(sm + kDz_);
   const int bh = blockIdx.x;
   const int nchunk = (int)((T + kTC - 1) / kTC);
@@ -558,6 +597,7 @@ template <class Kern>
 static int x_opt_in(Kern kern, uint32_t bytes, const char* what) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) return fail((int)e, "%s: cannot reserve %u bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);   // a hint only
   return 0;
 }
 
