@@ -32,7 +32,12 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[bFull + i], 1); mbar_init(&bars[bEmpty + i], 129); mbar_init(&bars[bU + i], 1); mbar_init(&bars[bUFree + i], 128); }
     mbar_init(&bars[bEpi], 128);
     mbar_fence_init();
-    tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_phi);
+    // the first tiles are requested before the rest of the prologue (W_h, tensor memory), which their flight then hides
+    for (int i = 0; i < 2 && i < ntile; ++i) {
+      mbar_arrive_expect_tx(&bars[bFull + i], kBox);
+      tma_load_3d(sm + kX + i * kStage, &tm_x, &bars[bFull + i], 0, h, (blockIdx.x + i * gridDim.x) * kTC);
+    }
+    tma_prefetch_desc(&tm_phi);
   }
   // W_h as an fp16 K-major operand tile [64 rows j][64 i]
   for (int i = tid; i < 64 * 8; i += kThreads_) {
@@ -52,9 +57,9 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
 
   if (warp == 0) {
     if (lane == 0)
-      for (int i = 0; i < ntile; ++i) {
+      for (int i = 2; i < ntile; ++i) {
         const int st = i & 1;
-        if (i >= 2 && !mbar_wait(&bars[bEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
+        if (!mbar_wait(&bars[bEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
         const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
         mbar_arrive_expect_tx(&bars[bFull + st], kBox);
         tma_load_3d(sm + kX + st * kStage, &tm_x, &bars[bFull + st], 0, h, row0);
@@ -169,17 +174,21 @@ int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* ro
 // follows gh in shared memory -- accumulator rows 64..127 are never read.
 // HBM-bound: 384 bytes in, 128 bytes out per (row, head).
 namespace fmb {
-constexpr int kThreads_ = 320;                 // warp 0 TMA, warp 1 MMA issuer, warps 2..5 group 1 (g_u), warps 6..9 group 2 (g_x)
+// warp 0 TMA, warp 1 MMA issuer, warps 2..5 and 6..9 group 1 (g_u: columns 0..31 and 32..63 of every row -- the sin/cos
+// chain of a whole row in one thread was the slowest stage of the tile pipeline), warps 10..13 group 2 (g_x)
+constexpr int kThreads_ = 448;
 constexpr uint32_t kX = 0, kGP = kBox, kStage = 3 * kBox;          // per stage: x tile, g_phi tile (two boxes)
-constexpr uint32_t kGH = 2 * kStage;           // two gh tiles; the output staging tile follows them
+constexpr int kRing = 3;                       // staged tiles in flight: a stage lives through the tile's whole dependent chain
+constexpr uint32_t kGH = kRing * kStage;       // two gh tiles; the output staging tile follows them
 constexpr uint32_t kOut = kGH + 2 * kBox;
 constexpr uint32_t kW = kOut + kBox;           // W  as [j][i] (K-major, contraction over i)
 constexpr uint32_t kWt = kW + 8192;            // W^T as [i][j] (K-major, contraction over j)
-constexpr uint32_t kRn = kWt + 8192;           // float2 [2][128]: (inv, inv / |x|) of the tile's rows
-constexpr uint32_t kBarOff = kRn + 2048;
+constexpr uint32_t kRn = kWt + 8192;           // float2 [kRing][128]: (inv, inv / |x|) of the tile's rows, one set per stage
+constexpr uint32_t kBarOff = kRn + kRing * 1024;
 constexpr uint32_t kSmem = kBarOff + 256 + 1024;
 constexpr uint32_t cU = 0, cGX = 128, cGW = 256;
-enum { bFull = 0, bEmpty = 2, bU = 4, bUFree = 6, bGH = 8, bGHFree = 10, bGX = 12, bGXFree = 14, bEpi = 16, bDone = 17, bNum = 18 };
+enum { bFull = 0, bEmpty = 3, bU = 6, bUFree = 8, bGH = 10, bGHFree = 12, bGX = 14, bGXFree = 16, bEpi = 18, bDone = 19, bNum = 20 };
+static_assert(kRing == 3 && bNum * 8 + 4 <= 256, "feature_map_bwd: barrier block");
 }
 
 __global__ void __launch_bounds__(fmb::kThreads_, 1)
@@ -199,16 +208,27 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
   const int ntile_all = (int)((rows + kTC - 1) / kTC);
   const int ntile = blockIdx.x < ntile_all ? (ntile_all - 1 - blockIdx.x) / gridDim.x + 1 : 0;   // tiles blockIdx.x, +gridDim.x, ...
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kRing; ++i) {
       mbar_init(&bars[bFull + i], 1);
-      mbar_init(&bars[bEmpty + i], 257);       // the issuer's commit + both epilogue groups
-      mbar_init(&bars[bU + i], 1); mbar_init(&bars[bUFree + i], 128);
-      mbar_init(&bars[bGH + i], 128); mbar_init(&bars[bGHFree + i], 1);
+      mbar_init(&bars[bEmpty + i], 385);       // the issuer's commit + the three epilogue groups
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[bU + i], 1); mbar_init(&bars[bUFree + i], 256);
+      mbar_init(&bars[bGH + i], 256); mbar_init(&bars[bGHFree + i], 1);
       mbar_init(&bars[bGX + i], 1); mbar_init(&bars[bGXFree + i], 128);
     }
     mbar_init(&bars[bEpi], 128); mbar_init(&bars[bDone], 1);
     mbar_fence_init();
-    tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_gp); tma_prefetch_desc(&tm_gx);
+    // the first tiles are requested before the rest of the prologue (W_h, tensor memory), which their flight then hides
+    for (int i = 0; i < kRing && i < ntile; ++i) {
+      const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+      unsigned char* base = sm + i * kStage;
+      mbar_arrive_expect_tx(&bars[bFull + i], kStage);
+      tma_load_3d(base + kX, &tm_x, &bars[bFull + i], 0, h, row0);
+      tma_load_3d(base + kGP, &tm_gp, &bars[bFull + i], 0, h, row0);
+      tma_load_3d(base + kGP + kBox, &tm_gp, &bars[bFull + i], 64, h, row0);
+    }
+    tma_prefetch_desc(&tm_gx);
   }
   // W_h as two fp16 K-major operand tiles: [j][i] and its transpose [i][j]
   for (int idx = tid; idx < 64 * 8; idx += kThreads_) {
@@ -232,15 +252,15 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
 
   if (warp == 0) {
     if (lane == 0)
-      for (int i = 0; i < ntile; ++i) {
-        const int st = i & 1;
-        if (i >= 2 && !mbar_wait(&bars[bEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(11); break; }
+      for (int i = kRing; i < ntile; ++i) {
+        const int sg = i % kRing;
+        if (!mbar_wait(&bars[bEmpty + sg], ((i / kRing) + 1) & 1)) { tc_fail(11); break; }
         const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
-        unsigned char* base = sm + st * kStage;
-        mbar_arrive_expect_tx(&bars[bFull + st], kStage);
-        tma_load_3d(base + kX, &tm_x, &bars[bFull + st], 0, h, row0);
-        tma_load_3d(base + kGP, &tm_gp, &bars[bFull + st], 0, h, row0);
-        tma_load_3d(base + kGP + kBox, &tm_gp, &bars[bFull + st], 64, h, row0);
+        unsigned char* base = sm + sg * kStage;
+        mbar_arrive_expect_tx(&bars[bFull + sg], kStage);
+        tma_load_3d(base + kX, &tm_x, &bars[bFull + sg], 0, h, row0);
+        tma_load_3d(base + kGP, &tm_gp, &bars[bFull + sg], 0, h, row0);
+        tma_load_3d(base + kGP + kBox, &tm_gp, &bars[bFull + sg], 64, h, row0);
       }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -255,18 +275,18 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       const uint64_t dGHm = umma_smem_desc(sbase + kGH, kBox, 1024, kSwizzle128B);      // gh, MN-major; second M block = next tile
       constexpr uint64_t kSt = kStage >> 4, kTile = kBox >> 4;
       auto issue_u = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(12); return false; }
+        const int st = i & 1, sg = i % kRing;
+        if (!mbar_wait(&bars[bFull + sg], (i / kRing) & 1)) { tc_fail(12); return false; }
         if (i >= 2 && !mbar_wait(&bars[bUFree + st], ((i >> 1) + 1) & 1)) { tc_fail(13); return false; }
         tc_fence_after_sync();
-        umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + cU + st * 64, dX + st * kSt, dW, idKK, 0);
+        umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + cU + st * 64, dX + sg * kSt, dW, idKK, 0);
         umma_commit(&bars[bU + st]);
         return true;
       };
       bool ok = ntile > 0 ? issue_u(0) : true;
 #pragma unroll 1
       for (int i = 0; ok && i < ntile; ++i) {
-        const int st = i & 1;
+        const int st = i & 1, sg = i % kRing;
         if (i + 1 < ntile && !issue_u(i + 1)) break;
         if (!mbar_wait(&bars[bGH + st], (i >> 1) & 1)) { tc_fail(14); break; }
         if (i >= 2 && !mbar_wait(&bars[bGXFree + st], ((i >> 1) + 1) & 1)) { tc_fail(15); break; }
@@ -274,23 +294,23 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
         umma_chain_ss<4, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + cGX + st * 64, dGH + st * kTile, dWt, idKK, 0);   // gx' = gh W
         umma_commit(&bars[bGX + st]);
         if (want_gw)                                                                                                  // g_W += gh^T X
-          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + cGW, dGHm + st * kTile, dXm + st * kSt, idMM, i > 0 ? 1u : 0u);
+          umma_chain_ss<8, kStepMN, kBlockMN, kStepMN, kBlockMN>(lead, tmem + cGW, dGHm + st * kTile, dXm + sg * kSt, idMM, i > 0 ? 1u : 0u);
         umma_commit(&bars[bGHFree + st]);
-        umma_commit(&bars[bEmpty + st]);
+        umma_commit(&bars[bEmpty + sg]);
       }
       umma_commit(&bars[bDone]);
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ group 1: inv, u, g_u -> gh
-    const int quarter = warp & 3, row = quarter * 32 + lane;
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ group 1: inv, u, g_u -> gh (half of the columns each)
+    const int quarter = warp & 3, row = quarter * 32 + lane, half = (warp - 2) >> 2;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     for (int i = 0; i < ntile; ++i) {
-      const int st = i & 1;
-      unsigned char* base = sm + st * kStage;
+      const int st = i & 1, sg = i % kRing;
+      unsigned char* base = sm + sg * kStage;
       const int64_t grow = (int64_t)(blockIdx.x + i * gridDim.x) * kTC + row;
       // a masked row's features are constant zeros: no gradient flows through it
       const float scale_row = (row_mask && grow < rows && row_mask[grow]) ? 0.f : scale;
-      if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(16); break; }
+      if (!mbar_wait(&bars[bFull + sg], (i / kRing) & 1)) { tc_fail(16); break; }
       float ss = 0.f;                                  // |x|^2 of this thread's row
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
@@ -304,18 +324,18 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       const float n = sqrtf(ss), inv = 1.f / (n + kNormEps);
       if (!mbar_wait(&bars[bU + st], (i >> 1) & 1)) { tc_fail(17); break; }
       tc_fence_after_sync();
-      uint32_t u[64];
-      tmem_ld32(tmem + lane_addr + cU + st * 64, u);
-      tmem_ld32(tmem + lane_addr + cU + st * 64 + 32, u + 32);
+      uint32_t u[32];
+      tmem_ld32(tmem + lane_addr + cU + st * 64 + half * 32, u);
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[bUFree + st]);
       // the gh tile of this parity was last read by the products of tile i - 2
       if (i >= 2 && !mbar_wait(&bars[bGHFree + st], ((i >> 1) + 1) & 1)) { tc_fail(18); break; }
-      rn[st * 128 + row] = make_float2(inv, n > 0.f ? inv / n : 0.f);
+      if (half == 0) rn[sg * 128 + row] = make_float2(inv, n > 0.f ? inv / n : 0.f);      // read by group 2 before it releases the stage
       const float sc = scale_row * inv;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int ch = half * 4 + c4;
         const uint4 gs = *reinterpret_cast<const uint4*>(base + kGP + row_chunk1(row, ch));          // g_sin, columns 8 ch ..
         const uint4 gc = *reinterpret_cast<const uint4*>(base + kGP + kBox + row_chunk1(row, ch));   // g_cos
         const uint32_t gsw[4] = {gs.x, gs.y, gs.z, gs.w}, gcw[4] = {gc.x, gc.y, gc.z, gc.w};
@@ -324,28 +344,30 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
         for (int e = 0; e < 4; ++e) {
           const float2 a = unpack_half2(gsw[e]), b = unpack_half2(gcw[e]);
           float s0, c0, s1, c1;
-          __sincosf(__uint_as_float(u[ch * 8 + 2 * e]) * inv, &s0, &c0);
-          __sincosf(__uint_as_float(u[ch * 8 + 2 * e + 1]) * inv, &s1, &c1);
+          __sincosf(__uint_as_float(u[c4 * 8 + 2 * e]) * inv, &s0, &c0);
+          __sincosf(__uint_as_float(u[c4 * 8 + 2 * e + 1]) * inv, &s1, &c1);
           o[e] = pack_half2(sc * (a.x * c0 - b.x * s0), sc * (a.y * c1 - b.y * s1));
         }
         *reinterpret_cast<uint4*>(sm + kGH + st * kBox + row_chunk1(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       fence_async_smem();
       mbar_arrive(&bars[bGH + st]);
-      mbar_arrive(&bars[bEmpty + st]);                 // this group's reads of the stage are done
+      mbar_arrive(&bars[bEmpty + sg]);                 // this group's reads of the stage are done
     }
   } else {
     // ------------------------------------------------------------------ group 2: g_x
-    const int quarter = warp & 3, row = quarter * 32 + lane, etid = tid - 192;
+    const int quarter = warp & 3, row = quarter * 32 + lane, etid = tid - 320;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     uint32_t epi_phase = 0;
     bool ok = true;
     for (int i = 0; ok && i < ntile; ++i) {
-      const int st = i & 1;
-      unsigned char* base = sm + st * kStage;
+      const int st = i & 1, sg = i % kRing;
+      unsigned char* base = sm + sg * kStage;
       const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
-      if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(19); ok = false; break; }
-      if (!mbar_wait(&bars[bGH + st], (i >> 1) & 1)) { tc_fail(20); ok = false; break; }      // orders the read of rn
+      if (!mbar_wait(&bars[bFull + sg], (i / kRing) & 1)) { tc_fail(19); ok = false; break; }
+      // gx' of this tile exists only after the issuer saw group 1's gh, which group 1 signalled after writing rn: waiting
+      // for the product orders the read of rn too.  (Group 1 may run two tiles ahead of this group, so this group must
+      // not wait on bGH: that barrier can complete twice before this group looks.)
       if (!mbar_wait(&bars[bGX + st], (i >> 1) & 1)) { tc_fail(21); ok = false; break; }
       tc_fence_after_sync();
       uint32_t gx[64];
@@ -354,15 +376,12 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&bars[bGXFree + st]);
-      const float2 r2 = rn[st * 128 + row];
-      uint4 xu[8];
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) xu[ch] = *reinterpret_cast<const uint4*>(base + kX + row_chunk1(row, ch));
-      mbar_arrive(&bars[bEmpty + st]);                 // this group's reads of the stage are done
+      const float2 r2 = rn[sg * 128 + row];
       float dot = 0.f;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        const uint32_t xw[4] = {xu[ch].x, xu[ch].y, xu[ch].z, xu[ch].w};
+        const uint4 xu = *reinterpret_cast<const uint4*>(base + kX + row_chunk1(row, ch));
+        const uint32_t xw[4] = {xu.x, xu.y, xu.z, xu.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f = unpack_half2(xw[e]);
@@ -377,7 +396,8 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       }
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        const uint32_t xw[4] = {xu[ch].x, xu[ch].y, xu[ch].z, xu[ch].w};
+        const uint4 xu = *reinterpret_cast<const uint4*>(base + kX + row_chunk1(row, ch));   // read again rather than held: registers
+        const uint32_t xw[4] = {xu.x, xu.y, xu.z, xu.w};
         uint32_t o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -386,6 +406,7 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
         }
         *reinterpret_cast<uint4*>(sm + kOut + row_chunk1(row, ch)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
+      mbar_arrive(&bars[bEmpty + sg]);                 // this group's reads of the stage are done
       fence_async_smem();
       if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(23); ok = false; break; }
       if (etid == 0) {
@@ -393,18 +414,25 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
         tma_store_commit();
       }
     }
-    // ---- g_W of this CTA's tiles: rows j = 0..63 of the accumulator
+    // ---- g_W of this CTA's tiles: rows j = 0..63 of the accumulator, transposed through shared memory (the first stage:
+    // every load has been consumed once bDone fires) so that a warp's atomics fall on consecutive addresses
     if (ok && want_gw && ntile > 0) {
-      if (!mbar_wait(&bars[bDone], 0)) tc_fail(24);
-      else if (row < 64) {
+      float* tr = reinterpret_cast<float*>(sm);            // [64][65] floats
+      if (!mbar_wait(&bars[bDone], 0)) { tc_fail(24); ok = false; }
+      if (ok && row < 64) {
         tc_fence_after_sync();
         uint32_t gw[64];
         tmem_ld32(tmem + lane_addr + cGW, gw);
         tmem_ld32(tmem + lane_addr + cGW + 32, gw + 32);
         tmem_ld_wait();
-        float* dst = g_w + ((size_t)h * 64 + row) * 64;
 #pragma unroll
-        for (int e = 0; e < 64; ++e) atomicAdd(dst + e, __uint_as_float(gw[e]));
+        for (int e = 0; e < 64; ++e) tr[row * 65 + e] = __uint_as_float(gw[e]);
+      }
+      if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(25); ok = false; }
+      if (ok) {
+        float* dst = g_w + (size_t)h * 64 * 64;
+#pragma unroll 4
+        for (int idx = etid; idx < 64 * 64; idx += 128) atomicAdd(dst + idx, tr[(idx >> 6) * 65 + (idx & 63)]);
       }
     }
     if (etid == 0) tma_store_wait<0>();
