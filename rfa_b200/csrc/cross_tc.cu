@@ -47,7 +47,9 @@ constexpr int kXThreads = 192;
   tc_fence_before_sync();                                                 \
   __syncthreads();                                                        \
   tc_fence_after_sync();                                                  \
-  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem = *tmem_slot;                                       \
+  pdl_wait(); /* nothing above touches global memory: all of it overlaps the previous kernel's tail */ \
+  pdl_launch_dependents();
 
 #define RFA_X_FINISH(TMEM_COLS)                          \
   tc_fence_before_sync();                                \
@@ -613,10 +615,10 @@ int launch_cross_state_fwd_tc(const __half* k, const __half* v, const uint8_t* p
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if ((int64_t)BH * nseg > sms) {            // more CTAs than SMs: two per SM, two stages each
     if (int e = x_opt_in(cross_state_fwd_tc_kernel<2>, xs::L<2>::kSmem, "cross_state_fwd")) return e;
-    cross_state_fwd_tc_kernel<2><<<dim3(BH, nseg), kXThreads, xs::L<2>::kSmem, st>>>(tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
+    launch_pdl(cross_state_fwd_tc_kernel<2>, dim3(BH, nseg), kXThreads, xs::L<2>::kSmem, st, tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
   } else {
     if (int e = x_opt_in(cross_state_fwd_tc_kernel<4>, xs::L<4>::kSmem, "cross_state_fwd")) return e;
-    cross_state_fwd_tc_kernel<4><<<dim3(BH, nseg), kXThreads, xs::L<4>::kSmem, st>>>(tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
+    launch_pdl(cross_state_fwd_tc_kernel<4>, dim3(BH, nseg), kXThreads, xs::L<4>::kSmem, st, tk, tv, pad_mask, s, z, T, BH, H, nseg, tseg);
   }
   return check_launch("rfa_cross_state_fwd");
 }
@@ -626,7 +628,7 @@ int launch_cross_query_fwd_tc(const __half* q, const float* s, const float* z, _
   if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&to, out, T, BH, kD, kTC))
     return fail(RFA_EDEVICE, "cross_query_fwd: cuTensorMapEncodeTiled failed or is unavailable");
   if (int e = x_opt_in(cross_query_fwd_tc_kernel, xq::kSmem, "cross_query_fwd")) return e;
-  cross_query_fwd_tc_kernel<<<BH, kXThreads, xq::kSmem, st>>>(tq, to, s, z, T, BH);
+  launch_pdl(cross_query_fwd_tc_kernel, dim3(BH), kXThreads, xq::kSmem, st, tq, to, s, z, T, BH);
   return check_launch("rfa_cross_query_fwd");
 }
 
@@ -636,7 +638,7 @@ int launch_cross_query_bwd_tc(const __half* q, const float* s, const float* z, c
   if (make_tmap_rows(&tq, q, T, BH, kK, kTC) || make_tmap_rows(&tg, g, T, BH, kD, kTC) || make_tmap_rows(&tgq, gq, T, BH, kK, kTC))
     return fail(RFA_EDEVICE, "cross_query_bwd: cuTensorMapEncodeTiled failed or is unavailable");
   if (int e = x_opt_in(cross_query_bwd_tc_kernel, xb::kSmem, "cross_query_bwd")) return e;
-  cross_query_bwd_tc_kernel<<<BH, kXThreads, xb::kSmem, st>>>(tq, tg, tgq, s, z, d_s, d_z, T, BH);
+  launch_pdl(cross_query_bwd_tc_kernel, dim3(BH), kXThreads, xb::kSmem, st, tq, tg, tgq, s, z, d_s, d_z, T, BH);
   return check_launch("rfa_cross_query_bwd");
 }
 
@@ -647,7 +649,7 @@ int launch_cross_state_bwd_tc(const __half* k, const __half* v, const uint8_t* p
       make_tmap_rows(&tgk, gk, T, BH, kK, kTC) || make_tmap_rows(&tgv, gv, T, BH, kD, kTC))
     return fail(RFA_EDEVICE, "cross_state_bwd: cuTensorMapEncodeTiled failed or is unavailable");
   if (int e = x_opt_in(cross_state_bwd_tc_kernel, xk::kSmem, "cross_state_bwd")) return e;
-  cross_state_bwd_tc_kernel<<<BH, kXThreads, xk::kSmem, st>>>(tk, tv, tgk, tgv, pad_mask, d_s, d_z, T, BH, H);
+  launch_pdl(cross_state_bwd_tc_kernel, dim3(BH), kXThreads, xk::kSmem, st, tk, tv, tgk, tgv, pad_mask, d_s, d_z, T, BH, H);
   return check_launch("rfa_cross_state_bwd");
 }
 
