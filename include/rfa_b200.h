@@ -312,6 +312,30 @@ int rfa_cross_decode_step(const void* phi_q, int in_dtype,
                           const float* const* s_ptrs, const float* const* z_ptrs,
                           void* out, int L, int BH, int K, int d, rfa_stream_t stream);
 
+/* Causal forward with the feature map inside the kernel: replaces
+ * utils.random_project on q and k (utils.py:100-120, called at
+ * causal_attention.py:241-248, with the masked_fill of padded keys at :137-143)
+ * followed by RFA.forward (rfa.py:113-124, cuda/forward.cu:16-169).
+ * x_q, x_k, v, out: [T, B*H, d] fp16, the head index fastest in the middle axis;
+ * w [H, D, d] fp32 (the matrices build_random_matrices returns, sigma and 1/tau
+ * folded in); row_mask [T, B] bytes, nonzero = padded key, or NULL; scale = the
+ * feature scale (D^-1/2 upstream).  The features phi [T, B*H, 2D] are formed tile
+ * by tile in shared memory and never written.  d = 64, D = 64 only.  One CTA per
+ * (batch, head): meant for B*H of about the SM count or more.
+ * s_in/z_in/s_out/z_out as in rfa_causal_fwd.  save_den != 0: the raw
+ * denominators are left in `workspace` (rfa_causal_workspace_bytes(T, B*H, 2D, d))
+ * where rfa_causal_bwd_saved(..., ws_has = RFA_WS_DEN) finds them, once the caller
+ * has recomputed the features with rfa_feature_map_fwd[_masked]; otherwise the
+ * workspace may be NULL. */
+int rfa_causal_fwd_fused(const void* x_q, const void* x_k, const void* v,
+                         const float* w, const uint8_t* row_mask, float scale,
+                         void* out,
+                         const float* s_in, const float* z_in,
+                         float* s_out, float* z_out,
+                         void* workspace, size_t workspace_bytes,
+                         int64_t T, int B, int H, int d, int D,
+                         int save_den, rfa_stream_t stream);
+
 /* Measurement aid, no upstream counterpart: streams in [T, BH, 64*nb] fp16 through
  * shared memory with the tile pattern of the causal kernels (one CTA per (batch,
  * head), chunks of 128 tokens, nb boxes of 128 rows x 128 bytes per chunk, two

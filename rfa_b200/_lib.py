@@ -39,6 +39,7 @@ SIGNATURES = {
     "rfa_causal_bwd_q": (_int, [_vp] * 4 + [_vp] + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_causal_bwd_kv": (_int, [_vp] * 4 + [_vp] * 2 + [_vp] * 2 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_causal_fwd_staged": (_int, [_vp] * 4 + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _int, _int, _vp]),
+    "rfa_causal_fwd_fused": (_int, [_vp] * 3 + [_vp, _vp, _f32, _vp] + [_vp] * 4 + [_vp, _sz, _i64, _int, _int, _int, _int, _int, _vp]),
     "rfa_causal_shard_total": (_int, [_vp] * 3 + [_vp, _sz, _i64, _int, _int, _int, _vp]),
     "rfa_exclusive_scan_gathered": (_int, [_vp, _int, _int, _int, _vp, _vp, _int, _int, _int, _vp]),
     "rfa_causal_bwd_q_staged": (_int, [_vp] * 6 + [_vp] * 3 + [_vp, _sz, _i64, _int, _int, _int, _int, _vp]),

@@ -27,7 +27,8 @@ int check_launch(const char* what) {
 
 // per kernel family (one translation unit each): read-and-clear of the device status word, and the setter of the
 // mapped host word its kernels mirror a failure into
-#define RFA_TC_FAMILIES(X) X(causal_fwd, 1) X(causal_bwd, 2) X(causal_bwd_kv, 3) X(cross, 4) X(feature_map, 5) X(causal_bwd_saved, 6) X(stream_probe, 7)
+#define RFA_TC_FAMILIES(X) X(causal_fwd, 1) X(causal_bwd, 2) X(causal_bwd_kv, 3) X(cross, 4) X(feature_map, 5) X(causal_bwd_saved, 6) X(stream_probe, 7) \
+  X(causal_fwd_fused, 8)
 #define RFA_DECLARE(name, id) int tc_status_##name(); int tc_mirror_##name(int*);
 RFA_TC_FAMILIES(RFA_DECLARE)
 #undef RFA_DECLARE

@@ -27,6 +27,10 @@ constexpr int kSegAlign = 128;
 int launch_causal_fwd_tc(const __half* q, const __half* k, const __half* v, __half* out, const float* s_seg,
                          const float* z_seg, float* s_out, float* z_out, float* den_out, int64_t T, int BH, int nseg,
                          int64_t tseg, cudaStream_t st);
+// forward with the feature map of q and k computed in the kernel (causal_fused_tc.cu)
+int launch_causal_fwd_fused_tc(const __half* xq, const __half* xk, const __half* v, const float* w, const uint8_t* row_mask,
+                               __half* out, const float* s_in, const float* z_in, float* s_out, float* z_out, float* den_out,
+                               int64_t T, int BH, int H, float scale, cudaStream_t st);
 // forward-direction sweep from the forward's saved output and raw denominators (causal_bwd_q_saved_tc.cu)
 int launch_causal_bwd_q_saved_tc(const __half* q, const __half* k, const __half* v, const __half* g, const __half* out,
                                  const float* den_raw, __half* gq, const float* s_seg, const float* z_seg, float* ws_gz,
@@ -275,6 +279,42 @@ extern "C" int rfa_causal_fwd_staged(const void* q, const void* k, const void* v
   }
   return launch_causal_fwd_tc((const __half*)q, (const __half*)k, (const __half*)v, (__half*)out, s_seg, z_seg, s_out,
                               z_out, save_den ? ws.den : nullptr, T, BH, p.nseg, p.tseg, st);
+}
+
+extern "C" int rfa_causal_fwd_fused(const void* x_q, const void* x_k, const void* v, const float* w, const uint8_t* row_mask,
+                                    float scale, void* out, const float* s_in, const float* z_in, float* s_out, float* z_out,
+                                    void* workspace, size_t workspace_bytes, int64_t T, int B, int H, int d, int D,
+                                    int save_den, rfa_stream_t stream) {
+  RFA_REQUIRE(B > 0 && H > 0, RFA_EINVAL, "causal_fwd_fused: B=%d H=%d", B, H);
+  RFA_REQUIRE(d == kD && D == kK / 2, RFA_EUNSUPPORTED,
+              "causal_fwd_fused: built for head_dim = %d, proj_dim = %d (got %d, %d): use rfa_feature_map_fwd + rfa_causal_fwd", kD,
+              kK / 2, d, D);
+  const int BH = B * H;
+  if (int e = check_geometry("causal_fwd_fused", T, BH, kK, kD, false)) return e;
+  RFA_REQUIRE((s_in == nullptr) == (z_in == nullptr) && (s_out == nullptr) == (z_out == nullptr), RFA_EINVAL,
+              "causal_fwd_fused: s/z pointers must be given in pairs");
+  RFA_REQUIRE(T == 0 || (x_q && x_k && v && out && w), RFA_EINVAL, "causal_fwd_fused: null pointer");
+  RFA_REQUIRE(aligned16(x_q) && aligned16(x_k) && aligned16(v) && aligned16(out) && aligned16(w) && aligned16(s_in) &&
+                  aligned16(z_in) && aligned16(s_out) && aligned16(z_out), RFA_EALIGN, "causal_fwd_fused: 16-byte alignment required");
+  RFA_REQUIRE(((uintptr_t)out & 31u) == 0, RFA_EALIGN, "causal_fwd_fused: out must be 32-byte aligned");
+  cudaStream_t st = as_stream(stream);
+  if (T == 0) {
+    if (s_out) {
+      if (s_in) {
+        cudaMemcpyAsync(s_out, s_in, (size_t)BH * kK * kD * sizeof(float), cudaMemcpyDeviceToDevice, st);
+        cudaMemcpyAsync(z_out, z_in, (size_t)BH * kK * sizeof(float), cudaMemcpyDeviceToDevice, st);
+      } else {
+        cudaMemsetAsync(s_out, 0, (size_t)BH * kK * kD * sizeof(float), st);
+        cudaMemsetAsync(z_out, 0, (size_t)BH * kK * sizeof(float), st);
+      }
+    }
+    return check_launch("causal_fwd_fused(T=0)");
+  }
+  CausalWs ws{};
+  if (save_den)      // the denominators go where a later backward on the same T, BH expects them
+    if (int e = check_ws("causal_fwd_fused", workspace, workspace_bytes, T, BH, plan_causal(T, BH), &ws)) return e;
+  return launch_causal_fwd_fused_tc((const __half*)x_q, (const __half*)x_k, (const __half*)v, w, row_mask, (__half*)out, s_in, z_in,
+                                    s_out, z_out, save_den ? ws.den : nullptr, T, BH, H, scale, st);
 }
 
 extern "C" int rfa_causal_fwd(const void* q, const void* k, const void* v, void* out,

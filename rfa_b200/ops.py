@@ -176,6 +176,48 @@ def causal_fwd_saved(q: Tensor, k: Tensor, v: Tensor, s_in: Optional[Tensor] = N
     return out, ws, _lib.WS_STATES | _lib.WS_DEN
 
 
+def fused_forward_supported(x: Tensor, w: Tensor) -> bool:
+    """Whether ``causal_fwd_fused`` takes these inputs: fp16 vectors of head_dim 64 with proj_dim 64 matrices, and enough
+    (batch, head) sequences that one CTA each fills the GPU (the kernel does not cut a sequence into segments)."""
+    T, B, H, d = x.shape
+    return (x.dtype == torch.float16 and x.is_cuda and d == 64 and tuple(w.shape[-2:]) == (64, 64)
+            and (B * H >= 120 or T < 1024))
+
+
+def causal_fwd_fused(x_q: Tensor, x_k: Tensor, v: Tensor, w: Tensor, scale: float, row_mask: Optional[Tensor] = None,
+                     s_in: Optional[Tensor] = None, z_in: Optional[Tensor] = None, return_state: bool = False,
+                     save_den: bool = False):
+    """Causal RFA forward from the raw per-head vectors: x_q, x_k, v [T, B, H, 64] fp16, w [H, 64, 64] fp32; the features
+    scale * [sin | cos]((W x) / (|x| + 1e-3)) of q and k are formed inside the kernel.  row_mask [T, B] (or [T * B]) marks
+    padded keys.  Returns out [T, B*H, 64] and, as asked, the final state (s, z) and the workspace holding the raw
+    denominators for ``causal_bwd_saved(..., ws_has=WS_DEN)``: (out[, s, z][, ws])."""
+    require_half(x_q, x_k, v)
+    T, B, H, d = x_q.shape
+    D = w.shape[-2]
+    x_q, x_k, v = x_q.contiguous(), x_k.contiguous(), v.contiguous()
+    w = w.contiguous().float()
+    BH = B * H
+    out = torch.empty(T, BH, d, dtype=torch.float16, device=x_q.device)
+    m = _row_mask(row_mask, T * B, x_q.device)
+    s_out = z_out = None
+    if return_state:
+        s_out = torch.empty(BH, 2 * D, d, dtype=torch.float32, device=x_q.device)
+        z_out = torch.empty(BH, 2 * D, dtype=torch.float32, device=x_q.device)
+    ws = None
+    if save_den:
+        ws, _ = _workspace(max(T, 1), BH, 2 * D, d, x_q)
+    with _guard(x_q):
+        check(_lib.load().rfa_causal_fwd_fused(ptr(x_q), ptr(x_k), ptr(v), ptr(w), ptr(m), float(scale), ptr(out), ptr(s_in),
+                                               ptr(z_in), ptr(s_out), ptr(z_out), ptr(ws), ws.numel() if ws is not None else 0,
+                                               T, B, H, d, D, 1 if save_den else 0, stream_of(x_q)), "rfa_causal_fwd_fused")
+    res = (out,)
+    if return_state:
+        res += (s_out, z_out)
+    if save_den:
+        res += (ws,)
+    return res if len(res) > 1 else out
+
+
 def causal_bwd_saved(q: Tensor, k: Tensor, v: Tensor, g: Tensor, out: Tensor, ws: Tensor, ws_has: int,
                      s_in: Optional[Tensor] = None, z_in: Optional[Tensor] = None):
     """Backward from the forward's output and kept workspace (``causal_fwd_saved``)."""
