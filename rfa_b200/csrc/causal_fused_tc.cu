@@ -16,9 +16,10 @@
 // full (A/P 128, N 2 x 80, [S|z] 80, U_q 64, U_k 64 columns), hence a single A/P buffer: scores of chunk c + 1 follow
 // P V of chunk c in the issuing thread's order.
 //
-// Warp roles (608 threads): 0 = TMA producer; 1 = issuer A (U, scores, P V); 2 = issuer B (phi_q [S|z], state update);
-// 3..6 = score group; 7..10 = output/state group; 11..14 = query features; 15..18 = key features.  Within a group
-// thread <-> TMEM lane <-> token row / state row.  All waits are bounded.
+// Warp roles (640 threads): 0 = TMA producer; 1 = issuer A (scores, P V); 2 = issuer B (phi_q [S|z], state update);
+// 19 = issuer U (the projections: issuing a product costs its thread about as long as the tensor pipe takes to run it, so
+// the three chains are issued by three threads); 3..6 = score group; 7..10 = output/state group; 11..14 = query features;
+// 15..18 = key features.  Within a group thread <-> TMEM lane <-> token row / state row.  All waits are bounded.
 #include <type_traits>
 
 #define RFA_TC_FAMILY 8
@@ -26,7 +27,7 @@
 
 namespace rfa {
 namespace fz {
-constexpr int kThreads_ = 608;
+constexpr int kThreads_ = 640;
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kXq = 0, kXk = kBox, kRaw = 2 * kBox;          // raw ring: two stages of (x_q, x_k)
 constexpr uint32_t kV = 2 * kRaw;                                  // V ring: two stages of one box
@@ -142,31 +143,14 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ issuer A: U of the next chunk, scores, P V
+    // ------------------------------------------------------------------ issuer A: scores, P V
     if (lane == 0) {
       constexpr uint32_t lead = 1u;
-      constexpr uint32_t idU = umma_idesc_f16(128, 64, false, false);    // X W^T
       constexpr uint32_t idA = umma_idesc_f16(128, 128, false, false);   // phi_q phi_k^T
       constexpr uint32_t idPV = umma_idesc_f16(128, 64, false, true);    // P V (B MN-major)
-      const uint64_t dXq = umma_smem_desc(sbase + kXq, 0, 1024, kSwizzle128B), dXk = umma_smem_desc(sbase + kXk, 0, 1024, kSwizzle128B);
-      const uint64_t dW = umma_smem_desc(sbase + kW, 0, 1024, kSwizzle128B);
       const uint64_t dQ = umma_smem_desc(sbase + kPhiQ, 0, 1024, kSwizzle128B), dK = umma_smem_desc(sbase + kPhiK, 0, 1024, kSwizzle128B);
       const uint64_t dV = umma_smem_desc(sbase + kV, kBox, 1024, kSwizzle128B);
-      auto issue_U = [&](int c) -> bool {
-        const int st = c & 1;
-        const uint64_t so = (uint64_t)st * (kRaw >> 4);
-        if (!mbar_wait(&bars[xFull + st], (c >> 1) & 1)) { tc_fail(3); return false; }
-        if (c >= 1 && !mbar_wait(&bars[uFree], (c - 1) & 1)) { tc_fail(4); return false; }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) umma_ss_w(lead, tmem + cUq, dXq + so + (uint64_t)(j * 2), dW + (uint64_t)(j * 2), idU, j > 0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) umma_ss_w(lead, tmem + cUk, dXk + so + (uint64_t)(j * 2), dW + (uint64_t)(j * 2), idU, j > 0);
-        umma_commit(&bars[uFull]);
-        umma_commit(&bars[xEmpty + st]);
-        return true;
-      };
-      bool ok = nchunk > 0 ? issue_U(0) : true;
+      bool ok = true;
 #pragma unroll 1
       for (int c = 0; ok && c < nchunk; ++c) {
         const int st = c & 1;
@@ -176,7 +160,6 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
         umma_chain_ss<8, kStepK, kBlockK, kStepK, kBlockK>(lead, tmem + cA, dQ, dK, idA, 0);
         umma_commit(&bars[aFull]);
         umma_commit(&bars[phiFree]);
-        if (c + 1 < nchunk && !issue_U(c + 1)) break;
         if (!mbar_wait(&bars[pFull], c & 1)) { tc_fail(6); break; }
         if (!mbar_wait(&bars[sDone + st], (c >> 1) & 1)) { tc_fail(7); break; }      // phi_q [S|z] has written the N buffer
         if (!mbar_wait(&bars[vFull + st], (c >> 1) & 1)) { tc_fail(8); break; }
@@ -212,6 +195,29 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
         umma_commit(&bars[sDone + st]);
         umma_commit(&bars[phiFree]);
         umma_commit(&bars[vEmpty + st]);
+      }
+    }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ issuer U: the projections of chunk c as soon as its
+    // raw tiles are in and the feature warps have taken the previous chunk's U out of tensor memory
+    if (lane == 0) {
+      constexpr uint32_t lead = 1u;
+      constexpr uint32_t idU = umma_idesc_f16(128, 64, false, false);    // X W^T
+      const uint64_t dXq = umma_smem_desc(sbase + kXq, 0, 1024, kSwizzle128B), dXk = umma_smem_desc(sbase + kXk, 0, 1024, kSwizzle128B);
+      const uint64_t dW = umma_smem_desc(sbase + kW, 0, 1024, kSwizzle128B);
+#pragma unroll 1
+      for (int c = 0; c < nchunk; ++c) {
+        const int st = c & 1;
+        const uint64_t so = (uint64_t)st * (kRaw >> 4);
+        if (!mbar_wait(&bars[xFull + st], (c >> 1) & 1)) { tc_fail(3); break; }
+        if (c >= 1 && !mbar_wait(&bars[uFree], (c - 1) & 1)) { tc_fail(4); break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) umma_ss_w(lead, tmem + cUq, dXq + so + (uint64_t)(j * 2), dW + (uint64_t)(j * 2), idU, j > 0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) umma_ss_w(lead, tmem + cUk, dXk + so + (uint64_t)(j * 2), dW + (uint64_t)(j * 2), idU, j > 0);
+        umma_commit(&bars[uFull]);
+        umma_commit(&bars[xEmpty + st]);
       }
     }
   } else if (warp < 7) {
@@ -352,7 +358,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
                              __uint_as_float(r[4 * n + 3]));
       z_out[(size_t)bh * kK + row] = __uint_as_float(r[64]);
     }
-  } else {
+  } else if (warp < 19) {
     // ------------------------------------------------------------------ feature groups: query (warps 11..14), key (15..18)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
