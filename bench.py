@@ -384,6 +384,28 @@ def extras(device, stream, hbm):
                               "bwd_frac_of_hbm": T * BH * 512 / (ms_b * 1e-3) / 1e9 / hbm}
     except Exception as e:  # noqa: BLE001
         out["feature_map"] = {"error": repr(e)}
+    # ---- forward from the raw q, k (feature map inside the attention kernel) against the two launches it replaces
+    try:
+        g = torch.Generator().manual_seed(0)
+        xq, xk, xv = (torch.randn(T, B, H, 64, generator=g).half().to(device) for _ in range(3))
+        w = torch.randn(H, 64, 64, generator=g).to(device)
+
+        def two_step():
+            pq = ops.feature_map_fwd(xq, w, 0.1).view(T, BH, K_FEAT)
+            pk = ops.feature_map_fwd(xk, w, 0.1).view(T, BH, K_FEAT)
+            return ops.causal_fwd(pq, pk, xv.view(T, BH, D_HEAD))
+        for _ in range(3):
+            ops.causal_fwd_fused(xq, xk, xv, w, 0.1)
+            two_step()
+        ms_1, how = timed_replayed(lambda: ops.causal_fwd_fused(xq, xk, xv, w, 0.1), 10, stream)
+        ms_2, _ = timed_replayed(two_step, 10, stream)
+        nb = T * BH * 512                 # x_q, x_k, v in and the output out: 4 x 128 bytes per (token, head)
+        out["fused_forward"] = {"workload": "causal forward from raw q, k (feature map inside the kernel), B8 H16 T2048 d64 D64 fp16",
+                                "timing": how + ", 10 calls", "ms": ms_1, "frac_of_hbm": nb / (ms_1 * 1e-3) / 1e9 / hbm,
+                                "algorithmic_bytes": nb, "two_step_ms": ms_2,
+                                "two_step_algorithmic_bytes": T * BH * (2 * 384 + 768)}
+    except Exception as e:  # noqa: BLE001
+        out["fused_forward"] = {"error": repr(e)}
     return out
 
 

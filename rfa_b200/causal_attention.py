@@ -16,7 +16,7 @@ from torch.nn import Parameter
 
 from . import ops
 from .rfa import RFA
-from .utils import (EPS, build_random_matrices, normalize_attn_weights, random_project,
+from .utils import (EPS, SCALE, build_random_matrices, normalize_attn_weights, random_project,
                     upgrade_state_dict_named)
 
 
@@ -133,6 +133,51 @@ def cuda_causal_rfa(*, phi_q: Tensor, phi_k: Tensor, v: Tensor,
     return attn.view(tgt_len, bsz, num_heads * head_dim).to(dtype)
 
 
+class _FusedCausalRFA(torch.autograd.Function):
+    """Causal RFA from the raw per-head q and k: the forward forms the features inside the attention kernel
+    (``ops.causal_fwd_fused``), so phi_q and phi_k are neither written to memory nor kept for the backward; the backward
+    recomputes them with the feature-map kernel and runs the saved-output sweeps from the forward's output and raw
+    denominators, then the feature map's own backward.  Replaces, for the kernel path, upstream's random_project on q and
+    k followed by RFA.apply (causal_attention.py:241-248, 137-147; rfa.py:113-145)."""
+
+    @staticmethod
+    def forward(ctx, x_q, x_k, v, w, scale, row_mask):
+        out, ws = ops.causal_fwd_fused(x_q, x_k, v, w, scale, row_mask=row_mask, save_den=True)
+        ctx.save_for_backward(x_q, x_k, v, w, out, ws)
+        ctx.scale, ctx.row_mask = scale, row_mask
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from . import _lib
+        x_q, x_k, v, w, out, ws = ctx.saved_tensors
+        T, B, H, d = x_q.shape
+        wf = w.float()
+        phi_q = ops.feature_map_fwd(x_q, wf, ctx.scale).view(T, B * H, -1)
+        phi_k = ops.feature_map_fwd(x_k, wf, ctx.scale, row_mask=ctx.row_mask).view(T, B * H, -1)
+        g_pq, g_pk, g_v = ops.causal_bwd_saved(phi_q, phi_k, v.view(T, B * H, d), g.contiguous().to(torch.float16), out, ws,
+                                               _lib.WS_DEN)
+        need_w = ctx.needs_input_grad[3]
+        g_xq, g_wq = ops.feature_map_bwd(x_q, wf, g_pq.view(T, B, H, -1), ctx.scale, need_w)
+        g_xk, g_wk = ops.feature_map_bwd(x_k, wf, g_pk.view(T, B, H, -1), ctx.scale, need_w, row_mask=ctx.row_mask)
+        g_w = (g_wq + g_wk).to(w.dtype) if need_w else None
+        return g_xq, g_xk, g_v.view(T, B, H, d), g_w, None, None
+
+
+def fused_causal_rfa(*, q: Tensor, k: Tensor, v: Tensor, random_matrices: Tensor, scale: float = SCALE,
+                     key_padding_mask: Optional[Tensor] = None) -> Tensor:
+    """q, k, v ``[tgt_len, bsz, num_heads, head_dim]`` fp16 (before the feature map), random_matrices ``[num_heads,
+    proj_dim, head_dim]`` -> ``[tgt_len, bsz, num_heads*head_dim]``: ``cuda_causal_rfa(random_project(q), random_project(k),
+    v)`` in one kernel.  Use ``ops.fused_forward_supported`` to see whether the sizes are ones the kernel is built for."""
+    tgt_len, bsz, num_heads, head_dim = q.shape
+    row_mask = None
+    if key_padding_mask is not None and key_padding_mask.dim() > 0:
+        assert key_padding_mask.shape == (bsz, tgt_len)
+        row_mask = key_padding_mask.to(torch.bool).t().contiguous()
+    attn = _FusedCausalRFA.apply(q.contiguous(), k.contiguous(), v.contiguous(), random_matrices, scale, row_mask)
+    return attn.view(tgt_len, bsz, num_heads * head_dim)
+
+
 class CausalAttention(nn.Module):
     """Random feature causal self-attention layer (upstream causal_attention.py:154-280):
     q/k/v projections, per-head feature map with W' = sigma * W / tau, causal RFA,
@@ -190,6 +235,10 @@ class CausalAttention(nn.Module):
         w = build_random_matrices(random_matrices=random_matrices, tau=self.tau,
                                   sigma=self.sigma if self.reparam_proj else None,
                                   reparam_proj=self.reparam_proj)
+        if saved_state is None and self.cuda_causal_rfa and ops.fused_forward_supported(q, w):
+            # head_dim 64, proj_dim 64, fp16, enough sequences to fill the GPU: features formed inside the kernel
+            attn = fused_causal_rfa(q=q, k=k, v=v, random_matrices=w, key_padding_mask=key_padding_mask)
+            return self.out_proj(attn.to(x.dtype))
         # the padding mask of the kernel path is applied inside the feature map of k (no separate pass over phi_k)
         fused_mask = key_padding_mask if (saved_state is None and self.cuda_causal_rfa) else None
         phi_q = random_project(x=q, random_matrices=w)

@@ -115,3 +115,40 @@ def test_fused_forward_at_the_benchmark_shape(dev):
 def _status():
     from rfa_b200 import _lib
     return _lib.load().rfa_debug_status()
+
+
+def test_causal_attention_module_uses_the_fused_forward(dev, monkeypatch):
+    """A half-precision CausalAttention layer (head_dim 64, proj_dim 64, many heads): the forward goes through the fused
+    kernel; output and every gradient agree with the same layer run through the two-step path."""
+    from rfa_b200 import causal_attention as CA
+    from rfa_b200 import ops
+    T, B, E, H = 256, 4, 512, 8
+    torch.manual_seed(3)
+    layer = CA.CausalAttention(embed_dim=E, num_heads=H, head_dim=64, proj_dim=64, tau=1.0, reparam_proj=True).to(dev).half()
+    w = torch.from_numpy(O.draw_matrices("orf", H, 64, 64, 9)).half().to(dev).requires_grad_(True)
+    x = torch.randn(T, B, E, device=dev).half().requires_grad_(True)
+    pad = torch.zeros(B, T, dtype=torch.bool, device=dev)
+    pad[1, 200:] = True
+    pad[3, 77:] = True
+    up = torch.randn(T, B, E, device=dev).half()
+
+    calls = []
+    real = ops.causal_fwd_fused
+    monkeypatch.setattr(ops, "causal_fwd_fused", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+
+    def run():
+        for p in list(layer.parameters()) + [w, x]:
+            p.grad = None
+        y = layer(x, w, key_padding_mask=pad)
+        y.backward(up)
+        return [y.detach().clone(), x.grad.clone(), w.grad.clone()] + [p.grad.clone() for p in layer.parameters()]
+
+    fused = run()
+    assert calls, "the fused forward was not used"
+    monkeypatch.setattr(ops, "fused_forward_supported", lambda *_: False)
+    n = len(calls)
+    two = run()
+    assert len(calls) == n
+    names = ["out", "g_x", "g_w"] + ["g_" + k for k, _ in layer.named_parameters()]
+    for a, b, name in zip(fused, two, names):
+        assert_close(a, b, "module " + name, rel=2e-3)
