@@ -138,7 +138,9 @@ class _FusedCausalRFA(torch.autograd.Function):
     (``ops.causal_fwd_fused``), so phi_q and phi_k are neither written to memory nor kept for the backward; the backward
     recomputes them with the feature-map kernel and runs the saved-output sweeps from the forward's output and raw
     denominators, then the feature map's own backward.  Replaces, for the kernel path, upstream's random_project on q and
-    k followed by RFA.apply (causal_attention.py:241-248, 137-147; rfa.py:113-145)."""
+    k followed by RFA.apply (causal_attention.py:241-248, 137-147; rfa.py:113-145).  A trade of time for memory when a
+    gradient is wanted: the step saves the two feature tensors and one launch in the forward and pays two feature-map
+    launches in the backward."""
 
     @staticmethod
     def forward(ctx, x_q, x_k, v, w, scale, row_mask):
@@ -190,6 +192,9 @@ class CausalAttention(nn.Module):
         self.embed_dim, self.num_heads, self.head_dim = embed_dim, num_heads, head_dim
         self.proj_dim, self.tau = proj_dim, tau
         self.reparam_proj, self.cuda_causal_rfa = reparam_proj, cuda_causal_rfa
+        # training with the feature map inside the attention kernel: phi_q, phi_k are then not kept for the backward (which
+        # recomputes them), at the price of those two extra launches; an addition, off by default
+        self.fuse_feature_map = False
         self.q_proj = nn.Linear(embed_dim, embed_dim, bias=True)
         self.k_proj = nn.Linear(embed_dim, embed_dim, bias=True)
         self.v_proj = nn.Linear(embed_dim, embed_dim, bias=True)
@@ -235,8 +240,12 @@ class CausalAttention(nn.Module):
         w = build_random_matrices(random_matrices=random_matrices, tau=self.tau,
                                   sigma=self.sigma if self.reparam_proj else None,
                                   reparam_proj=self.reparam_proj)
-        if saved_state is None and self.cuda_causal_rfa and ops.fused_forward_supported(q, w):
-            # head_dim 64, proj_dim 64, fp16, enough sequences to fill the GPU: features formed inside the kernel
+        recording = torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or self.q_proj.weight.requires_grad)
+        if (saved_state is None and self.cuda_causal_rfa and ops.fused_forward_supported(q, w)
+                and (self.fuse_feature_map if recording else True)):
+            # head_dim 64, proj_dim 64, fp16, enough sequences to fill the GPU: features formed inside the kernel.  Always
+            # when no gradient is recorded (prefill, evaluation: one launch instead of three); when one is, only on
+            # request (fuse_feature_map), because the backward then has to form the features again
             attn = fused_causal_rfa(q=q, k=k, v=v, random_matrices=w, key_padding_mask=key_padding_mask)
             return self.out_proj(attn.to(x.dtype))
         # the padding mask of the kernel path is applied inside the feature map of k (no separate pass over phi_k)

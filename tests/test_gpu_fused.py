@@ -118,8 +118,9 @@ def _status():
 
 
 def test_causal_attention_module_uses_the_fused_forward(dev, monkeypatch):
-    """A half-precision CausalAttention layer (head_dim 64, proj_dim 64, many heads): the forward goes through the fused
-    kernel; output and every gradient agree with the same layer run through the two-step path."""
+    """A half-precision CausalAttention layer (head_dim 64, proj_dim 64, many heads): without a gradient, and on request
+    with one, the forward goes through the fused kernel; output and every gradient agree with the same layer run through
+    the two-step path."""
     from rfa_b200 import causal_attention as CA
     from rfa_b200 import ops
     T, B, E, H = 256, 4, 512, 8
@@ -135,6 +136,15 @@ def test_causal_attention_module_uses_the_fused_forward(dev, monkeypatch):
     calls = []
     real = ops.causal_fwd_fused
     monkeypatch.setattr(ops, "causal_fwd_fused", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    # without a gradient the layer takes the fused kernel by itself; with one, only when asked to
+    with torch.no_grad():
+        y0 = layer(x, w, key_padding_mask=pad)
+    assert len(calls) == 1
+    y1 = layer(x, w, key_padding_mask=pad)
+    assert len(calls) == 1
+    assert_close(y0, y1, "module out, no-grad fused vs recorded two-step", rel=2e-3)
+    calls.clear()
+    layer.fuse_feature_map = True
 
     def run():
         for p in list(layer.parameters()) + [w, x]:
