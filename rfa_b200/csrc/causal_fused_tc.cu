@@ -16,10 +16,14 @@
 // full (A/P 128, N 2 x 80, [S|z] 80, U_q 64, U_k 64 columns), hence a single A/P buffer: scores of chunk c + 1 follow
 // P V of chunk c in the issuing thread's order.
 //
-// Warp roles (640 threads): 0 = TMA producer; 1 = issuer A (scores, P V); 2 = issuer B (phi_q [S|z], state update);
-// 19 = issuer U (the projections: issuing a product costs its thread about as long as the tensor pipe takes to run it, so
-// the three chains are issued by three threads); 3..6 = score group; 7..10 = output/state group; 11..14 = query features;
-// 15..18 = key features.  Within a group thread <-> TMEM lane <-> token row / state row.  All waits are bounded.
+// Warp roles (896 threads, seven warpgroups): 0 = TMA producer; 1 = issuer A (scores, P V); 2 = issuer B (phi_q [S|z],
+// state update); 3 = issuer U (the projections: issuing a product costs its thread about as long as the tensor pipe takes
+// to run it, so the three chains are issued by three threads); 4..7 = score group; 8..11 = output/state group; 12..19 =
+// query features, 20..27 = key features (two warpgroups each: thread <-> row, and half of the 64 projected columns per
+// warpgroup -- the sines and cosines are the longest step of a chunk and bound by the special-function unit, which
+// sixteen warps keep busier than eight).  Register budgets differ by role (setmaxnreg): issuers 64, score group 104,
+// output/state group 112, feature warps 56.  Within a group thread <-> TMEM lane <-> token row / state row.  All waits
+// are bounded.
 #include <type_traits>
 
 #define RFA_TC_FAMILY 8
@@ -27,7 +31,7 @@
 
 namespace rfa {
 namespace fz {
-constexpr int kThreads_ = 640;
+constexpr int kThreads_ = 896;
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kXq = 0, kXk = kBox, kRaw = 2 * kBox;          // raw ring: two stages of (x_q, x_k)
 constexpr uint32_t kV = 2 * kRaw;                                  // V ring: two stages of one box
@@ -42,7 +46,7 @@ static_assert(kSmem <= 227 * 1024, "causal_fwd_fused: shared memory map");
 // TMEM columns
 constexpr uint32_t cA = 0, cN = 128, cS = 288, cUq = 368, cUk = 432;
 enum { xFull = 0, xEmpty = 2, vFull = 4, vEmpty = 6, uFull = 8, uFree = 9, phiFull = 10, phiFree = 11, aFull = 12, pFull = 13,
-       sDone = 14, nFull = 16, nFree = 18, bSt = 20, bNum = 21 };
+       sDone = 14, nFull = 16, nFree = 18, bSt = 20, bCarry = 21, bNum = 22 };
 // xFull/xEmpty: a raw stage (free once U has been formed from it and both feature groups have taken their rows' norms);
 // vFull/vEmpty: a V tile (free once P V and the state update have read it); uFull/uFree: the U accumulators;
 // phiFull/phiFree: the feature tiles (free = both issuers' products of the chunk are complete); aFull/pFull: scores
@@ -71,7 +75,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[xFull + i], 1);
-      mbar_init(&bars[xEmpty + i], 257);      // issuer A's commit + both feature groups
+      mbar_init(&bars[xEmpty + i], 513);      // issuer U's commit + the four feature warpgroups
       mbar_init(&bars[vFull + i], 1);
       mbar_init(&bars[vEmpty + i], 2);        // one commit from each issuer
       mbar_init(&bars[sDone + i], 1);
@@ -79,12 +83,13 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       mbar_init(&bars[nFree + i], 128);
     }
     mbar_init(&bars[uFull], 1);
-    mbar_init(&bars[uFree], 256);
-    mbar_init(&bars[phiFull], 256);
+    mbar_init(&bars[uFree], 512);
+    mbar_init(&bars[phiFull], 512);
     mbar_init(&bars[phiFree], 2);             // one commit from each issuer
     mbar_init(&bars[aFull], 1);
     mbar_init(&bars[pFull], 128);
     mbar_init(&bars[bSt], 128);
+    mbar_init(&bars[bCarry], 128);
     mbar_fence_init();
     tma_prefetch_desc(&tm_xq); tma_prefetch_desc(&tm_xk); tma_prefetch_desc(&tm_v);
   }
@@ -110,25 +115,23 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
     u.x = pack_half2(a.x, a.y); u.y = pack_half2(a.z, a.w); u.z = pack_half2(b.x, b.y); u.w = pack_half2(b.z, b.w);
     *reinterpret_cast<uint4*>(sm + kW + row_chunk1(j, ch)) = u;
   }
-  // The state entering the sequence is fetched here, before the first TMA load is issued, by the threads that will store
-  // it (output/state group: thread <-> state row).  Fetched after the barrier instead, these global loads coincide with
-  // the landing of the first raw tiles, and the feature warps' first reads of those tiles then returned stale data.
-  uint32_t carry[65];
-  if (warp >= 7 && warp < 11) {
-    const int srow = (warp & 3) * 32 + lane;
-#pragma unroll
-    for (int n = 0; n < 64; ++n) carry[n] = s_in ? __float_as_uint(s_in[(size_t)srow * kD + n]) : 0u;
-    carry[64] = z_in ? __float_as_uint(z_in[srow]) : 0u;
-  }
   fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
+  // Register budgets by role (the kernel starts with 72 per thread): the issuers and the feature warps give some back,
+  // the score and output/state groups take more.  Each branch below is one or more whole warpgroups.
+  if (warp < 4) {
+  setmaxnreg_dec<64>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // The state entering the sequence is fetched by the output/state group before the first TMA load is issued: with
+      // those global loads in flight while the first raw tiles landed, the feature warps' first reads of the tiles
+      // returned stale data in an earlier version of this kernel.
+      if (s_in && !mbar_wait(&bars[bCarry], 0)) tc_fail(20);
       for (int c = 0; c < nchunk; ++c) {
         const int st = c & 1;
         const int t0 = c * kTC;
@@ -197,7 +200,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
         umma_commit(&bars[vEmpty + st]);
       }
     }
-  } else if (warp == 19) {
+  } else if (warp == 3) {
     // ------------------------------------------------------------------ issuer U: the projections of chunk c as soon as its
     // raw tiles are in and the feature warps have taken the previous chunk's U out of tensor memory
     if (lane == 0) {
@@ -220,7 +223,9 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
         umma_commit(&bars[xEmpty + st]);
       }
     }
-  } else if (warp < 7) {
+  }
+  } else if (warp < 8) {
+    setmaxnreg_inc<104>();
     // ------------------------------------------------------------------ score group: P = mask(A), row sums
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -265,7 +270,8 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       tc_fence_before_sync();
       mbar_arrive(&bars[pFull]);
     }
-  } else if (warp < 11) {
+  } else if (warp < 12) {
+    setmaxnreg_inc<112>();
     // ------------------------------------------------------------------ output / state group
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // token row in the chunk / state row k
@@ -275,9 +281,17 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
     {
       uint32_t r[80];
 #pragma unroll
-      for (int n = 0; n < 65; ++n) r[n] = carry[n];
+      for (int n = 0; n < 64; ++n) r[n] = s_in ? __float_as_uint(s_in[(size_t)row * kD + n]) : 0u;
+      r[64] = z_in ? __float_as_uint(z_in[row]) : 0u;
 #pragma unroll
       for (int n = 65; n < 80; ++n) r[n] = 0u;
+      if (s_in) {                       // every value has arrived (they are used below): the producer may start
+        uint32_t any = 0;
+#pragma unroll
+        for (int n = 0; n < 65; ++n) any |= r[n];
+        asm volatile("" ::"r"(any) : "memory");
+        mbar_arrive(&bars[bCarry]);
+      }
       store_state_row(s_tile, row, r);
 #pragma unroll
       for (int ch = 1; ch < 8; ++ch) *reinterpret_cast<uint4*>(s_tile + kBox + row_chunk1(row, ch)) = make_uint4(0, 0, 0, 0);
@@ -358,12 +372,14 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
                              __uint_as_float(r[4 * n + 3]));
       z_out[(size_t)bh * kK + row] = __uint_as_float(r[64]);
     }
-  } else if (warp < 19) {
-    // ------------------------------------------------------------------ feature groups: query (warps 11..14), key (15..18)
+  } else {
+    setmaxnreg_dec<56>();
+    // ------------------------------------------------------------------ feature groups: query (warps 12..19), key (20..27)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const bool is_key = warp >= 15;
+    const bool is_key = warp >= 20;
+    const int half = ((warp - 12) >> 2) & 1;       // which 32 of the 64 projected columns
     const uint32_t colU = is_key ? cUk : cUq;
     unsigned char* tile = sm + (is_key ? kPhiK : kPhiQ);
     const int nb = BH / H;                           // batch size: row_mask is [T][batch]
@@ -376,9 +392,8 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       // every byte of it
       if (!mbar_wait(&bars[uFull], c & 1)) { tc_fail(18); break; }
       tc_fence_after_sync();
-      uint32_t u[64];
-      tmem_ld32(tmem + lane_addr + colU, u);
-      tmem_ld32(tmem + lane_addr + colU + 32, u + 32);
+      uint32_t u[32];
+      tmem_ld32(tmem + lane_addr + colU + 32 * half, u);
       float ss = 0.f, ss_b = 0.f;                    // |x|^2 of this thread's row
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
@@ -399,7 +414,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       mbar_arrive(&bars[uFree]);
       // features into registers, packed fp16 in place: u[2i] <- the sines, u[2i + 1] <- the cosines of columns 2i, 2i + 1 ...
 #pragma unroll
-      for (int i = 0; i < 32; i += 1) {
+      for (int i = 0; i < 16; i += 1) {
         float s0, c0, s1, c1;
         __sincosf(__uint_as_float(u[2 * i]) * inv, &s0, &c0);
         __sincosf(__uint_as_float(u[2 * i + 1]) * inv, &s1, &c1);
@@ -410,9 +425,9 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       // ... and into the operand tile once the products of the previous chunk have let go of it
       if (c >= 1 && !mbar_wait(&bars[phiFree], (c - 1) & 1)) { tc_fail(19); break; }
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        *reinterpret_cast<uint4*>(tile + row_chunk2(row, ch)) = make_uint4(u[8 * ch], u[8 * ch + 2], u[8 * ch + 4], u[8 * ch + 6]);           // sin block
-        *reinterpret_cast<uint4*>(tile + row_chunk2(row, 8 + ch)) = make_uint4(u[8 * ch + 1], u[8 * ch + 3], u[8 * ch + 5], u[8 * ch + 7]);   // cos block
+      for (int ch = 0; ch < 4; ++ch) {
+        *reinterpret_cast<uint4*>(tile + row_chunk2(row, 4 * half + ch)) = make_uint4(u[8 * ch], u[8 * ch + 2], u[8 * ch + 4], u[8 * ch + 6]);           // sin block
+        *reinterpret_cast<uint4*>(tile + row_chunk2(row, 8 + 4 * half + ch)) = make_uint4(u[8 * ch + 1], u[8 * ch + 3], u[8 * ch + 5], u[8 * ch + 7]);   // cos block
       }
       fence_async_smem();
       mbar_arrive(&bars[phiFull]);
