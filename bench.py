@@ -378,7 +378,12 @@ def extras(device, stream, hbm):
             ops.feature_map_fwd(x, w, 0.1)
         ms_f, how = timed_replayed(lambda: ops.feature_map_fwd(x, w, 0.1), 10, stream)
         ms_b, _ = timed_replayed(lambda: ops.feature_map_bwd(x, w, gp, 0.1, True), 10, stream)
+        ms_pf, _ = timed_replayed(lambda: ops.feature_map_fwd_pair(x, x, w, 0.1), 10, stream)
+        ms_pb, _ = timed_replayed(lambda: ops.feature_map_bwd_pair(x, x, w, gp, gp, 0.1, True), 10, stream)
         nb = T * BH * 384
+        out["feature_map_pair"] = {"workload": "q and k of one layer in one launch each way, same shape as feature_map",
+                                   "fwd_ms": ms_pf, "fwd_frac_of_hbm": 2 * nb / (ms_pf * 1e-3) / 1e9 / hbm,
+                                   "bwd_ms": ms_pb, "bwd_frac_of_hbm": 2 * T * BH * 512 / (ms_pb * 1e-3) / 1e9 / hbm}
         out["feature_map"] = {"timing": how + ", 10 calls", "fwd_ms": ms_f, "fwd_GBps": nb / (ms_f * 1e-3) / 1e9, "fwd_frac_of_hbm": nb / (ms_f * 1e-3) / 1e9 / hbm,
                               "bwd_ms": ms_b, "bwd_GBps": T * BH * 512 / (ms_b * 1e-3) / 1e9,
                               "bwd_frac_of_hbm": T * BH * 512 / (ms_b * 1e-3) / 1e9 / hbm}

@@ -105,6 +105,24 @@ int rfa_feature_map_bwd_masked(const void* x, int x_dtype, const float* w,
                                int64_t rows, int H, int d, int D, float scale,
                                rfa_stream_t stream);
 
+/* The same for two arrays of one shape that share w (q and k of a self-attention
+ * layer: random_project is called on both, causal_attention.py:241-248) in ONE
+ * launch: one ramp and one copy of W_h instead of two, and in the backward one g_w
+ * accumulator for both (g_w receives the sum of the two contributions).  fp16
+ * arrays with d = D = 64 only (RFA_EUNSUPPORTED otherwise); either mask may be
+ * NULL. */
+int rfa_feature_map_fwd_pair(const void* x_a, const void* x_b, const float* w,
+                             const uint8_t* row_mask_a, const uint8_t* row_mask_b,
+                             void* phi_a, void* phi_b,
+                             int64_t rows, int H, int d, int D, float scale,
+                             rfa_stream_t stream);
+int rfa_feature_map_bwd_pair(const void* x_a, const void* x_b, const float* w,
+                             const uint8_t* row_mask_a, const uint8_t* row_mask_b,
+                             const void* g_phi_a, const void* g_phi_b,
+                             void* g_x_a, void* g_x_b, float* g_w,
+                             int64_t rows, int H, int d, int D, float scale,
+                             rfa_stream_t stream);
+
 /* Effective random matrices for a whole step in one launch:
  *   out[i] = sigma[i] * bank[idx[i]] * inv_tau[i],  i < n_out
  * bank [n_bank, D, d] (fp16 or fp32, resident on the device), idx [n_out] int64,

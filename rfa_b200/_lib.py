@@ -30,6 +30,8 @@ SIGNATURES = {
     "rfa_status_peek": (_int, []),
     "rfa_feature_map_fwd": (_int, [_vp, _int, _vp, _vp, _int, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_feature_map_bwd": (_int, [_vp, _int, _vp, _vp, _int, _vp, _int, _vp, _i64, _int, _int, _int, _f32, _vp]),
+    "rfa_feature_map_fwd_pair": (_int, [_vp] * 7 + [_i64, _int, _int, _int, _f32, _vp]),
+    "rfa_feature_map_bwd_pair": (_int, [_vp] * 10 + [_i64, _int, _int, _int, _f32, _vp]),
     "rfa_feature_map_fwd_masked": (_int, [_vp, _int, _vp, _vp, _vp, _int, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_feature_map_bwd_masked": (_int, [_vp, _int, _vp, _vp, _vp, _int, _vp, _int, _vp, _i64, _int, _int, _int, _f32, _vp]),
     "rfa_gather_random_matrices": (_int, [_vp, _int, _i64, _vp, _i64, _vp, _vp, _vp, _int, _int, _vp, _vp]),

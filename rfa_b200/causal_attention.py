@@ -16,7 +16,7 @@ from torch.nn import Parameter
 
 from . import ops
 from .rfa import RFA
-from .utils import (EPS, SCALE, build_random_matrices, normalize_attn_weights, random_project,
+from .utils import (EPS, SCALE, build_random_matrices, normalize_attn_weights, random_project, random_project_pair,
                     upgrade_state_dict_named)
 
 
@@ -155,15 +155,13 @@ class _FusedCausalRFA(torch.autograd.Function):
         x_q, x_k, v, w, out, ws = ctx.saved_tensors
         T, B, H, d = x_q.shape
         wf = w.float()
-        phi_q = ops.feature_map_fwd(x_q, wf, ctx.scale).view(T, B * H, -1)
-        phi_k = ops.feature_map_fwd(x_k, wf, ctx.scale, row_mask=ctx.row_mask).view(T, B * H, -1)
-        g_pq, g_pk, g_v = ops.causal_bwd_saved(phi_q, phi_k, v.view(T, B * H, d), g.contiguous().to(torch.float16), out, ws,
-                                               _lib.WS_DEN)
+        phi_q, phi_k = ops.feature_map_fwd_pair(x_q, x_k, wf, ctx.scale, None, ctx.row_mask)      # one launch for both
+        g_pq, g_pk, g_v = ops.causal_bwd_saved(phi_q.view(T, B * H, -1), phi_k.view(T, B * H, -1), v.view(T, B * H, d),
+                                               g.contiguous().to(torch.float16), out, ws, _lib.WS_DEN)
         need_w = ctx.needs_input_grad[3]
-        g_xq, g_wq = ops.feature_map_bwd(x_q, wf, g_pq.view(T, B, H, -1), ctx.scale, need_w)
-        g_xk, g_wk = ops.feature_map_bwd(x_k, wf, g_pk.view(T, B, H, -1), ctx.scale, need_w, row_mask=ctx.row_mask)
-        g_w = (g_wq + g_wk).to(w.dtype) if need_w else None
-        return g_xq, g_xk, g_v.view(T, B, H, d), g_w, None, None
+        g_xq, g_xk, g_w = ops.feature_map_bwd_pair(x_q, x_k, wf, g_pq.view(T, B, H, -1), g_pk.view(T, B, H, -1), ctx.scale,
+                                                   need_w, None, ctx.row_mask)
+        return g_xq, g_xk, g_v.view(T, B, H, d), (g_w.to(w.dtype) if need_w else None), None, None
 
 
 def fused_causal_rfa(*, q: Tensor, k: Tensor, v: Tensor, random_matrices: Tensor, scale: float = SCALE,
@@ -250,8 +248,7 @@ class CausalAttention(nn.Module):
             return self.out_proj(attn.to(x.dtype))
         # the padding mask of the kernel path is applied inside the feature map of k (no separate pass over phi_k)
         fused_mask = key_padding_mask if (saved_state is None and self.cuda_causal_rfa) else None
-        phi_q = random_project(x=q, random_matrices=w)
-        phi_k = random_project(x=k, random_matrices=w, key_padding_mask=fused_mask)
+        phi_q, phi_k = random_project_pair(x_a=q, x_b=k, random_matrices=w, key_padding_mask_b=fused_mask)
         if saved_state is not None:
             assert tgt_len == 1
             prev_s, prev_z = saved_state.get("prev_s"), saved_state.get("prev_z")

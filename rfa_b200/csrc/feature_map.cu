@@ -192,9 +192,10 @@ feature_map_bwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, co
 }
 
 // tensor-core forward for fp16 rows with head_dim = proj_dim = 64 (feature_map_tc.cu)
-int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* row_mask, __half* phi, int64_t rows, int H, float scale,
-                              int sms, cudaStream_t st);
-int launch_feature_map_bwd_tc(const __half* x, const float* w, const uint8_t* row_mask, const __half* g_phi, __half* g_x, float* g_w,
+int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* row_mask, __half* phi, const __half* x2,
+                              const uint8_t* row_mask2, __half* phi2, int64_t rows, int H, float scale, int sms, cudaStream_t st);
+int launch_feature_map_bwd_tc(const __half* x, const float* w, const uint8_t* row_mask, const __half* g_phi, __half* g_x,
+                              const __half* x2, const uint8_t* row_mask2, const __half* g_phi2, __half* g_x2, float* g_w,
                               int64_t rows, int H, float scale, int sms, cudaStream_t st);
 
 static int fm_check(const void* x, const float* w, int64_t rows, int H, int d, int D) {
@@ -238,7 +239,8 @@ extern "C" int rfa_feature_map_fwd_masked(const void* x, int x_dtype, const floa
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return launch_feature_map_fwd_tc((const __half*)x, w, row_mask, (__half*)phi, rows, H, scale, sms, as_stream(stream));
+    return launch_feature_map_fwd_tc((const __half*)x, w, row_mask, (__half*)phi, nullptr, nullptr, nullptr, rows, H, scale, sms,
+                                     as_stream(stream));
   }
   size_t smem = 0;
   const int R = fm_pick_rows(D, d, false, false, &smem);
@@ -278,8 +280,8 @@ extern "C" int rfa_feature_map_bwd_masked(const void* x, int x_dtype, const floa
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return launch_feature_map_bwd_tc((const __half*)x, w, row_mask, (const __half*)g_phi, (__half*)g_x, g_w, rows, H, scale, sms,
-                                     as_stream(stream));
+    return launch_feature_map_bwd_tc((const __half*)x, w, row_mask, (const __half*)g_phi, (__half*)g_x, nullptr, nullptr, nullptr,
+                                     nullptr, g_w, rows, H, scale, sms, as_stream(stream));
   }
   size_t smem = 0;
   const int R = fm_pick_rows(D, d, true, g_w != nullptr, &smem);
@@ -303,6 +305,42 @@ extern "C" int rfa_feature_map_bwd(const void* x, int x_dtype, const float* w, c
                                    void* g_x, int gx_dtype, float* g_w, int64_t rows, int H, int d, int D,
                                    float scale, rfa_stream_t stream) {
   return rfa_feature_map_bwd_masked(x, x_dtype, w, nullptr, g_phi, g_dtype, g_x, gx_dtype, g_w, rows, H, d, D, scale, stream);
+}
+
+// The feature maps of two arrays of one shape that share W (q and k of a self-attention layer) in one launch: one ramp
+// and one W tile instead of two, and in the backward one g_W accumulator for both.  fp16, head_dim = proj_dim = 64 only
+// (RFA_EUNSUPPORTED otherwise: call the single-array entry points twice).
+extern "C" int rfa_feature_map_fwd_pair(const void* x_a, const void* x_b, const float* w, const uint8_t* row_mask_a,
+                                        const uint8_t* row_mask_b, void* phi_a, void* phi_b, int64_t rows, int H, int d, int D,
+                                        float scale, rfa_stream_t stream) {
+  if (int e = fm_check(x_a, w, rows, H, d, D)) return e;
+  RFA_REQUIRE(d == 64 && D == 64, RFA_EUNSUPPORTED, "feature_map_fwd_pair: built for head_dim = proj_dim = 64, fp16 (got %d, %d)", d, D);
+  RFA_REQUIRE(rows == 0 || (x_b && phi_a && phi_b), RFA_EINVAL, "feature_map_fwd_pair: null pointer");
+  RFA_REQUIRE(aligned16(x_a) && aligned16(x_b) && aligned16(w) && aligned16(phi_a) && aligned16(phi_b), RFA_EALIGN,
+              "feature_map_fwd_pair: 16-byte alignment required");
+  if (rows == 0) return 0;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return launch_feature_map_fwd_tc((const __half*)x_a, w, row_mask_a, (__half*)phi_a, (const __half*)x_b, row_mask_b, (__half*)phi_b,
+                                   rows, H, scale, sms, as_stream(stream));
+}
+
+extern "C" int rfa_feature_map_bwd_pair(const void* x_a, const void* x_b, const float* w, const uint8_t* row_mask_a,
+                                        const uint8_t* row_mask_b, const void* g_phi_a, const void* g_phi_b, void* g_x_a,
+                                        void* g_x_b, float* g_w, int64_t rows, int H, int d, int D, float scale,
+                                        rfa_stream_t stream) {
+  if (int e = fm_check(x_a, w, rows, H, d, D)) return e;
+  RFA_REQUIRE(d == 64 && D == 64, RFA_EUNSUPPORTED, "feature_map_bwd_pair: built for head_dim = proj_dim = 64, fp16 (got %d, %d)", d, D);
+  RFA_REQUIRE(rows == 0 || (x_b && g_phi_a && g_phi_b && g_x_a && g_x_b), RFA_EINVAL, "feature_map_bwd_pair: null pointer");
+  RFA_REQUIRE(aligned16(x_a) && aligned16(x_b) && aligned16(w) && aligned16(g_phi_a) && aligned16(g_phi_b) && aligned16(g_x_a) &&
+                  aligned16(g_x_b) && aligned16(g_w), RFA_EALIGN, "feature_map_bwd_pair: 16-byte alignment required");
+  if (rows == 0) return 0;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return launch_feature_map_bwd_tc((const __half*)x_a, w, row_mask_a, (const __half*)g_phi_a, (__half*)g_x_a, (const __half*)x_b,
+                                   row_mask_b, (const __half*)g_phi_b, (__half*)g_x_b, g_w, rows, H, scale, sms, as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -17,7 +17,9 @@ enum { bFull = 0, bEmpty = 2, bU = 4, bUFree = 6, bEpi = 8, bNum = 9 };
 
 __global__ void __launch_bounds__(fm::kThreads_, 2)
 feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_phi,
-                          const float* __restrict__ w, const uint8_t* __restrict__ row_mask, int64_t rows, int H, float scale) {
+                          const __grid_constant__ CUtensorMap tm_x2, const __grid_constant__ CUtensorMap tm_phi2,
+                          const float* __restrict__ w, const uint8_t* __restrict__ row_mask, const uint8_t* __restrict__ row_mask2,
+                          int64_t rows, int H, float scale, int pair) {
   using namespace fm;
   extern __shared__ unsigned char fm_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fm_raw) + 1023) & ~uintptr_t(1023));
@@ -26,16 +28,25 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
   const uint32_t sbase = smem_u32(sm);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
-  const int ntile_all = (int)((rows + kTC - 1) / kTC);
+  // pair != 0: two arrays of the same shape share the launch and W_h (phi of q and of k): virtual tile v is row tile
+  // v / 2 of array v % 2
+  const int ntile_all = (int)((rows + kTC - 1) / kTC) * (pair ? 2 : 1);
   const int ntile = blockIdx.x < ntile_all ? (ntile_all - 1 - blockIdx.x) / gridDim.x + 1 : 0;   // tiles blockIdx.x, +gridDim.x, ...
+  auto tile_row0 = [&](int i, int& which) -> int {
+    const int v = blockIdx.x + i * gridDim.x;
+    which = pair ? (v & 1) : 0;
+    return (pair ? (v >> 1) : v) * kTC;
+  };
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(&bars[bFull + i], 1); mbar_init(&bars[bEmpty + i], 129); mbar_init(&bars[bU + i], 1); mbar_init(&bars[bUFree + i], 128); }
     mbar_init(&bars[bEpi], 128);
     mbar_fence_init();
     // the first tiles are requested before the rest of the prologue (W_h, tensor memory), which their flight then hides
     for (int i = 0; i < 2 && i < ntile; ++i) {
+      int which;
+      const int row0 = tile_row0(i, which);
       mbar_arrive_expect_tx(&bars[bFull + i], kBox);
-      tma_load_3d(sm + kX + i * kStage, &tm_x, &bars[bFull + i], 0, h, (blockIdx.x + i * gridDim.x) * kTC);
+      tma_load_3d(sm + kX + i * kStage, which ? &tm_x2 : &tm_x, &bars[bFull + i], 0, h, row0);
     }
     tma_prefetch_desc(&tm_phi);
   }
@@ -60,9 +71,10 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       for (int i = 2; i < ntile; ++i) {
         const int st = i & 1;
         if (!mbar_wait(&bars[bEmpty + st], ((i >> 1) + 1) & 1)) { tc_fail(1); break; }
-        const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+        int which;
+        const int row0 = tile_row0(i, which);
         mbar_arrive_expect_tx(&bars[bFull + st], kBox);
-        tma_load_3d(sm + kX + st * kStage, &tm_x, &bars[bFull + st], 0, h, row0);
+        tma_load_3d(sm + kX + st * kStage, which ? &tm_x2 : &tm_x, &bars[bFull + st], 0, h, row0);
       }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -87,7 +99,9 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
     bool ok = true;
     for (int i = 0; ok && i < ntile; ++i) {
       const int st = i & 1;
-      const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+      int which;
+      const int row0 = tile_row0(i, which);
+      const uint8_t* mask = which ? row_mask2 : row_mask;
       if (!mbar_wait(&bars[bFull + st], (i >> 1) & 1)) { tc_fail(4); ok = false; break; }
       float ss = 0.f;                                  // |x|^2 of this thread's row
 #pragma unroll
@@ -114,7 +128,7 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
         if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(6); ok = false; break; }
       }
       // a masked row (a padded key) gets all-zero features
-      const float sc_row = (row_mask && (int64_t)row0 + row < rows && row_mask[(int64_t)row0 + row]) ? 0.f : scale;
+      const float sc_row = (mask && (int64_t)row0 + row < rows && mask[(int64_t)row0 + row]) ? 0.f : scale;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         float sn[8], cs[8];
@@ -133,8 +147,8 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       fence_async_smem();
       if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(7); ok = false; break; }
       if (etid == 0) {
-        tma_store_3d(&tm_phi, sm + kOut, 0, h, row0);
-        tma_store_3d(&tm_phi, sm + kOut + kBox, 64, h, row0);
+        tma_store_3d(which ? &tm_phi2 : &tm_phi, sm + kOut, 0, h, row0);
+        tma_store_3d(which ? &tm_phi2 : &tm_phi, sm + kOut + kBox, 64, h, row0);
         tma_store_commit();
       }
     }
@@ -145,19 +159,23 @@ feature_map_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
   if (warp == 1) tmem_dealloc(tmem, 128);
 }
 
-// x [rows][H][64] fp16, w [H][64][64] fp32, phi [rows][H][128] fp16
-int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* row_mask, __half* phi, int64_t rows, int H, float scale,
-                              int sms, cudaStream_t st) {
-  CUtensorMap tx, tp;
-  if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tp, phi, rows, H, 128, kTC))
+// x [rows][H][64] fp16, w [H][64][64] fp32, phi [rows][H][128] fp16; x2 / phi2 / row_mask2: a second array of the same
+// shape sharing the launch (null: none)
+int launch_feature_map_fwd_tc(const __half* x, const float* w, const uint8_t* row_mask, __half* phi, const __half* x2,
+                              const uint8_t* row_mask2, __half* phi2, int64_t rows, int H, float scale, int sms, cudaStream_t st) {
+  const int pair = x2 != nullptr;
+  CUtensorMap tx, tp, tx2, tp2;
+  if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tp, phi, rows, H, 128, kTC) ||
+      make_tmap_rows(&tx2, pair ? x2 : x, rows, H, 64, kTC) || make_tmap_rows(&tp2, pair ? phi2 : phi, rows, H, 128, kTC))
     return fail(RFA_EDEVICE, "feature_map_fwd: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(feature_map_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fm::kSmem);
   if (e != cudaSuccess) return fail((int)e, "feature_map_fwd: cannot reserve %u bytes of shared memory: %s", fm::kSmem, cudaGetErrorString(e));
-  const int64_t ntile = (rows + kTC - 1) / kTC;
+  const int64_t ntile = (rows + kTC - 1) / kTC * (pair ? 2 : 1);
   int64_t gx = 2LL * sms / H;                    // two CTAs per SM, and never more CTAs than fit at once
   if (gx > ntile) gx = ntile;
   if (gx < 1) gx = 1;
-  feature_map_fwd_tc_kernel<<<dim3((unsigned)gx, H), fm::kThreads_, fm::kSmem, st>>>(tx, tp, w, row_mask, rows, H, scale);
+  feature_map_fwd_tc_kernel<<<dim3((unsigned)gx, H), fm::kThreads_, fm::kSmem, st>>>(tx, tp, tx2, tp2, w, row_mask, row_mask2, rows, H,
+                                                                                     scale, pair);
   return check_launch("rfa_feature_map_fwd");
 }
 
@@ -193,8 +211,10 @@ static_assert(kRing == 3 && bNum * 8 + 4 <= 256, "feature_map_bwd: barrier block
 
 __global__ void __launch_bounds__(fmb::kThreads_, 1)
 feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gp,
-                          const __grid_constant__ CUtensorMap tm_gx, const float* __restrict__ w, float* __restrict__ g_w,
-                          const uint8_t* __restrict__ row_mask, int64_t rows, int H, float scale) {
+                          const __grid_constant__ CUtensorMap tm_gx, const __grid_constant__ CUtensorMap tm_x2,
+                          const __grid_constant__ CUtensorMap tm_gp2, const __grid_constant__ CUtensorMap tm_gx2,
+                          const float* __restrict__ w, float* __restrict__ g_w, const uint8_t* __restrict__ row_mask,
+                          const uint8_t* __restrict__ row_mask2, int64_t rows, int H, float scale, int pair) {
   using namespace fmb;
   extern __shared__ unsigned char fmb_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fmb_raw) + 1023) & ~uintptr_t(1023));
@@ -205,8 +225,15 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
   const bool want_gw = g_w != nullptr;
-  const int ntile_all = (int)((rows + kTC - 1) / kTC);
+  // pair != 0: two arrays of the same shape share the launch, W_h and the g_W accumulator (q and k of one layer):
+  // virtual tile v is row tile v / 2 of array v % 2
+  const int ntile_all = (int)((rows + kTC - 1) / kTC) * (pair ? 2 : 1);
   const int ntile = blockIdx.x < ntile_all ? (ntile_all - 1 - blockIdx.x) / gridDim.x + 1 : 0;   // tiles blockIdx.x, +gridDim.x, ...
+  auto tile_row0 = [&](int i, int& which) -> int {
+    const int v = blockIdx.x + i * gridDim.x;
+    which = pair ? (v & 1) : 0;
+    return (pair ? (v >> 1) : v) * kTC;
+  };
   if (tid == 0) {
     for (int i = 0; i < kRing; ++i) {
       mbar_init(&bars[bFull + i], 1);
@@ -221,12 +248,13 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
     mbar_fence_init();
     // the first tiles are requested before the rest of the prologue (W_h, tensor memory), which their flight then hides
     for (int i = 0; i < kRing && i < ntile; ++i) {
-      const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+      int which;
+      const int row0 = tile_row0(i, which);
       unsigned char* base = sm + i * kStage;
       mbar_arrive_expect_tx(&bars[bFull + i], kStage);
-      tma_load_3d(base + kX, &tm_x, &bars[bFull + i], 0, h, row0);
-      tma_load_3d(base + kGP, &tm_gp, &bars[bFull + i], 0, h, row0);
-      tma_load_3d(base + kGP + kBox, &tm_gp, &bars[bFull + i], 64, h, row0);
+      tma_load_3d(base + kX, which ? &tm_x2 : &tm_x, &bars[bFull + i], 0, h, row0);
+      tma_load_3d(base + kGP, which ? &tm_gp2 : &tm_gp, &bars[bFull + i], 0, h, row0);
+      tma_load_3d(base + kGP + kBox, which ? &tm_gp2 : &tm_gp, &bars[bFull + i], 64, h, row0);
     }
     tma_prefetch_desc(&tm_gx);
   }
@@ -255,12 +283,13 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       for (int i = kRing; i < ntile; ++i) {
         const int sg = i % kRing;
         if (!mbar_wait(&bars[bEmpty + sg], ((i / kRing) + 1) & 1)) { tc_fail(11); break; }
-        const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+        int which;
+        const int row0 = tile_row0(i, which);
         unsigned char* base = sm + sg * kStage;
         mbar_arrive_expect_tx(&bars[bFull + sg], kStage);
-        tma_load_3d(base + kX, &tm_x, &bars[bFull + sg], 0, h, row0);
-        tma_load_3d(base + kGP, &tm_gp, &bars[bFull + sg], 0, h, row0);
-        tma_load_3d(base + kGP + kBox, &tm_gp, &bars[bFull + sg], 64, h, row0);
+        tma_load_3d(base + kX, which ? &tm_x2 : &tm_x, &bars[bFull + sg], 0, h, row0);
+        tma_load_3d(base + kGP, which ? &tm_gp2 : &tm_gp, &bars[bFull + sg], 0, h, row0);
+        tma_load_3d(base + kGP + kBox, which ? &tm_gp2 : &tm_gp, &bars[bFull + sg], 64, h, row0);
       }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -307,9 +336,11 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
     for (int i = 0; i < ntile; ++i) {
       const int st = i & 1, sg = i % kRing;
       unsigned char* base = sm + sg * kStage;
-      const int64_t grow = (int64_t)(blockIdx.x + i * gridDim.x) * kTC + row;
+      int which;
+      const int64_t grow = (int64_t)tile_row0(i, which) + row;
+      const uint8_t* mask = which ? row_mask2 : row_mask;
       // a masked row's features are constant zeros: no gradient flows through it
-      const float scale_row = (row_mask && grow < rows && row_mask[grow]) ? 0.f : scale;
+      const float scale_row = (mask && grow < rows && mask[grow]) ? 0.f : scale;
       if (!mbar_wait(&bars[bFull + sg], (i / kRing) & 1)) { tc_fail(16); break; }
       float ss = 0.f;                                  // |x|^2 of this thread's row
 #pragma unroll
@@ -363,7 +394,8 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
     for (int i = 0; ok && i < ntile; ++i) {
       const int st = i & 1, sg = i % kRing;
       unsigned char* base = sm + sg * kStage;
-      const int row0 = (blockIdx.x + i * gridDim.x) * kTC;
+      int which;
+      const int row0 = tile_row0(i, which);
       if (!mbar_wait(&bars[bFull + sg], (i / kRing) & 1)) { tc_fail(19); ok = false; break; }
       // gx' of this tile exists only after the issuer saw group 1's gh, which group 1 signalled after writing rn: waiting
       // for the product orders the read of rn too.  (Group 1 may run two tiles ahead of this group, so this group must
@@ -410,7 +442,7 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
       fence_async_smem();
       if (!epi_sync(&bars[bEpi], epi_phase)) { tc_fail(23); ok = false; break; }
       if (etid == 0) {
-        tma_store_3d(&tm_gx, sm + kOut, 0, h, row0);
+        tma_store_3d(which ? &tm_gx2 : &tm_gx, sm + kOut, 0, h, row0);
         tma_store_commit();
       }
     }
@@ -442,19 +474,25 @@ feature_map_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-// x, g_x [rows][H][64] fp16, g_phi [rows][H][128] fp16, w [H][64][64] fp32, g_w [H][64][64] fp32 accumulated into (may be null)
-int launch_feature_map_bwd_tc(const __half* x, const float* w, const uint8_t* row_mask, const __half* g_phi, __half* g_x, float* g_w,
+// x, g_x [rows][H][64] fp16, g_phi [rows][H][128] fp16, w [H][64][64] fp32, g_w [H][64][64] fp32 accumulated into (may be null);
+// x2 / g_phi2 / g_x2 / row_mask2: a second set of arrays of the same shape sharing the launch and g_w (x2 null: none)
+int launch_feature_map_bwd_tc(const __half* x, const float* w, const uint8_t* row_mask, const __half* g_phi, __half* g_x,
+                              const __half* x2, const uint8_t* row_mask2, const __half* g_phi2, __half* g_x2, float* g_w,
                               int64_t rows, int H, float scale, int sms, cudaStream_t st) {
-  CUtensorMap tx, tg, to;
-  if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tg, g_phi, rows, H, 128, kTC) || make_tmap_rows(&to, g_x, rows, H, 64, kTC))
+  const int pair = x2 != nullptr;
+  CUtensorMap tx, tg, to, tx2, tg2, to2;
+  if (make_tmap_rows(&tx, x, rows, H, 64, kTC) || make_tmap_rows(&tg, g_phi, rows, H, 128, kTC) || make_tmap_rows(&to, g_x, rows, H, 64, kTC) ||
+      make_tmap_rows(&tx2, pair ? x2 : x, rows, H, 64, kTC) || make_tmap_rows(&tg2, pair ? g_phi2 : g_phi, rows, H, 128, kTC) ||
+      make_tmap_rows(&to2, pair ? g_x2 : g_x, rows, H, 64, kTC))
     return fail(RFA_EDEVICE, "feature_map_bwd: cuTensorMapEncodeTiled failed or is unavailable");
   cudaError_t e = cudaFuncSetAttribute(feature_map_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fmb::kSmem);
   if (e != cudaSuccess) return fail((int)e, "feature_map_bwd: cannot reserve %u bytes of shared memory: %s", fmb::kSmem, cudaGetErrorString(e));
-  const int64_t ntile = (rows + kTC - 1) / kTC;
+  const int64_t ntile = (rows + kTC - 1) / kTC * (pair ? 2 : 1);
   int64_t gx = sms / H;                          // one CTA per SM (shared memory): never more CTAs than SMs, or a second wave runs
   if (gx > ntile) gx = ntile;
   if (gx < 1) gx = 1;
-  feature_map_bwd_tc_kernel<<<dim3((unsigned)gx, H), fmb::kThreads_, fmb::kSmem, st>>>(tx, tg, to, w, g_w, row_mask, rows, H, scale);
+  feature_map_bwd_tc_kernel<<<dim3((unsigned)gx, H), fmb::kThreads_, fmb::kSmem, st>>>(tx, tg, to, tx2, tg2, to2, w, g_w, row_mask,
+                                                                                        row_mask2, rows, H, scale, pair);
   return check_launch("rfa_feature_map_bwd");
 }
 

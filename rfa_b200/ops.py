@@ -86,6 +86,49 @@ def feature_map_bwd(x: Tensor, w: Tensor, g_phi: Tensor, scale: float, need_gw: 
     return g_x, g_w
 
 
+def feature_map_pair_supported(x_a: Tensor, x_b: Tensor, w: Tensor) -> bool:
+    """Whether the one-launch feature map of two arrays takes these: same shape, fp16, head_dim = proj_dim = 64."""
+    return (x_a.shape == x_b.shape and x_a.dtype == x_b.dtype == torch.float16 and x_a.is_cuda and x_b.is_cuda
+            and tuple(w.shape[-2:]) == (64, 64))
+
+
+def feature_map_fwd_pair(x_a: Tensor, x_b: Tensor, w: Tensor, scale: float, row_mask_a: Optional[Tensor] = None,
+                         row_mask_b: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    """phi of x_a and of x_b (same shape [..., H, 64], fp16; w [H, 64, 64]) in one launch."""
+    H, D, d = w.shape
+    assert x_a.shape == x_b.shape and x_a.shape[-2] == H and x_a.shape[-1] == d, (x_a.shape, x_b.shape, w.shape)
+    require_half(x_a, x_b)
+    x_a, x_b = x_a.contiguous(), x_b.contiguous()
+    w = w.contiguous().float()
+    phi_a = torch.empty(*x_a.shape[:-1], 2 * D, dtype=torch.float16, device=x_a.device)
+    phi_b = torch.empty_like(phi_a)
+    rows = x_a.numel() // (H * d)
+    ma, mb = _row_mask(row_mask_a, rows, x_a.device), _row_mask(row_mask_b, rows, x_a.device)
+    with _guard(x_a):
+        check(_lib.load().rfa_feature_map_fwd_pair(ptr(x_a), ptr(x_b), ptr(w), ptr(ma), ptr(mb), ptr(phi_a), ptr(phi_b), rows, H, d, D,
+                                                   float(scale), stream_of(x_a)), "rfa_feature_map_fwd_pair")
+    return phi_a, phi_b
+
+
+def feature_map_bwd_pair(x_a: Tensor, x_b: Tensor, w: Tensor, g_phi_a: Tensor, g_phi_b: Tensor, scale: float, need_gw: bool,
+                         row_mask_a: Optional[Tensor] = None, row_mask_b: Optional[Tensor] = None):
+    """Backward of ``feature_map_fwd_pair``: (g_x_a, g_x_b, g_w) with g_w the sum of both arrays' contributions (or None)."""
+    H, D, d = w.shape
+    require_half(x_a, x_b)
+    x_a, x_b = x_a.contiguous(), x_b.contiguous()
+    w = w.contiguous().float()
+    g_phi_a, g_phi_b = g_phi_a.contiguous().to(torch.float16), g_phi_b.contiguous().to(torch.float16)
+    g_x_a, g_x_b = torch.empty_like(x_a), torch.empty_like(x_b)
+    g_w = torch.zeros(H, D, d, dtype=torch.float32, device=x_a.device) if need_gw else None
+    rows = x_a.numel() // (H * d)
+    ma, mb = _row_mask(row_mask_a, rows, x_a.device), _row_mask(row_mask_b, rows, x_a.device)
+    with _guard(x_a):
+        check(_lib.load().rfa_feature_map_bwd_pair(ptr(x_a), ptr(x_b), ptr(w), ptr(ma), ptr(mb), ptr(g_phi_a), ptr(g_phi_b), ptr(g_x_a),
+                                                   ptr(g_x_b), ptr(g_w), rows, H, d, D, float(scale), stream_of(x_a)),
+              "rfa_feature_map_bwd_pair")
+    return g_x_a, g_x_b, g_w
+
+
 def gather_random_matrices(bank: Tensor, picks: Tensor, sigma: Optional[Tensor] = None,
                            inv_tau: Optional[Tensor] = None) -> Tensor:
     """bank [N, D, d] (fp16 / fp32, on the device), picks [n] int64 -> [n, D, d] fp32 = sigma[i] * bank[picks[i]] * inv_tau[i]

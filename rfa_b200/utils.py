@@ -164,6 +164,39 @@ class _FeatureMap(torch.autograd.Function):
         return g_x, (g_w.to(w.dtype) if need_w else None), None, None
 
 
+class _FeatureMapPair(torch.autograd.Function):
+    """The feature maps of two arrays that share W (q and k of a self-attention layer) as one launch each way."""
+
+    @staticmethod
+    def forward(ctx, x_a, x_b, w, scale, row_mask_a, row_mask_b):
+        ctx.save_for_backward(x_a, x_b, w)
+        ctx.scale, ctx.masks = scale, (row_mask_a, row_mask_b)
+        return ops.feature_map_fwd_pair(x_a, x_b, w, scale, row_mask_a, row_mask_b)
+
+    @staticmethod
+    def backward(ctx, g_a, g_b):
+        x_a, x_b, w = ctx.saved_tensors
+        need_w = ctx.needs_input_grad[2]
+        g_x_a, g_x_b, g_w = ops.feature_map_bwd_pair(x_a, x_b, w, g_a, g_b, ctx.scale, need_w, ctx.masks[0], ctx.masks[1])
+        return g_x_a, g_x_b, (g_w.to(w.dtype) if need_w else None), None, None, None
+
+
+def random_project_pair(*, x_a: Tensor, x_b: Tensor, random_matrices: Tensor, scale: float = SCALE,
+                        key_padding_mask_b: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    """``random_project`` of two arrays of one shape with the same matrices -- the q and k of a self-attention layer
+    (upstream calls it twice, causal_attention.py:241-248) -- in one launch when the sizes allow (fp16, head_dim =
+    proj_dim = 64), else as two calls.  ``key_padding_mask_b`` ``[bsz, seq_len]`` zeroes the features of x_b's padded
+    positions."""
+    if not ops.feature_map_pair_supported(x_a, x_b, random_matrices):
+        return (random_project(x=x_a, random_matrices=random_matrices, scale=scale),
+                random_project(x=x_b, random_matrices=random_matrices, scale=scale, key_padding_mask=key_padding_mask_b))
+    row_mask = None
+    if key_padding_mask_b is not None and key_padding_mask_b.dim() > 0:
+        assert key_padding_mask_b.shape == (x_b.size(1), x_b.size(0)), (key_padding_mask_b.shape, x_b.shape)
+        row_mask = key_padding_mask_b.to(torch.bool).t().contiguous()
+    return _FeatureMapPair.apply(x_a, x_b, random_matrices, scale, None, row_mask)
+
+
 def random_project(*, x: Tensor, random_matrices: Tensor, scale: float = SCALE,
                    key_padding_mask: Optional[Tensor] = None) -> Tensor:
     """x ``[seq_len, bsz, num_heads, head_dim]``, random_matrices ``[num_heads, proj_dim,

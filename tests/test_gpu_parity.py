@@ -559,3 +559,25 @@ def test_causal_long_sequence_late_tokens(dev):
     for name, a, b in (("out", out, ro), ("gq", gq, rq), ("gk", gk, rk), ("gv", gv, rv)):
         assert_close(a, b, name)
         assert_close(a[tail], b[tail], name + " (last eighth)")
+
+
+@pytest.mark.parametrize("rows,B,H,masked", [(1, 1, 1, False), (300, 2, 3, True), (2048, 8, 16, True)])
+def test_feature_map_pair_equals_two_single_launches(dev, rows, B, H, masked):
+    """rfa_feature_map_fwd_pair / _bwd_pair (q and k of one layer in one launch) against the single-array entry points."""
+    from rfa_b200 import ops
+    gen = torch.Generator().manual_seed(rows + H)
+    w = torch.from_numpy(O.draw_matrices("orf", H, 64, 64, 3)).float().to(dev)
+    xa, xb = (torch.randn(rows, B, H, 64, generator=gen).half().to(dev) for _ in range(2))
+    ga, gb = (torch.randn(rows, B, H, 128, generator=gen).half().to(dev) for _ in range(2))
+    mask = (torch.rand(rows, B, generator=gen) < 0.2).to(dev) if masked else None
+    pa, pb = ops.feature_map_fwd_pair(xa, xb, w, 0.1, None, mask)
+    assert torch.equal(pa, ops.feature_map_fwd(xa, w, 0.1))
+    assert torch.equal(pb, ops.feature_map_fwd(xb, w, 0.1, row_mask=mask))
+    gxa, gxb, gw = ops.feature_map_bwd_pair(xa, xb, w, ga, gb, 0.1, True, None, mask)
+    sa, wa = ops.feature_map_bwd(xa, w, ga, 0.1, True)
+    sb, wb = ops.feature_map_bwd(xb, w, gb, 0.1, True, row_mask=mask)
+    assert torch.equal(gxa, sa) and torch.equal(gxb, sb)
+    assert_close(gw, wa + wb, "g_w of the pair", rel=1e-5, mabs=1e-2)
+    # against the oracle as well (float64 reference of the analytic gradient)
+    want_a, want_wa = O.random_project_backward(xa.float().cpu(), w.cpu(), ga.float().cpu(), 0.1)
+    assert_close(gxa, want_a, "g_x (pair, first array)")
