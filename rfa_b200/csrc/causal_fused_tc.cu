@@ -12,7 +12,7 @@
 //
 // Shared memory holds ONE pair of feature tiles (64 KB; two would not fit beside the raw rings), so the products that
 // read them (A, N, the state update) of chunk c must finish before the features of chunk c + 1 are stored: the feature
-// warps compute a chunk ahead into registers and only the 16 stores per thread sit on that chain.  Tensor memory is
+// warps compute a chunk ahead into registers and only the 8 stores per thread sit on that chain.  Tensor memory is
 // full (A/P 128, N 2 x 80, [S|z] 80, U_q 64, U_k 64 columns), hence a single A/P buffer: scores of chunk c + 1 follow
 // P V of chunk c in the issuing thread's order.
 //
@@ -50,7 +50,8 @@ enum { xFull = 0, xEmpty = 2, vFull = 4, vEmpty = 6, uFull = 8, uFree = 9, phiFu
 // xFull/xEmpty: a raw stage (free once U has been formed from it and both feature groups have taken their rows' norms);
 // vFull/vEmpty: a V tile (free once P V and the state update have read it); uFull/uFree: the U accumulators;
 // phiFull/phiFree: the feature tiles (free = both issuers' products of the chunk are complete); aFull/pFull: scores
-// written / packed; sDone (per N buffer): issuer B's products complete; nFull/nFree: an N buffer; bSt: state tile exported.
+// written / packed; sDone (per N buffer): issuer B's products complete; nFull/nFree: an N buffer; bSt: state tile exported;
+// bCarry: the state entering the sequence has been loaded (the producer starts after it).
 }  // namespace fz
 
 __global__ void __launch_bounds__(fz::kThreads_, 1)
