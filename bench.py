@@ -411,6 +411,39 @@ def extras(device, stream, hbm):
                                 "two_step_algorithmic_bytes": T * BH * (2 * 384 + 768)}
     except Exception as e:  # noqa: BLE001
         out["fused_forward"] = {"error": repr(e)}
+    # ---- one CausalAttention layer, forward + backward, at the headline shape (embed 1024 = 16 heads x 64): the four
+    # projections (cuBLAS), the paired feature map, the causal kernels and the feature map's backward
+    try:
+        from rfa_b200.causal_attention import CausalAttention
+        torch.manual_seed(0)
+        layer = CausalAttention(embed_dim=H * D_HEAD, num_heads=H, head_dim=D_HEAD, proj_dim=D_PROJ).to(device).half()
+        xm = torch.randn(T, B, H * D_HEAD, device=device).half().requires_grad_(True)
+        wm = torch.randn(H, D_PROJ, D_HEAD, device=device).half()
+        upm = torch.randn(T, B, H * D_HEAD, device=device).half()
+
+        def layer_step():
+            xm.grad = None
+            for p_ in layer.parameters():
+                p_.grad = None
+            layer(xm, wm).backward(upm)
+        for _ in range(3):
+            layer_step()
+        side = torch.cuda.Stream(device)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            layer_step()
+        stream.wait_stream(side)
+        ms_l, how = timed_replayed(layer_step, 5, stream)
+        with torch.no_grad():
+            for _ in range(3):
+                layer(xm, wm)
+            ms_i, _ = timed_replayed(lambda: layer(xm, wm), 5, stream)
+        out["layer"] = {"workload": "CausalAttention layer B8 T2048 embed 1024 (16 heads x 64), proj_dim 64, fp16: forward + backward, "
+                                    "and the forward alone without a gradient (feature map inside the attention kernel)",
+                        "timing": how + ", 5 calls", "fwd_bwd_ms": ms_l, "tokens_per_s": B * T / (ms_l * 1e-3),
+                        "no_grad_fwd_ms": ms_i}
+    except Exception as e:  # noqa: BLE001
+        out["layer"] = {"error": repr(e)}
     return out
 
 
