@@ -74,28 +74,51 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc = index, None
+        self.index, self.proc, self.lines, self.reader = index, None, [], None
 
     def __enter__(self):
+        """Starts nvidia-smi and returns once it has printed its first line (its start-up takes a few hundred
+        milliseconds, longer with one per rank): the lines kept are those printed from then on, i.e. under load as long as
+        the caller keeps the GPU busy (``busy_until_sampled``)."""
+        import threading
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-i", str(self.index), "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return self
+        first = threading.Event()
+
+        def pump():
+            for line in self.proc.stdout:
+                if first.is_set():
+                    self.lines.append(line)
+                first.set()
+        self.reader = threading.Thread(target=pump, daemon=True)
+        self.reader.start()
+        first.wait(timeout=10.0)
         return self
+
+    def busy_until_sampled(self, work, want=3, limit_s=2.0):
+        """Keeps the GPU on ``work`` (untimed) until ``want`` lines have been printed since the start."""
+        t_end = time.time() + limit_s
+        while self.proc is not None and len(self.lines) < want and time.time() < t_end:
+            work()
+            torch.cuda.synchronize()
 
     def __exit__(self, *a):
         self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return
-        time.sleep(0.15)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        if self.reader is not None:
+            self.reader.join(timeout=2.0)
+        out = "".join(self.lines)
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
@@ -509,14 +532,19 @@ def long_sequence(steps, warmup, rank, world, device, use_graph=True):
         except Exception as e:                      # noqa: BLE001 -- report and measure eagerly
             mode = f"eager (graph capture failed: {type(e).__name__})"
             torch.cuda.synchronize()
-    barrier()
     with ClockSampler(device.index) as clk:
+        barrier()                                   # after the sampler's start-up, which differs from rank to rank
         ms = timed(held["run"], steps, stream)
         barrier()
-    t = torch.tensor([ms], device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+        t = torch.tensor([ms], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        # the sampler's period is 100 ms: the same step keeps running (untimed) for about 0.35 s so that the clocks
+        # reported are clocks under this load -- the same number of replays on every rank (the step holds collectives)
+        for _ in range(min(2000, int(350.0 / max(ms, 1e-3)) + 1)):
+            held["run"]()
+        barrier()
 
     def release():
         held["run"] = None
@@ -646,8 +674,8 @@ def main():
 
     for _ in range(args.warmup):
         step()
-    barrier()
     with ClockSampler(local_rank) as clk:
+        barrier()                                   # after the sampler's start-up, which differs from rank to rank
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -658,6 +686,9 @@ def main():
         # per-kernel durations, also inside the sampled region
         per = {"causal_fwd": timed(fwd, args.steps, stream), "causal_bwd_q": timed(bwd_q, args.steps, stream),
                "causal_bwd_kv": timed(bwd_kv, args.steps, stream)}
+        # the timed region lasts a few milliseconds and the sampler's period is 100 ms: the same step keeps running
+        # (untimed) until the sampler has printed a few lines, so that the clocks reported are clocks under this load
+        clk.busy_until_sampled(lambda: [step() for _ in range(50)])
     t = torch.tensor([total_ms], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
