@@ -35,14 +35,14 @@ def oracle_features(xq, xk, w, mask):
     return pq, pk.reshape(T, B * H, 128)
 
 
-@pytest.mark.parametrize("T,B,H,masked", [(128, 1, 1, False), (300, 2, 3, False), (300, 2, 3, True), (1000, 2, 4, True),
-                                          (77, 3, 2, False)])
+@pytest.mark.parametrize("T,B,H,masked", [(1, 1, 1, False), (128, 1, 1, False), (129, 2, 1, True), (300, 2, 3, False),
+                                          (300, 2, 3, True), (1000, 2, 4, True), (77, 3, 2, False)])
 def test_fused_forward_against_oracle(dev, T, B, H, masked):
     from rfa_b200 import ops
     xq, xk, v, _, w = raw_inputs(T, B, H, 11)
     mask = None
     if masked:                       # padded keys: the tail of each sequence, a different length per batch element
-        lens = torch.tensor([T - 17 * (b + 1) for b in range(B)])
+        lens = torch.tensor([max(1, T - 17 * (b + 1)) for b in range(B)])
         mask = torch.arange(T)[:, None] >= lens[None, :]
     pq, pk = oracle_features(xq, xk, w, mask)
     want, s_w, z_w = O.causal_forward(pq, pk, v.reshape(T, B * H, 64), return_state=True)
