@@ -21,8 +21,8 @@
 // to run it, so the three chains are issued by three threads); 4..7 = score group; 8..11 = output/state group; 12..19 =
 // query features, 20..27 = key features (two warpgroups each: thread <-> row, and half of the 64 projected columns per
 // warpgroup -- the sines and cosines are the longest step of a chunk and bound by the special-function unit, which
-// sixteen warps keep busier than eight).  Register budgets differ by role (setmaxnreg): issuers 64, score group 104,
-// output/state group 112, feature warps 56.  Within a group thread <-> TMEM lane <-> token row / state row.  All waits
+// sixteen warps keep busier than eight).  Register budgets differ by role (setmaxnreg): issuers 64, score group 96,
+// output/state group 104, feature warps 56.  Within a group thread <-> TMEM lane <-> token row / state row.  All waits
 // are bounded.
 #include <type_traits>
 
@@ -32,6 +32,12 @@
 namespace rfa {
 namespace fz {
 constexpr int kThreads_ = 896;
+// Register budgets per thread by role.  setmaxnreg.inc blocks until the SM's pool holds the registers it asks for, with no
+// time limit: the budgets must leave slack.  (A set that summed to exactly 64 K registers never got its increase and
+// hung the kernel.)  The kernel starts with 72 registers x 896 threads = 63 K; after the changes 61 K.
+constexpr int kRegIssue = 64, kRegScore = 96, kRegOut = 104, kRegFeat = 56;
+static_assert(128 * (kRegIssue + kRegScore + kRegOut + 4 * kRegFeat) + 3072 <= 65536, "causal_fwd_fused: register budgets need slack");
+static_assert(72 * kThreads_ <= 65536, "causal_fwd_fused: launch register count");
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kXq = 0, kXk = kBox, kRaw = 2 * kBox;          // raw ring: two stages of (x_q, x_k)
 constexpr uint32_t kV = 2 * kRaw;                                  // V ring: two stages of one box
@@ -125,7 +131,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
   // Register budgets by role (the kernel starts with 72 per thread): the issuers and the feature warps give some back,
   // the score and output/state groups take more.  Each branch below is one or more whole warpgroups.
   if (warp < 4) {
-  setmaxnreg_dec<64>();
+  setmaxnreg_dec<kRegIssue>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -226,7 +232,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
     }
   }
   } else if (warp < 8) {
-    setmaxnreg_inc<104>();
+    setmaxnreg_inc<kRegScore>();
     // ------------------------------------------------------------------ score group: P = mask(A), row sums
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -272,7 +278,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       mbar_arrive(&bars[pFull]);
     }
   } else if (warp < 12) {
-    setmaxnreg_inc<112>();
+    setmaxnreg_inc<kRegOut>();
     // ------------------------------------------------------------------ output / state group
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // token row in the chunk / state row k
@@ -374,7 +380,7 @@ causal_fwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_xq, const __gr
       z_out[(size_t)bh * kK + row] = __uint_as_float(r[64]);
     }
   } else {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<kRegFeat>();
     // ------------------------------------------------------------------ feature groups: query (warps 12..19), key (20..27)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
